@@ -1,0 +1,114 @@
+// Embedding gather, rotary tables, gated activation, residual add.
+#include "common.cuh"
+
+// x[t, :] = table[token[t], :] * scale.  A token id outside [0, V) writes zeros and sets *bad.
+// Reference: gather then scale, crates/kf-layers/src/basic.rs:35-36.
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float scale,
+                             float* __restrict__ out, int H, int V, int* __restrict__ bad) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < V;
+  if (!ok && threadIdx.x == 0 && bad) atomicExch(bad, 1);
+  const TW* row = table + (size_t)(ok ? tok : 0) * H;
+  float* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? kf_load(row, i) * scale : 0.f;
+}
+
+KF_API int kf_embed(const int* tokens, const void* table, int table_dtype, float scale, float* out,
+                    int T, int H, int V, int* bad_flag, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == KF_F32)
+    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, scale, out, H, V, bad_flag);
+  else if (table_dtype == KF_BF16)
+    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, scale, out, H, V, bad_flag);
+  else
+    return KF_ERR_DTYPE;
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// cos/sin of position * inv_freq[i], all in 32-bit (accurate sincosf: no fast-math in this library).
+// Reference: crates/kf-backend-cuda/src/kernels/rope.cu:4-14.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  const int t = idx / half, i = idx - t * half;
+  const float angle = (float)positions[t] * inv_freq[i];
+  float s, c;
+  sincosf(angle, &s, &c);
+  cos_out[idx] = c;
+  sin_out[idx] = s;
+}
+
+KF_API int kf_rope_table(const int* positions, const float* inv_freq, float* cos_out, float* sin_out,
+                         int T, int half, cudaStream_t stream) {
+  if (T <= 0 || half <= 0) return KF_OK;
+  const int n = T * half;
+  rope_table_kernel<<<kf_ceil_div(n, 256), 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, T, half);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// out[t, j] = act(gu[t, j]) * gu[t, I + j]: gate columns first, up columns second.
+// Reference: crates/kf-backend-cuda/src/kernels/elementwise.cu:42-44.
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int I, int act) {
+  const size_t n = (size_t)T * I;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I, j = idx - t * I;
+    const float g = kf_load(gu, t * 2 * I + j), u = kf_load(gu, t * 2 * I + I + j);
+    kf_store(out, idx, kf_act(g, act) * u);
+  }
+}
+
+KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int act, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  const size_t n = (size_t)T * I;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  if (in_dtype == KF_F32 && out_dtype == KF_F32)
+    gated_act_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, T, I, act);
+  else if (in_dtype == KF_F32 && out_dtype == KF_BF16)
+    gated_act_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gu, (__nv_bfloat16*)out, T, I, act);
+  else if (in_dtype == KF_BF16 && out_dtype == KF_BF16)
+    gated_act_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, act);
+  else
+    return KF_ERR_DTYPE;
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+__global__ void add_kernel(const float* __restrict__ a, float* __restrict__ x, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] += a[i];
+}
+
+KF_API int kf_add(const float* a, float* x, long n, cudaStream_t stream) {
+  if (n <= 0) return KF_OK;
+  const long b = (n + 255) / 256;
+  add_kernel<<<(int)(b > 148 * 16 ? 148 * 16 : b), 256, 0, stream>>>(a, x, (size_t)n);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// dst = (bf16 or f32) copy of src with conversion; used where a 32-bit weight meets bf16 activations.
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ src, TO* __restrict__ dst, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    kf_store(dst, i, kf_load(src, i));
+}
+
+KF_API int kf_convert(const void* src, int src_dtype, void* dst, int dst_dtype, long n, cudaStream_t stream) {
+  if (n <= 0) return KF_OK;
+  const long b = (n + 255) / 256;
+  const int blocks = (int)(b > 148 * 16 ? 148 * 16 : b);
+  if (src_dtype == KF_BF16 && dst_dtype == KF_F32)
+    convert_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (float*)dst, (size_t)n);
+  else if (src_dtype == KF_F32 && dst_dtype == KF_BF16)
+    convert_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)src, (__nv_bfloat16*)dst, (size_t)n);
+  else
+    return KF_ERR_DTYPE;
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

@@ -1,0 +1,24 @@
+// Library-wide state: the last CUDA error text, version, device checks.
+#include "common.cuh"
+#include <string.h>
+#include <stdio.h>
+
+static char g_last_error[512] = "";
+
+extern "C" int kf_record_cuda_error(cudaError_t e) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  return (int)e;
+}
+
+KF_API const char* kf_last_cuda_error() { return g_last_error; }
+
+KF_API int kf_abi_version() { return 1; }
+
+// Compute capability of the current device as major*10+minor, or -1.
+KF_API int kf_device_arch() {
+  int dev = 0, major = 0, minor = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return -1;
+  return major * 10 + minor;
+}

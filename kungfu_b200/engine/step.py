@@ -1,0 +1,247 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere, runs exactly
+those tokens as one batch and returns the logits at the wanted places.  The reference's backend
+takes the same shape of input, rows of several sequences in one pass with per-row tokens,
+positions and sequence ids (crates/kf-core/src/backend.rs:113-129, runs :190-203), though its scheduler
+never mixes prompt rows with decode rows; here that is the normal case.
+
+Per step the host builds one block of 32-bit integers (tokens, positions, the request of each row,
+per request its rows / length / state slot, the block tables of every cache group, the rows whose
+logits are wanted) and sends it to the device in one copy; every kernel of the step reads from it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+
+
+@dataclass
+class StepEntry:
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)      # places among `tokens` whose logits are wanted
+
+
+class StepError(ValueError):
+    pass
+
+
+class BufferPool:
+    """Named device buffers that keep their address from step to step (grown when a step needs more)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._flat: dict[str, torch.Tensor] = {}
+        self.generation = 0                                   # bumps whenever a buffer moves
+
+    def get(self, tag: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = max(n * torch.empty(0, dtype=dtype).element_size(), 16)
+        flat = self._flat.get(tag)
+        if flat is None or flat.numel() < nbytes:
+            grow = nbytes if flat is None else max(nbytes, 2 * flat.numel())
+            flat = torch.empty(grow, dtype=torch.uint8, device=self.device)
+            self._flat[tag] = flat
+            self.generation += 1
+        return flat[: n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(*shape)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() for t in self._flat.values())
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepContext:
+    """Everything parts may read during one step.  Integer arrays live on the device."""
+
+    def __init__(self, runner: "Runner"):
+        self._runner = runner
+        self.act_dtype = runner.act_dtype
+        self.device = runner.device
+        self.memo: dict = {}
+        self.n_rows = 0
+        self.n_reqs = 0
+        self.n_logits = 0
+        self.decode_only = False
+        self.max_rows_per_req = 0
+        # device views, set by Runner._fill
+        self.tokens = self.positions = self.row_req = self.logit_rows = None
+        self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
+        self.block_tables: list[torch.Tensor] = []
+        # host copies
+        self.host: dict[str, np.ndarray] = {}
+
+    def buf(self, tag: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        return self._runner.buffers.get(tag, shape, dtype)
+
+    def cache_view(self, cache_slot: int, writes: bool):
+        return self._runner.cache.view(cache_slot, writes)
+
+
+class Runner:
+    """Owns the model, the cache manager and the device buffers, and runs steps."""
+
+    def __init__(self, model, cache: CacheManager, *, act_dtype: torch.dtype, device):
+        self.model = model
+        self.cache = cache
+        self.act_dtype = act_dtype
+        self.device = torch.device(device)
+        self.buffers = BufferPool(self.device)
+        self.vocab = model.vocab
+        self._staging: list = []                  # ring of (pinned host block, event of its last copy)
+        self._staging_next = 0
+        self._meta_dev: torch.Tensor | None = None
+        self.steps_run = 0
+        self.launch_count_hint = 0
+
+    # ---- metadata -----------------------------------------------------------------------------------
+    def _meta_buffers(self, n_ints: int):
+        """A pinned host block whose last copy has finished, and the device block it is copied to."""
+        cuda = self.device.type == "cuda"
+        if self._meta_dev is None or self._meta_dev.numel() < n_ints:
+            cap = max(n_ints, 1024)
+            cap = 1 << (cap - 1).bit_length()
+            if cuda:
+                torch.cuda.current_stream().synchronize()
+            self._staging = [[torch.empty(cap, dtype=torch.int32, pin_memory=cuda), None] for _ in range(3)]
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self.buffers.generation += 1
+        slot = self._staging[self._staging_next]
+        self._staging_next = (self._staging_next + 1) % len(self._staging)
+        if slot[1] is not None:
+            slot[1].synchronize()
+        return slot, self._meta_dev
+
+    def _fill(self, entries: Sequence[StepEntry]) -> StepContext:
+        cache = self.cache
+        ctx = StepContext(self)
+        B = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        n_out = sum(len(e.want) for e in entries)
+        G = len(cache.groups)
+        # table width: the most pages any request of this step addresses
+        width = 1
+        for e in entries:
+            n_after = cache.length(e.request) + len(e.tokens)
+            width = max(width, -(-n_after // cache.page_size))
+        width = _align4(width)
+        # layout (in ints); every section starts on a 16-byte boundary
+        o = 0
+        sec = {}
+        for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", max(n_out, 1)),
+                        ("req_row_start", B), ("req_n_rows", B), ("req_kv_len", B), ("req_state_slot", B)):
+            sec[name] = (o, n)
+            o += _align4(n)
+        for g in range(G):
+            sec[f"table{g}"] = (o, B * width)
+            o += _align4(B * width)
+        slot, dev = self._meta_buffers(o)
+        host = slot[0]
+        h = host.numpy()
+
+        def view(name):
+            a, n = sec[name]
+            return h[a:a + n]
+
+        tokens, positions, row_req = view("tokens"), view("positions"), view("row_req")
+        logit_rows = view("logit_rows")
+        logit_rows[:] = 0
+        r = 0
+        k = 0
+        max_rows = 0
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            start = cache.length(e.request)
+            tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int64)
+            positions[r:r + n] = np.arange(start, start + n, dtype=np.int32)
+            row_req[r:r + n] = b
+            view("req_row_start")[b] = r
+            view("req_n_rows")[b] = n
+            view("req_kv_len")[b] = start + n
+            view("req_state_slot")[b] = cache.state_slot(e.request)
+            for w in e.want:
+                logit_rows[k] = r + int(w)
+                k += 1
+            for g in range(G):
+                a, _ = sec[f"table{g}"]
+                row = h[a + b * width: a + (b + 1) * width]
+                row[:] = -1
+                tab = cache.block_table(g, e.request)
+                row[:len(tab)] = tab
+            max_rows = max(max_rows, n)
+            r += n
+        dev[:o].copy_(host[:o], non_blocking=True)
+        if self.device.type == "cuda":
+            if slot[1] is None:
+                slot[1] = torch.cuda.Event()
+            slot[1].record()
+
+        def dview(name):
+            a, n = sec[name]
+            return dev[a:a + n]
+
+        ctx.n_rows, ctx.n_reqs, ctx.n_logits = T, B, n_out
+        ctx.max_rows_per_req = max_rows
+        ctx.decode_only = max_rows == 1
+        ctx.tokens, ctx.positions, ctx.row_req = dview("tokens"), dview("positions"), dview("row_req")
+        ctx.logit_rows = dview("logit_rows")[:n_out] if n_out else dview("logit_rows")[:0]
+        ctx.req_row_start, ctx.req_n_rows = dview("req_row_start"), dview("req_n_rows")
+        ctx.req_kv_len, ctx.req_state_slot = dview("req_kv_len"), dview("req_state_slot")
+        ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]
+        ctx.host = {name: view(name).copy() for name in ("positions", "row_req", "req_row_start", "req_n_rows",
+                                                         "req_kv_len", "req_state_slot")}
+        return ctx
+
+    # ---- the step -------------------------------------------------------------------------------------
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if e.request not in self.cache:
+                raise StepError(f"request {e.request!r} is not live")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < self.vocab):
+                    raise StepError(f"request {e.request!r}: token id {t} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        """Run the tokens of `entries` as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
+        in the order of the entries and of each entry's `want`, or None when nothing is wanted.  The result
+        lives in a buffer the next step overwrites.  Raises OutOfPages before touching anything when the
+        pages for the new tokens cannot all be had."""
+        entries = list(entries)
+        if not entries:
+            return None
+        self.validate(entries)
+        reserved = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.request, len(e.tokens))
+                reserved.append(e)
+        except OutOfPages:
+            for e in reserved:
+                self.cache.cancel_reservation(e.request)
+            raise
+        ctx = self._fill(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.commit(e.request, len(e.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,215 @@
+"""The operations parts are written in, each one a hand-written CUDA kernel of `csrc/`.
+
+Every function here checks its arguments on the host and launches on the current CUDA stream.
+There is no CPU implementation and no library fallback: a tensor that is not on a CUDA device, a
+missing compiler or a failed build raises.  (Tests that have no GPU replace this table of
+functions with a slow emulation of their own through `set_override`; the package ships none.)
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+F32, BF16 = 0, 1
+_ACT = {"gelu_tanh": 0, "gelu_erf": 1, "silu": 2}
+_STATUS = {1: "unsupported combination of element types", 2: "unsupported size", 3: "CUDA launch failed",
+           4: "alignment rule broken", 5: "one-time set-up failed"}
+
+MAX_HEAD_DIM = 256
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_lib_lock = threading.Lock()
+_override = None
+
+
+def set_override(impl) -> None:
+    """Tests without a GPU install an object whose attributes replace the functions of this module."""
+    global _override
+    _override = impl
+
+
+def library():
+    """The compiled kernel library (built at first use)."""
+    global _lib
+    if _lib is None:
+        with _lib_lock:
+            if _lib is None:
+                from .csrc import build as _build
+                path = _build.build()
+                lib = ctypes.CDLL(path)
+                lib.kf_last_cuda_error.restype = ctypes.c_char_p
+                _lib = lib
+    return _lib
+
+
+def library_path() -> str:
+    from .csrc import build as _build
+    return os.path.join(_build.build_dir(), _build.LIB_NAME)
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        detail = _STATUS.get(status, f"status {status}")
+        if status == 3:
+            detail += f" ({library().kf_last_cuda_error().decode()})"
+        raise KernelError(f"{what}: {detail}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {t.dtype} is not supported (float32 and bfloat16 are)")
+
+
+def _p(t: torch.Tensor | None):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kungfu_b200 kernels run on CUDA tensors only; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError("kernel arguments must be contiguous")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f(x: float):
+    return ctypes.c_float(x)
+
+
+def _dispatch(name):
+    def deco(fn):
+        def wrapper(*a, **k):
+            if _override is not None:
+                return getattr(_override, name)(*a, **k)
+            return fn(*a, **k)
+        wrapper.__name__ = name
+        wrapper.__doc__ = fn.__doc__
+        return wrapper
+    return deco
+
+
+# ---- size rules ---------------------------------------------------------------------------------------
+
+def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Head sizes the attention kernels take: 2..256, even.  Anything else is refused here, at build time."""
+    if head_dim < 2 or head_dim > MAX_HEAD_DIM or head_dim % 2:
+        raise KernelError(f"head_dim {head_dim} is not supported: the attention kernels take even sizes up to {MAX_HEAD_DIM}")
+    if n_kv_heads < 1 or n_heads % n_kv_heads:
+        raise KernelError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
+
+
+# ---- operations -----------------------------------------------------------------------------------------
+
+@_dispatch("embed")
+def embed(tokens, table, scale: float, out) -> None:
+    """out[t, :] = table[tokens[t], :] * scale (32-bit out).  Token ids are validated by the caller on the host."""
+    T, (V, H) = out.shape[0], table.shape
+    _check(library().kf_embed(_p(tokens), _p(table), _dt(table), _f(scale), _p(out), T, H, V, ctypes.c_void_p(0), _stream()),
+           "embed")
+
+
+@_dispatch("rmsnorm")
+def rmsnorm(x, weight, eps: float, plus_one: bool, out, rows=None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] if rows is given else x[r]) * (weight or 1 + weight)."""
+    n, H = out.shape
+    _check(library().kf_rmsnorm(_p(x), _p(weight), _dt(weight), _f(eps), int(plus_one), _p(out), _dt(out), _p(rows), n, H,
+                                _stream()), "rmsnorm")
+
+
+@_dispatch("add_rmsnorm")
+def add_rmsnorm(branch, weight, eps: float, plus_one: bool, residual, *, next_weight=None, next_eps: float = 0.0,
+                next_plus_one: bool = False, next_out=None) -> None:
+    """residual += rmsnorm(branch) * g; if next_out is given, next_out = rmsnorm(residual) * g_next."""
+    T, H = residual.shape
+    _check(library().kf_add_rmsnorm(_p(branch), _p(weight), _dt(weight), _f(eps), int(plus_one), _p(residual),
+                                    _p(next_weight), _dt(next_weight) if next_weight is not None else F32, _f(next_eps),
+                                    int(next_plus_one), _p(next_out), _dt(next_out) if next_out is not None else F32,
+                                    T, H, _stream()), "add_rmsnorm")
+
+
+@_dispatch("add")
+def add(a, x) -> None:
+    """x += a (32-bit)."""
+    _check(library().kf_add(_p(a), _p(x), ctypes.c_long(x.numel()), _stream()), "add")
+
+
+@_dispatch("linear")
+def linear(x, weight, out, softcap: float = 0.0) -> None:
+    """out[T, N] = x[T, K] . weight[N, K]^T, 32-bit accumulation; softcap > 0 applies cap*tanh(v/cap)."""
+    T, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or tuple(out.shape) != (T, N):
+        raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    _check(library().kf_linear_simt(_p(x), _dt(x), _p(weight), _dt(weight), _p(out), _dt(out), T, N, K, _f(softcap),
+                                    _stream()), "linear")
+
+
+@_dispatch("linear_gated")
+def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
+    """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows."""
+    T = x.shape[0]
+    I = out.shape[1]
+    gu = ctx.buf("ffn_gate_up", (T, 2 * I), torch.float32)
+    linear(x, w_gate_up, gu)
+    _check(library().kf_gated_act(_p(gu), _dt(gu), _p(out), _dt(out), T, I, _ACT[activation], _stream()), "gated_act")
+
+
+@_dispatch("rope_table")
+def rope_table(positions, inv_freq, cos, sin) -> None:
+    """cos/sin[t, i] of positions[t] * inv_freq[i], 32-bit."""
+    T, half = cos.shape
+    _check(library().kf_rope_table(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, half, _stream()), "rope_table")
+
+
+@_dispatch("rope_kv_append")
+def rope_kv_append(qkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_dim: int, ctx, cache, q_out) -> None:
+    """Rotate q and k (pairs i, i+rot/2), write q to q_out and k, v into the pages of `cache` (if it writes)."""
+    T = qkv.shape[0]
+    table = ctx.block_tables[cache.group]
+    _check(library().kf_rope_kv_append(_p(qkv), _p(cos), _p(sin), rot, n_heads, n_kv_heads, head_dim,
+                                       _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
+                                       _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out), int(cache.writes),
+                                       T, _stream()), "rope_kv_append")
+
+
+@_dispatch("paged_attention")
+def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float,
+                    window: int | None) -> None:
+    """Causal (optionally windowed, softcapped) attention of every row of the step over its request's pages."""
+    T = q.shape[0]
+    table = ctx.block_tables[cache.group]
+    _check(library().kf_attention_generic(_p(q), _p(out), _dt(q), _p(cache.pages), _dt(cache.pages), _p(ctx.positions),
+                                          _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, n_heads,
+                                          n_kv_heads, head_dim, _f(scale), _f(softcap), int(window or 0), T, _stream()),
+           "paged_attention")
+
+
+@_dispatch("argmax")
+def argmax(logits, out) -> None:
+    """out[r] = index of the first maximum of logits[r, :] (int32)."""
+    rows, V = logits.shape
+    _check(library().kf_argmax(_p(logits), _p(out), rows, V, _stream()), "argmax")
+
+
+@_dispatch("topk_lse")
+def topk_lse(logits, k: int, out_ids, out_vals, out_lse) -> None:
+    """Top-k ids (falling value, lower id first among equals), their values, and the row's log-sum-exp."""
+    rows, V = logits.shape
+    _check(library().kf_topk_lse(_p(logits), _p(out_ids), _p(out_vals), _p(out_lse), rows, V, k, _stream()), "topk_lse")
+
+
+def device_arch() -> int:
+    return int(library().kf_device_arch())

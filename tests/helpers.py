@@ -1,0 +1,172 @@
+"""Tiny configurations, model folders and traces shared by the tests."""
+from __future__ import annotations
+
+import json
+import os
+import random
+
+import torch
+
+# Two tiny Gemma 2 configurations that differ in every size and option.
+TINY_A = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+    "intermediate_size": 128, "vocab_size": 512, "rope_theta": 10000.0, "sliding_window": 8,
+    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 16,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 64,
+    "hidden_activation": "gelu_pytorch_tanh",
+}
+TINY_B = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32,
+    "intermediate_size": 320, "vocab_size": 1000, "rope_theta": 1000000.0, "sliding_window": 16,
+    "attn_logit_softcapping": 20.0, "final_logit_softcapping": 15.0, "query_pre_attn_scalar": 24,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 128,
+    "hidden_activation": "gelu_pytorch_tanh",
+}
+# Sizes that are no power of two anywhere, three query heads per kv head, an odd layer count, head size 48.
+TINY_C = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 5, "hidden_size": 120, "num_attention_heads": 9, "num_key_value_heads": 3, "head_dim": 48,
+    "intermediate_size": 200, "vocab_size": 777, "rope_theta": 50000.0, "sliding_window": 24,
+    "attn_logit_softcapping": 30.0, "final_logit_softcapping": 0.0, "query_pre_attn_scalar": 100,
+    "rms_norm_eps": 1e-4, "tie_word_embeddings": True, "max_position_embeddings": 256,
+    "hidden_activation": "gelu_pytorch_tanh",
+}
+
+
+def write_model(folder: str, cfg_dict: dict, seed: int, dtype=torch.bfloat16, matrix_scale: float = 1.0):
+    """A model folder with random weights through the framework's random-weights mode."""
+    from kungfu_b200.api import load_config
+    from kungfu_b200.weights import write_random_model
+    cfg = load_config(dict(cfg_dict))
+    write_random_model(folder, cfg, seed, dtype=dtype)
+    with open(os.path.join(folder, "config.json"), "w") as f:      # keep the test's own dictionary
+        json.dump(cfg_dict, f)
+    return folder
+
+
+def read_tensors(folder: str) -> dict:
+    """Tensors of a model folder through the safetensors library (not the framework's reader)."""
+    from safetensors.torch import load_file
+    return load_file(os.path.join(folder, "model.safetensors"))
+
+
+def random_tokens(n: int, vocab: int, seed: int) -> list[int]:
+    rng = random.Random(seed)
+    return [rng.randrange(vocab) for _ in range(n)]
+
+
+# ---- traces: lists of steps in the format bin/trace_run reads --------------------------------------------
+
+def trace_whole(reqs: dict) -> list[dict]:
+    """Each request alone and whole, all logits wanted."""
+    steps = []
+    for i, (rid, toks) in enumerate(reqs.items()):
+        steps.append({"step": i, "entries": [{"id": rid, "tokens": list(toks), "want": list(range(len(toks)))}],
+                      "end": [rid]})
+    return steps
+
+
+def trace_decode_tail(reqs: dict, tail: int = 32) -> list[dict]:
+    """Most of each request in one step, the last `tail` tokens one by one."""
+    steps = []
+    s = 0
+    for rid, toks in reqs.items():
+        n = len(toks)
+        head = max(1, n - tail)
+        steps.append({"step": s, "entries": [{"id": rid, "tokens": list(toks[:head]), "want": list(range(head))}], "end": []})
+        s += 1
+        for i in range(head, n):
+            steps.append({"step": s, "entries": [{"id": rid, "tokens": [toks[i]], "want": [0]}], "end": []})
+            s += 1
+        steps[-1]["end"] = [rid]
+    return steps
+
+
+def trace_chunks(reqs: dict, sizes=(7, 2, 5, 3, 2, 11, 4, 2, 9)) -> list[dict]:
+    """Each request in portions of changing size, down to two tokens."""
+    steps = []
+    s = 0
+    for rid, toks in reqs.items():
+        i = 0
+        c = 0
+        while i < len(toks):
+            n = min(sizes[c % len(sizes)], len(toks) - i)
+            c += 1
+            steps.append({"step": s, "entries": [{"id": rid, "tokens": list(toks[i:i + n]), "want": list(range(n))}], "end": []})
+            s += 1
+            i += n
+        steps[-1]["end"] = [rid]
+    return steps
+
+
+def trace_mixed(reqs: dict, seed: int = 0, max_live: int = 4, prefill_frac: float = 0.6) -> list[dict]:
+    """Up to `max_live` requests live at once: portions of some beside single tokens of others, some requests
+    skipping steps; a finished request makes room for the next one."""
+    rng = random.Random(seed)
+    waiting = list(reqs.items())
+    live: dict = {}                     # rid -> [tokens, fed]
+    steps = []
+    s = 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = [list(toks), 0]
+        entries, end = [], []
+        for rid, (toks, fed) in list(live.items()):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                    # this request sits the step out
+            left = len(toks) - fed
+            if fed < int(len(toks) * prefill_frac) and left > 1:
+                n = min(left, rng.choice([2, 3, 5, 8, 13]))
+            else:
+                n = 1
+            entries.append({"id": rid, "tokens": toks[fed:fed + n], "want": list(range(n))})
+            live[rid][1] = fed + n
+            if fed + n == len(toks):
+                end.append(rid)
+                del live[rid]
+        if not entries:
+            continue
+        steps.append({"step": s, "entries": entries, "end": end})
+        s += 1
+    return steps
+
+
+def trace_max_tokens(steps: list[dict], page: int = 64) -> int:
+    """The most tokens live requests hold at any time, each request's count rounded up to `page`."""
+    held: dict = {}
+    best = 0
+    for st in steps:
+        for e in st["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        best = max(best, sum(-(-n // page) * page for n in held.values()))
+        for rid in st["end"]:
+            held.pop(rid, None)
+    return best
+
+
+def run_trace_with_runner(runner, steps: list[dict]) -> dict:
+    """Drive a Runner with a trace; returns {(request, position): logits row (CPU float32)}."""
+    from kungfu_b200.engine import StepEntry
+    out = {}
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            if e["id"] not in runner.cache:
+                runner.cache.add_request(e["id"])
+            entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
+        starts = {e["id"]: runner.cache.length(e["id"]) for e in st["entries"]}
+        logits = runner.step(entries)
+        if logits is not None:
+            logits = logits.float().cpu()
+            k = 0
+            for e in st["entries"]:
+                for w in e["want"]:
+                    out[(e["id"], starts[e["id"]] + w)] = logits[k].clone()
+                    k += 1
+        for rid in st["end"]:
+            runner.cache.release(rid)
+        runner.cache.check()
+    return out

@@ -1,0 +1,48 @@
+"""The engine's host logic against the plain implementation, kernels replaced by the CPU stand-in.
+
+Covers the same four ways of cutting the work that the GPU tests cover: whole, most of it then token
+by token, portions of changing size, and mixed batches with so few pages that they are used again."""
+import pytest
+import torch
+
+import helpers
+import plain_gemma2
+from kungfu_b200 import api
+
+
+def _runner(folder, cfg_dict, page_size, max_tokens):
+    cfg, model = api.load_model(folder, dtype="float32", device="cpu")
+    return api.make_runner(cfg, model, dtype="float32", device="cpu", page_size=page_size, max_tokens=max_tokens,
+                           max_requests=8, max_context=cfg_dict["max_position_embeddings"])
+
+
+def _reference(folder, cfg_dict, reqs):
+    tensors = helpers.read_tensors(folder)
+    return {rid: plain_gemma2.forward(cfg_dict, tensors, toks).float() for rid, toks in reqs.items()}
+
+
+def _compare(got, ref, tol):
+    assert got, "no logits came back"
+    worst = 0.0
+    for (rid, pos), row in got.items():
+        worst = max(worst, float((row - ref[rid][pos]).abs().max()))
+    assert worst < tol, f"max abs logit difference {worst}"
+
+
+CASES = [(helpers.TINY_A, [5, 17, 23, 40], 4), (helpers.TINY_B, [1, 31, 40, 70], 8), (helpers.TINY_C, [3, 50, 64, 29, 33], 16)]
+
+
+@pytest.mark.parametrize("cfg_dict,lengths,page", CASES, ids=["A", "B", "C"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+def test_cpu_modes_match_plain(tmp_path, cpu_ops, cfg_dict, lengths, page, mode):
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=11, dtype=torch.float32)
+    reqs = {f"r{i}": helpers.random_tokens(n, cfg_dict["vocab_size"], 100 + i) for i, n in enumerate(lengths)}
+    ref = _reference(folder, cfg_dict, reqs)
+    steps = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 12),
+             "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=3)}[mode](reqs)
+    runner = _runner(folder, cfg_dict, page, helpers.trace_max_tokens(steps, page))
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert len(got) == sum(lengths)
+    _compare(got, ref, 2e-4)
+    assert runner.cache.n_live == 0
+    assert all(f == g.pool.n_pages for f, g in zip(runner.cache.free_pages(), runner.cache.groups))

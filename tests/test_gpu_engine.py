@@ -1,0 +1,109 @@
+"""The engine on the GPU against the plain implementation: every way of cutting the work, in 32-bit and bfloat16."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_gemma2
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# rel = max|got - ref| / max|ref| over all wanted rows.  32-bit: rounding of sums only.  bfloat16: activations and
+# cached keys/values are rounded to 8 bits of mantissa at every product (the reference's own bound for
+# half-precision caches is 2e-2, crates/kf-backend-cuda/tests/common/mod.rs:181-187).
+TOL = {"float32": 2e-4, "bfloat16": 2e-2}
+
+CASES = {"A": (helpers.TINY_A, [5, 17, 23, 40], 4), "B": (helpers.TINY_B, [1, 31, 40, 70], 8),
+         "C": (helpers.TINY_C, [3, 50, 64, 29, 120], 16)}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, (cfg, lengths, page) in CASES.items():
+        folder = helpers.write_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=21, dtype=torch.bfloat16)
+        reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 300 + i) for i, n in enumerate(lengths)}
+        tensors = helpers.read_tensors(folder)
+        ref = {rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+        out[name] = (folder, cfg, reqs, ref, page)
+    return out
+
+
+def _check(got, ref, tol):
+    scale = max(float(r.abs().max()) for r in ref.values())
+    worst, wrong_top = 0.0, 0
+    for (rid, pos), row in got.items():
+        worst = max(worst, float((row - ref[rid][pos]).abs().max()))
+        wrong_top += int(torch.argmax(row) != torch.argmax(ref[rid][pos]))
+    assert worst / scale < tol, f"rel err {worst / scale:.3e} (first wrong top-1 count {wrong_top}/{len(got)})"
+    return wrong_top
+
+
+def _steps(mode, reqs):
+    return {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 32),
+            "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=5)}[mode](reqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_modes_match_plain(models, name, mode, dtype):
+    from kungfu_b200 import api
+    folder, cfg, reqs, ref, page = models[name]
+    steps = _steps(mode, reqs)
+    c, model = api.load_model(folder, dtype=dtype, device=DEV)
+    runner = api.make_runner(c, model, dtype=dtype, device=DEV, page_size=page,
+                             max_tokens=helpers.trace_max_tokens(steps, page), max_requests=8,
+                             max_context=cfg["max_position_embeddings"])
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _check(got, ref, TOL[dtype])
+    assert runner.cache.n_live == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, tmp_path, dtype):
+    """bin/trace_run as a user runs it: steps on standard input, logits files out, `done` after every step."""
+    folder, cfg, reqs, ref, _ = models["B"]
+    steps = helpers.trace_mixed(reqs, seed=9)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(helpers.trace_max_tokens(steps, 64))],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.split("\n") if l] == [f"done {s['step']}" for s in steps]
+    V = cfg["vocab_size"]
+    got, fed = {}, {}
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        arr = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, V)
+        k = 0
+        for e in s["entries"]:
+            start = fed.get(e["id"], 0)
+            for w in e["want"]:
+                got[(e["id"], start + w)] = torch.from_numpy(arr[k].copy())
+                k += 1
+            fed[e["id"]] = start + len(e["tokens"])
+    _check(got, ref, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_and_first_tokens(models, dtype):
+    """A request decoded token by token from its very first token, far past the window and over many pages."""
+    from kungfu_b200 import api
+    folder, cfg, _, _, _ = models["A"]
+    toks = helpers.random_tokens(64, cfg["vocab_size"], 77)
+    ref = plain_gemma2.forward(cfg, helpers.read_tensors(folder), toks).float()
+    c, model = api.load_model(folder, dtype=dtype, device=DEV)
+    runner = api.make_runner(c, model, dtype=dtype, device=DEV, page_size=4, max_tokens=64, max_requests=2, max_context=64)
+    steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []} for i, t in enumerate(toks)]
+    steps[-1]["end"] = ["x"]
+    got = helpers.run_trace_with_runner(runner, steps)
+    _check(got, {"x": ref}, TOL[dtype])

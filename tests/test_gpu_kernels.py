@@ -1,0 +1,300 @@
+"""Each kernel alone against a plain torch reference of the same operation, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def rel_err(a, b):
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from kungfu_b200 import ops as o
+    o.library()
+    return o
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(ops, dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(301, 70, generator=g).to(dtype).to(DEV)
+    tokens = torch.randint(0, 301, (37,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(37, 70, device=DEV)
+    ops.embed(tokens, table, 8.3666, out)
+    ref = table.float()[tokens.long()] * torch.tensor(8.3666, dtype=torch.float32)
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("H", [70, 2304, 5000])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)])
+def test_rmsnorm(ops, H, wdtype, odtype):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(19, H, generator=g) * 3).to(DEV)
+    w = (torch.randn(H, generator=g) * 0.1).to(wdtype).to(DEV)
+    rows = torch.tensor([3, 0, 18, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        n = 19 if r is None else 4
+        out = torch.empty(n, H, dtype=odtype, device=DEV)
+        ops.rmsnorm(x, w, 1e-5, True, out, r)
+        xs = (x if r is None else x[r.long()]).double()
+        ref = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-5) * (1 + w.double())
+        assert rel_err(out, ref) < (1e-5 if odtype == torch.float32 else 6e-3)
+
+
+@pytest.mark.parametrize("H", [96, 3584])
+@pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(ops, H, odtype):
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(11, H, generator=g).to(DEV)
+    x = torch.randn(11, H, generator=g).to(DEV)
+    w1 = (torch.randn(H, generator=g) * 0.1).to(DEV)
+    w2 = (torch.randn(H, generator=g) * 0.1).to(DEV)
+    ad, xd = a.double(), x.double()
+    x_ref = xd + ad * torch.rsqrt(ad.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + w1.double())
+    n_ref = x_ref * torch.rsqrt(x_ref.pow(2).mean(-1, keepdim=True) + 1e-4) * w2.double()
+    x1 = x.clone()
+    ops.add_rmsnorm(a, w1, 1e-6, True, x1)
+    assert rel_err(x1, x_ref) < 1e-5
+    x2 = x.clone()
+    out = torch.empty(11, H, dtype=odtype, device=DEV)
+    ops.add_rmsnorm(a, w1, 1e-6, True, x2, next_weight=w2, next_eps=1e-4, next_plus_one=False, next_out=out)
+    assert torch.equal(x1, x2)
+    assert rel_err(out, n_ref) < (1e-5 if odtype == torch.float32 else 6e-3)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 1000, 96), (7, 130, 200), (65, 777, 123), (130, 64, 2304)])
+@pytest.mark.parametrize("xd,wd", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_linear(ops, T, N, K, xd, wd):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, K, generator=g).to(xd).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(wd).to(DEV)
+    ref = x.double() @ w.double().T
+    out = torch.empty(T, N, device=DEV)
+    ops.linear(x, w, out)
+    assert rel_err(out, ref) < 2e-6 * math.sqrt(K) + 1e-6
+    capped = torch.empty(T, N, device=DEV)
+    ops.linear(x, w, capped, softcap=0.7)
+    assert rel_err(capped, 0.7 * torch.tanh(ref / 0.7)) < 1e-5
+    # a row's result does not depend on the other rows of the launch
+    one = torch.empty(1, N, device=DEV)
+    ops.linear(x[T - 1:T].contiguous(), w, one)
+    assert torch.equal(one[0], out[T - 1])
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
+def test_linear_gated(ops, act):
+    from cpu_ops import _act
+
+    class Ctx:
+        def buf(self, tag, shape, dtype):
+            return torch.empty(shape, dtype=dtype, device=DEV)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(9, 72, generator=g).to(DEV)
+    w = (torch.randn(2 * 50, 72, generator=g) * 0.3).to(DEV)
+    out = torch.empty(9, 50, device=DEV)
+    ops.linear_gated(x, w, out, act, Ctx())
+    gu = x.double() @ w.double().T
+    ref = _act(act, gu[:, :50]) * gu[:, 50:]
+    assert rel_err(out, ref) < 1e-5
+
+
+def test_rope_table(ops):
+    pos = torch.tensor([0, 1, 5, 100, 8191], dtype=torch.int32, device=DEV)
+    inv = (10000.0 ** (-2.0 * torch.arange(24, dtype=torch.float64) / 48)).float().to(DEV)
+    cos = torch.empty(5, 24, device=DEV)
+    sin = torch.empty(5, 24, device=DEV)
+    ops.rope_table(pos, inv, cos, sin)
+    ang = (pos.float()[:, None] * inv[None, :]).double()          # the 32-bit angle is the contract
+    assert float((cos.double() - torch.cos(ang)).abs().max()) < 1e-6
+    assert float((sin.double() - torch.sin(ang)).abs().max()) < 1e-6
+
+
+class _View:
+    def __init__(self, pages, page_size, writes=True):
+        self.pages, self.page_size, self.group, self.writes = pages, page_size, 0, writes
+
+
+class _Ctx:
+    def __init__(self, positions, row_req, table):
+        self.positions, self.row_req, self.block_tables = positions, row_req, [table]
+
+
+def _paged_setup(dtype, nh, nkv, d, P, lens, seed, scramble=True):
+    """Random requests of the given lengths with their K/V spread over scrambled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-n // P) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist() if scramble else list(range(n_pages))
+    pages = torch.zeros(n_pages, 2, nkv, P, d, dtype=dtype)
+    width = max(-(-n // P) for n in lens)
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    ks, vs = [], []
+    nxt = 0
+    for r, n in enumerate(lens):
+        k = torch.randn(n, nkv, d, generator=g).to(dtype)
+        v = torch.randn(n, nkv, d, generator=g).to(dtype)
+        ks.append(k)
+        vs.append(v)
+        for i in range(-(-n // P)):
+            pg = perm[nxt]
+            nxt += 1
+            table[r, i] = pg
+            m = min(P, n - i * P)
+            pages[pg, 0, :, :m] = k[i * P:i * P + m].transpose(0, 1)
+            pages[pg, 1, :, :m] = v[i * P:i * P + m].transpose(0, 1)
+    return pages, table, ks, vs
+
+
+def _attn_ref(q, k, v, pos, nh, nkv, scale, cap, window):
+    """q [nh, d] at position pos against keys k, v [n, nkv, d] (double)."""
+    lo = max(0, pos - window + 1) if window else 0
+    out = []
+    for h in range(nh):
+        kh, vh = k[lo:pos + 1, h // (nh // nkv)].double(), v[lo:pos + 1, h // (nh // nkv)].double()
+        s = (kh @ q[h].double()) * scale
+        if cap > 0:
+            s = cap * torch.tanh(s / cap)
+        out.append(torch.softmax(s, 0) @ vh)
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (9, 3, 48, 8, 24, 0.0),
+                                                   (8, 4, 256, 64, 100, 50.0), (5, 5, 112, 32, None, 30.0), (16, 2, 128, 64, 4096, 50.0)])
+def test_paged_attention(ops, dtype, nh, nkv, d, P, window, cap):
+    lens = [1, 37, 150, 70]
+    pages, table, ks, vs = _paged_setup(dtype, nh, nkv, d, P, lens, seed=5)
+    # rows: the whole of request 1, the last row of request 2, rows 60..69 of request 3, the only row of request 0
+    rows = [(1, p) for p in range(37)] + [(2, 149)] + [(3, p) for p in range(60, 70)] + [(0, 0)]
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(len(rows), nh, d, generator=g).to(dtype)
+    # make one far key stand out for one row: scale a key and the query that should find it
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV))
+    out = torch.empty(len(rows), nh * d, dtype=dtype, device=DEV)
+    ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
+    ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
+    assert rel_err(out.view(len(rows), nh, d), ref) < (2e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(ops, dtype):
+    """One key among hundreds carries the answer: its score is made to stand out, on a page of its own."""
+    nh, nkv, d, P = 4, 2, 32, 16
+    n = 600
+    for far in (0, 15, 16, 333, 599 - 1):
+        pages, table, ks, vs = _paged_setup(dtype, nh, nkv, d, P, [n], seed=7)
+        q = torch.zeros(1, nh, d)
+        q[0, :, 3] = 40.0
+        k = ks[0].float() * 0.01
+        k[far, :, 3] = 10.0
+        v = vs[0].float()
+        for i in range(-(-n // P)):
+            pg = int(table[0, i])
+            m = min(P, n - i * P)
+            pages[pg, 0, :, :m] = k[i * P:i * P + m].transpose(0, 1).to(dtype)
+        ctx = _Ctx(torch.tensor([n - 1], dtype=torch.int32, device=DEV), torch.tensor([0], dtype=torch.int32, device=DEV), table.to(DEV))
+        out = torch.empty(1, nh * d, dtype=dtype, device=DEV)
+        ops.paged_attention(q.view(1, nh * d).to(dtype).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, 1.0, 0.0, None)
+        want = torch.stack([v[far, h // 2] for h in range(nh)]).to(dtype).float()
+        assert float((out.float().cpu().view(nh, d) - want).abs().max()) < 2e-2, far
+
+
+def test_window_edge(ops):
+    """The key exactly `window` behind must not be seen, the one at window - 1 must."""
+    nh, nkv, d, P, W = 2, 1, 16, 4, 8
+    n = 30
+    pages, table, ks, vs = _paged_setup(torch.float32, nh, nkv, d, P, [n], seed=8)
+    pos = n - 1
+    for back, seen in ((W - 1, True), (W, False)):
+        k = ks[0].clone() * 0.0
+        k[pos - back, :, 0] = 30.0
+        for i in range(-(-n // P)):
+            pg = int(table[0, i])
+            m = min(P, n - i * P)
+            pages[pg, 0, :, :m] = k[i * P:i * P + m].transpose(0, 1)
+        q = torch.zeros(1, nh * d)
+        q[0, 0] = 30.0
+        q[0, d] = 30.0
+        ctx = _Ctx(torch.tensor([pos], dtype=torch.int32, device=DEV), torch.tensor([0], dtype=torch.int32, device=DEV), table.to(DEV))
+        out = torch.empty(1, nh * d, device=DEV)
+        ops.paged_attention(q.to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, 1.0, 0.0, W)
+        target = vs[0][pos - back, 0]
+        close = float((out.cpu()[0, :d] - target).abs().max()) < 1e-3
+        assert close == seen
+
+
+@pytest.mark.parametrize("qd,kvd", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("nh,nkv,d,rot,P", [(4, 2, 16, 16, 4), (9, 3, 48, 32, 8), (8, 4, 256, 256, 64), (3, 1, 80, 0, 16)])
+def test_rope_kv_append(ops, qd, kvd, nh, nkv, d, rot, P):
+    g = torch.Generator().manual_seed(9)
+    lens = [20, 7]
+    starts = [13, 0]                   # request 0 continues at position 13, request 1 starts
+    T = sum(lens)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g)
+    positions = torch.tensor([starts[0] + i for i in range(lens[0])] + [starts[1] + i for i in range(lens[1])], dtype=torch.int32)
+    row_req = torch.tensor([0] * lens[0] + [1] * lens[1], dtype=torch.int32)
+    n_pages = 16
+    table = torch.full((2, 12), -1, dtype=torch.int32)
+    table[0, :9] = torch.tensor([5, 2, 9, 0, 11, 3, 14, 7, 1])
+    table[1, :2] = torch.tensor([4, 8])
+    pages = torch.full((n_pages, 2, nkv, P, d), 7.0, dtype=kvd)
+    half = rot // 2
+    inv = (10000.0 ** (-2.0 * torch.arange(max(half, 1), dtype=torch.float64) / max(rot, 2))).float()
+    ang = positions.float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    ctx = _Ctx(positions.to(DEV), row_req.to(DEV), table.to(DEV))
+    q_out = torch.empty(T, nh * d, dtype=qd, device=DEV)
+    view = _View(pages.to(DEV), P)
+    ops.rope_kv_append(qkv.to(DEV), cos.to(DEV) if rot else None, sin.to(DEV) if rot else None, rot, nh, nkv, d, ctx, view, q_out)
+
+    def rope(x):                       # x [T, heads, d] double
+        x = x.clone()
+        if rot:
+            a, b = x[..., :half].clone(), x[..., half:rot].clone()
+            c, s = cos.double()[:, None, :], sin.double()[:, None, :]
+            x[..., :half] = a * c - b * s
+            x[..., half:rot] = a * s + b * c
+        return x
+    q_ref = rope(qkv[:, :nh * d].double().view(T, nh, d))
+    k_ref = rope(qkv[:, nh * d:(nh + nkv) * d].double().view(T, nkv, d))
+    v_ref = qkv[:, (nh + nkv) * d:].double().view(T, nkv, d)
+    tol = 1e-6 if qd == torch.float32 else 5e-3
+    assert rel_err(q_out.view(T, nh, d), q_ref) < tol
+    got = view.pages.cpu()
+    touched = torch.zeros(n_pages, P, dtype=torch.bool)
+    for t in range(T):
+        r, pos = int(row_req[t]), int(positions[t])
+        pg = int(table[r, pos // P])
+        touched[pg, pos % P] = True
+        assert rel_err(got[pg, 0, :, pos % P], k_ref[t]) < tol
+        assert rel_err(got[pg, 1, :, pos % P], v_ref[t]) < tol
+    untouched = got.float()[:, :, :, :, :][~touched[:, None, None, :].expand(n_pages, 2, nkv, P)]
+    assert bool((untouched == 7.0).all()), "a slot outside the step's positions was written"
+
+
+@pytest.mark.parametrize("V", [512, 1000, 256000])
+def test_argmax_and_topk(ops, V):
+    g = torch.Generator().manual_seed(10)
+    logits = torch.randn(5, V, generator=g)
+    logits[1, 7] = logits[1, V - 3] = 99.0          # equal maxima: the first wins
+    logits[2] = torch.round(logits[2] * 2) / 2       # many ties
+    dev = logits.to(DEV)
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(dev, out)
+    assert out.tolist() == torch.argmax(logits, -1).tolist() and out[1].item() == 7
+    for k in (1, 40, 64):
+        ids = torch.empty(5, k, dtype=torch.int32, device=DEV)
+        vals = torch.empty(5, k, device=DEV)
+        lse = torch.empty(5, device=DEV)
+        ops.topk_lse(dev, k, ids, vals, lse)
+        order = torch.argsort(-logits.double(), dim=-1, stable=True)[:, :k]
+        assert ids.cpu().tolist() == order.tolist()
+        assert torch.equal(vals.cpu(), torch.gather(logits, 1, order))
+        assert float((lse.cpu().double() - torch.logsumexp(logits.double(), -1)).abs().max()) < 1e-4
