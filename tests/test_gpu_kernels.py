@@ -10,7 +10,8 @@ DEV = "cuda:0"
 
 
 def rel_err(a, b):
-    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+    a, b = a.detach().cpu().double(), b.detach().cpu().double()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
 @pytest.fixture(scope="module")
