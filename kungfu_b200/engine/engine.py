@@ -1,0 +1,171 @@
+"""The engine a user drives: requests in (token ids), tokens out.
+
+`Engine` wraps a model, a cache manager, the step runner, the scheduler and the sampler.  The reference's
+counterpart is a `Session` under a `Scheduler` (crates/kf-engine/src/session.rs:84-103,
+crates/kf-serve/src/engine.rs:375-430); its `generate` command is `Engine.generate` here
+(crates/kungfu/src/main.rs:611-645: seed 42, greedy at temperature 0).
+"""
+from __future__ import annotations
+
+import sys
+import time
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..sampling.sampler import CANDIDATES, Candidates, Sampling, sample, sample_sparse
+from .scheduler import Portion, Request, Scheduler
+from .step import Runner, StepEntry
+
+
+def emit_event(name: str, **fields) -> None:
+    """One structured line on stderr, `kungfu event=<name> k=v ...` (reference: crates/kf-core/src/event.rs:31-44)."""
+    parts = [f"kungfu event={name}"] + [f"{k}={v}" for k, v in fields.items()]
+    print(" ".join(parts), file=sys.stderr, flush=True)
+
+
+class Engine:
+    def __init__(self, model_dir: str | None = None, *, config=None, seed: int = 0, dtype="bfloat16", device="cuda:0",
+                 ctx: int | str = 4096, batch: int = 512, parallel: int = 8, page_size: int | None = None,
+                 max_tokens_in_cache: int | None = None, events: bool = False, runner: Runner | None = None,
+                 cuda_graphs: bool = True):
+        """`model_dir`: folder with config.json and model.safetensors; or `config` (typed configuration, dictionary
+        or config.json path) with `seed` for random weights.  `ctx`: context length per request ('auto' = the
+        model's trained length); `batch`: most tokens one step runs; `parallel`: most live requests.
+        `max_tokens_in_cache`: size of each cache group's pool in tokens (default: parallel * ctx)."""
+        from .. import api
+        self.events = events
+        if runner is not None:
+            self.runner = runner
+            self.cfg = None
+        else:
+            self.device = api.require_cuda(device)
+            ops.library()
+            t0 = time.time()
+            if model_dir is not None:
+                self.cfg, model = api.load_model(model_dir, dtype=dtype, device=self.device)
+            elif config is not None:
+                self.cfg, model = api.random_model(config, seed, dtype=dtype, device=self.device)
+            else:
+                raise ValueError("Engine needs a model folder or a configuration")
+            trained = getattr(self.cfg, "max_position_embeddings", 8192)
+            n_ctx = trained if ctx == "auto" else min(int(ctx), trained) if ctx else trained
+            page = page_size or api.DEFAULT_PAGE_SIZE
+            pool_tokens = max_tokens_in_cache or parallel * (-(-n_ctx // page) * page)
+            self.runner = api.make_runner(self.cfg, model, dtype=dtype, device=self.device, page_size=page,
+                                          max_tokens=pool_tokens, max_requests=parallel, max_context=n_ctx)
+            self.runner.cuda_graphs = cuda_graphs
+            if events:
+                emit_event("ready", model=self.cfg.architecture, dtype=str(api.parse_dtype(dtype)).split(".")[-1],
+                           weight_bytes=model.weight_bytes(), cache_bytes_per_token=self.runner.cache.bytes_per_token(),
+                           pool_tokens=pool_tokens, ctx=n_ctx, load_s=f"{time.time() - t0:.2f}")
+        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=batch, max_requests=parallel)
+        self._next_id = 0
+        self.requests: dict[Hashable, Request] = {}
+        self._t_start: dict = {}
+        dev = self.runner.device
+        self._ids_dev = None
+        self._cand_k = CANDIDATES
+
+    # ---- requests ---------------------------------------------------------------------------------------
+    def add_request(self, ids: Sequence[int], sampling: Sampling | None = None, *, max_tokens: int = 64,
+                    eos: Sequence[int] | None = None, ignore_eos: bool = False, seed: int = 42,
+                    request_id: Hashable | None = None) -> Hashable:
+        if request_id is None:
+            request_id = self._next_id
+            self._next_id += 1
+        if request_id in self.requests and self.requests[request_id].status != "finished":
+            raise ValueError(f"request id {request_id!r} is in use")
+        vocab = self.runner.vocab
+        for t in ids:
+            if not (0 <= int(t) < vocab):
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        if eos is None:
+            eos = tuple(getattr(self.cfg, "eos_token_id", ()) or ()) if self.cfg is not None else ()
+        req = Request(request_id, list(ids), sampling or Sampling(temperature=0.0), max_tokens=max_tokens,
+                      eos=tuple(eos), ignore_eos=ignore_eos, seed=seed)
+        self.requests[request_id] = req
+        self._t_start[request_id] = time.time()
+        self.scheduler.add(req)
+        return request_id
+
+    def cancel(self, request_id: Hashable) -> None:
+        req = self.requests[request_id]
+        if req.status != "finished":
+            self.scheduler.finish(req, "cancelled")
+
+    @property
+    def idle(self) -> bool:
+        return self.scheduler.idle
+
+    # ---- one step -----------------------------------------------------------------------------------------
+    def step(self) -> list[tuple]:
+        """Plan and run one step.  Returns (request id, token, finish reason or None) for every token produced,
+        and (request id, None, reason) for requests that ended without one (no_fit)."""
+        n_fin = len(self.scheduler.finished)
+        plan = self.scheduler.schedule()
+        events = [(r.id, None, r.finish_reason) for r in self.scheduler.finished[n_fin:]]
+        if not plan:
+            return events
+        entries = []
+        for p in plan:
+            toks = p.request.slice(p.start, p.n)
+            entries.append(StepEntry(p.request.id, toks, [p.n - 1] if p.wants_logits else []))
+        logits = self.runner.step(entries)
+        for p in plan:
+            self.scheduler.advance(p)
+        wanting = [p for p in plan if p.wants_logits]
+        if wanting:
+            tokens = self._pick(logits, [p.request for p in wanting])
+            for p, tok in zip(wanting, tokens):
+                reason = self.scheduler.on_token(p.request, tok)
+                events.append((p.request.id, tok, reason))
+                if reason is not None and self.events:
+                    self._request_event(p.request)
+        return events
+
+    def _pick(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
+        """One token per row of `logits` under each request's sampling."""
+        n = len(reqs)
+        if all(r.sampling.greedy for r in reqs):
+            out = self.runner.buffers.get("picked_ids", (n,), torch.int32)
+            ops.argmax(logits, out)
+            return out.cpu().tolist()
+        k = min(self._cand_k, logits.shape[1])
+        ids = self.runner.buffers.get("cand_ids", (n, k), torch.int32)
+        vals = self.runner.buffers.get("cand_vals", (n, k), torch.float32)
+        lse = self.runner.buffers.get("cand_lse", (n,), torch.float32)
+        ops.topk_lse(logits, k, ids, vals, lse)
+        ids_h, vals_h, lse_h = ids.cpu().numpy(), vals.cpu().numpy(), lse.cpu().numpy()
+        picked = []
+        for i, r in enumerate(reqs):
+            recent = r.output
+            c = Candidates(ids_h[i], vals_h[i], float(lse_h[i]), logits.shape[1])
+            tok = sample_sparse(c, r.sampling, recent, r.rng)
+            if tok is None:                              # the candidates do not settle it: take the whole row
+                tok = sample(logits[i].cpu().numpy(), r.sampling, recent, r.rng)
+            picked.append(int(tok))
+        return picked
+
+    def _request_event(self, r: Request) -> None:
+        dt = max(time.time() - self._t_start.get(r.id, time.time()), 1e-9)
+        emit_event("request", id=r.id, prompt_tokens=len(r.prompt), completion_tokens=len(r.output),
+                   finish=r.finish_reason, preempted=r.n_preempted, seconds=f"{dt:.3f}")
+
+    # ---- whole generations --------------------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], sampling: Sampling | None = None, *, max_tokens: int = 64,
+                 eos: Sequence[int] | None = None, ignore_eos: bool = False, seed: int = 42) -> list[list[int]]:
+        """Token ids in, generated token ids out, one list per prompt (host lists both ways)."""
+        ids = [self.add_request(p, sampling, max_tokens=max_tokens, eos=eos, ignore_eos=ignore_eos, seed=seed + i)
+               for i, p in enumerate(prompts)]
+        while any(self.requests[i].status != "finished" for i in ids):
+            before = sum(len(self.requests[i].output) for i in ids)
+            ev = self.step()
+            if not ev and before == sum(len(self.requests[i].output) for i in ids) and self.scheduler.idle:
+                break
+        return [list(self.requests[i].output) for i in ids]
+
+    def finish_reason(self, request_id: Hashable) -> str | None:
+        return self.requests[request_id].finish_reason

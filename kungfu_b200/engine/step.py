@@ -102,6 +102,8 @@ class Runner:
         self._staging_next = 0
         self._meta_dev: torch.Tensor | None = None
         self.steps_run = 0
+        self.last_meta_ints = 0
+        self.cuda_graphs = False
         self.launch_count_hint = 0
 
     # ---- metadata -----------------------------------------------------------------------------------
@@ -146,6 +148,7 @@ class Runner:
             sec[f"table{g}"] = (o, B * width)
             o += _align4(B * width)
         slot, dev = self._meta_buffers(o)
+        self.last_meta_ints = o
         host = slot[0]
         h = host.numpy()
 

@@ -70,15 +70,15 @@ def build(cfg: Gemma2Config, w: WeightStore) -> DecoderModel:
         w_gate_up = _stack([w.take(p + "mlp.gate_proj.weight", (I, H)), w.take(p + "mlp.up_proj.weight", (I, H))])
         w_down = w.take(p + "mlp.down_proj.weight", (H, I))
         w.release(p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight")
-        if w.faulty:
+        norms = [rms(p + n) for n in ("input_layernorm.weight", "post_attention_layernorm.weight",
+                                      "pre_feedforward_layernorm.weight", "post_feedforward_layernorm.weight")]
+        if w.faulty:                                # keep claiming tensors so the error lists everything; build nothing
             continue
         mixer = PagedAttention(wqkv, wo, n_heads=cfg.num_attention_heads, n_kv_heads=cfg.num_key_value_heads,
                                head_dim=cfg.head_dim, scale=cfg.attention_scale,
                                softcap=cfg.attn_logit_softcapping, window=cfg.window_of(l), position=rope)
         ffn = GatedFfn(w_gate_up, w_down, cfg.activation)
-        layers.append(SandwichBlock(rms(p + "input_layernorm.weight"), mixer, rms(p + "post_attention_layernorm.weight"),
-                                    rms(p + "pre_feedforward_layernorm.weight"), ffn,
-                                    rms(p + "post_feedforward_layernorm.weight")))
+        layers.append(SandwichBlock(norms[0], mixer, norms[1], norms[2], ffn, norms[3]))
     final_norm = rms("model.norm.weight")
     out = w.take_optional("lm_head.weight", (cfg.vocab_size, H))
     if out is None:

@@ -55,7 +55,22 @@ def library_path() -> str:
     return os.path.join(_build.build_dir(), _build.LIB_NAME)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (graph replays add the kernels they hold)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if status != 0:
         detail = _STATUS.get(status, f"status {status}")
         if status == 3:

@@ -46,3 +46,47 @@ def test_cpu_modes_match_plain(tmp_path, cpu_ops, cfg_dict, lengths, page, mode)
     _compare(got, ref, 2e-4)
     assert runner.cache.n_live == 0
     assert all(f == g.pool.n_pages for f, g in zip(runner.cache.free_pages(), runner.cache.groups))
+
+
+def _engine(folder, cfg_dict, *, page, pool_tokens, batch, parallel):
+    from kungfu_b200.engine.engine import Engine
+    cfg, model = api.load_model(folder, dtype="float32", device="cpu")
+    runner = api.make_runner(cfg, model, dtype="float32", device="cpu", page_size=page, max_tokens=pool_tokens,
+                             max_requests=parallel, max_context=cfg_dict["max_position_embeddings"])
+    return Engine(runner=runner, batch=batch, parallel=parallel)
+
+
+def test_generate_matches_plain_greedy_and_survives_preemption(tmp_path, cpu_ops):
+    """Greedy ids through the scheduler equal the plain implementation's, also when pages run out and a request
+    is preempted and recomputed."""
+    from kungfu_b200.sampling import Sampling
+    cfg_dict = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=4, dtype=torch.float32)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg_dict["vocab_size"], 50 + n) for n in (5, 17, 23)]
+    want = [plain_gemma2.greedy(cfg_dict, tensors, p, 8) for p in prompts]
+    roomy = _engine(folder, cfg_dict, page=4, pool_tokens=256, batch=16, parallel=4)
+    assert roomy.generate(prompts, Sampling(temperature=0.0), max_tokens=8) == want
+    assert roomy.scheduler.n_preemptions == 0
+    # all three are admitted (2 pages each) and then outgrow a pool of 9 pages: someone has to be preempted
+    short = [helpers.random_tokens(n, cfg_dict["vocab_size"], 90 + n) for n in (5, 7, 6)]
+    want_short = [plain_gemma2.greedy(cfg_dict, tensors, p, 8) for p in short]
+    tight = _engine(folder, cfg_dict, page=4, pool_tokens=36, batch=16, parallel=4)
+    assert tight.generate(short, Sampling(temperature=0.0), max_tokens=8) == want_short
+    assert tight.scheduler.n_preemptions > 0
+    assert tight.runner.cache.n_live == 0 and tight.runner.cache.free_pages() == [9, 9]
+
+
+def test_temperature_sampling_is_reproducible(tmp_path, cpu_ops):
+    from kungfu_b200.sampling import Sampling
+    cfg_dict = helpers.TINY_B
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=6, dtype=torch.float32)
+    prompts = [helpers.random_tokens(n, cfg_dict["vocab_size"], 70 + n) for n in (1, 31)]
+    outs = []
+    for _ in range(2):
+        e = _engine(folder, cfg_dict, page=8, pool_tokens=256, batch=7, parallel=4)
+        outs.append(e.generate(prompts, Sampling(temperature=0.8, top_k=0, top_p=1.0), max_tokens=12, seed=9))
+    assert outs[0] == outs[1] and all(len(o) == 12 for o in outs[0])
+    e = _engine(folder, cfg_dict, page=8, pool_tokens=256, batch=7, parallel=4)
+    other = e.generate(prompts, Sampling(temperature=0.8, top_k=0, top_p=1.0), max_tokens=12, seed=10)
+    assert other != outs[0]
