@@ -1,0 +1,420 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) with TMA-fed shared memory and the
+// accumulator in tensor memory:   out[T, N] = x[T, K] . w[N, K]^T,  32-bit accumulation.
+//
+// Shape of the kernel.  The weight tile is the MMA's "A" operand (128 rows of w = 128 output features = the 128
+// lanes of tensor memory) and the activation tile its "B" operand (BN token rows, BN in {16..256}), both K-major
+// in shared memory with the 128-byte swizzle, 64 k-elements per stage.  So the accumulator holds D[feature, token],
+// the same kernel serves decode (BN = 16, many stages of pure weight streaming) and prefill (BN = 256), and an
+// epilogue thread owns one output feature: for a given token the 32 lanes of a warp store 32 consecutive features.
+//   warp 0   : one lane issues the TMA loads (cp.async.bulk.tensor.2d) stage by stage
+//   warp 1   : allocates tensor memory; one lane issues tcgen05.mma (4 per stage, K = 16 each) and the commits
+//   warps 2-5: epilogue, each reads its quarter of the 128 lanes with tcgen05.ld and stores
+// Epilogues: plain 32-bit store with optional softcap (logits), bfloat16 store, and the gated feed-forward
+// (two accumulators, gate rows and up rows of the stacked matrix against the same activation tile, out =
+// act(gate) * up).  Split-K (grid z) writes 32-bit partials; the CTA that arrives last for a tile sums them in
+// split order and runs the epilogue, so the result does not depend on arrival order.
+// Ragged edges (N, T, K not multiples of the tile) are zero-filled by TMA and masked at the store.
+// Every wait on an mbarrier is bounded: after the limit the kernel records an error code and leaves through the
+// common exit that frees tensor memory.
+// The reference runs these products as 32-bit SIMT tiles (crates/kf-backend-cuda/src/kernels/quant.cuh:110-171).
+#include "common.cuh"
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+constexpr int BM = 128;            // output features per tile (tensor-memory lanes)
+constexpr int BK = 64;             // k elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr long WAIT_LIMIT = 40L * 1000 * 1000;
+
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_GATED = 2 };
+enum { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_ACC = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (long i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(const void* smem) {
+  const uint32_t a = smem_u32(smem);
+  uint64_t d = 0;
+  d |= (uint64_t)((a & 0x3FFFF) >> 4);          // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // version
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+struct Tile {
+  static constexpr int COLS = BN < 32 ? 32 : BN;                 // tensor-memory columns per accumulator
+  static constexpr int A_BYTES = BM * BK * 2;                    // 16 KB
+  static constexpr int B_BYTES = BN * BK * 2;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+               void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
+               int stages, float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ error_flag) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int NACC = GATED ? 2 : 1;
+  constexpr int COLS = Tile<BN>::COLS;
+  constexpr int TMEM_COLS = COLS * NACC;
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  int* s_flags = (int*)(tmem_slot + 1);                           // [0] abort, [1] arrival order of this CTA
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+  const int splits = gridDim.z;
+  const int nkb_total = (K + BK - 1) / BK;
+  const int kb_per = (nkb_total + splits - 1) / splits;
+  const int kb_begin = blockIdx.z * kb_per;
+  const int kb_end = min(nkb_total, kb_begin + kb_per);
+  const int nkb = kb_end - kb_begin;                              // >= 1 by the host's choice of splits
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    s_flags[0] = 0;
+    s_flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ------------------------------------------------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % stages;
+        if (i >= stages && !mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
+          atomicExch(error_flag, ERR_WAIT_EMPTY);
+          s_flags[0] = 1;
+          break;
+        }
+        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(st, &tm_w, &full[s], k, f0);
+        if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[s], k, up_offset + f0);
+        tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -------------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % stages;
+        if (!mbar_wait(&full[s], (i / stages) & 1)) {
+          atomicExch(error_flag, ERR_WAIT_FULL);
+          s_flags[0] = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+        const uint64_t da = umma_desc(st);
+        const uint64_t db = umma_desc(st + Tile<BN>::A_BYTES * NACC);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);            // 32 bytes per K = 16 step
+          umma(tmem_base, da + koff, db + koff, idesc, accumulate);
+          if (GATED) umma(tmem_base + COLS, umma_desc(st + Tile<BN>::A_BYTES) + koff, db + koff, idesc, accumulate);
+        }
+        umma_commit(&empty[s]);                                               // frees the stage when the MMAs have read it
+      }
+      umma_commit(acc_full);                                                   // accumulator complete (or abandoned)
+    }
+  } else {
+    // ---- epilogue: warps 2..5, each owns the lane quarter (warp % 4) ---------------------------------------------
+    const int quarter = warp & 3;
+    const int f = f0 + quarter * 32 + lane;                                    // this thread's output feature
+    const bool acc_ok = mbar_wait(acc_full, 0);
+    if (!acc_ok && lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool good = acc_ok && s_flags[0] == 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int n_out = GATED ? up_offset : N;                                   // features this launch produces
+    const int pw = GATED ? 2 * up_offset : N;                                  // width of a partial row
+
+    auto finish = [&](float v, float u) -> float {
+      if (EPI == EPI_GATED) return kf_act(v, act) * u;
+      if (EPI == EPI_F32) return kf_softcap(v, softcap);
+      return v;
+    };
+    auto store = [&](int t, float r) {
+      if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
+      else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
+    };
+
+    if (good) {
+      if (splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16], u[16];
+          tmem_ld16(lane_addr + c0, v);
+          if (GATED) tmem_ld16(lane_addr + COLS + c0, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < T && f < n_out) store(t, finish(v[j], GATED ? u[j] : 0.f));
+          }
+        }
+      } else {
+        float* mine = partial + (size_t)blockIdx.z * T * pw;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16], u[16];
+          tmem_ld16(lane_addr + c0, v);
+          if (GATED) tmem_ld16(lane_addr + COLS + c0, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < T && f < n_out) {
+              mine[(size_t)t * pw + f] = v[j];
+              if (GATED) mine[(size_t)t * pw + up_offset + f] = u[j];
+            }
+          }
+        }
+      }
+    }
+    if (splits > 1) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        s_flags[1] = atomicAdd(&counters[tile], 1);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_flags[1] == splits - 1) {                                          // last to arrive: reduce in split order
+        __threadfence();
+        const int t_end = min(T, t0 + BN);
+        if (f < n_out) {
+          for (int t = t0; t < t_end; ++t) {
+            float v = 0.f, u = 0.f;
+            for (int z = 0; z < splits; ++z) {
+              const float* p = partial + ((size_t)z * T + t) * pw;
+              v += __ldcg(p + f);
+              if (GATED) u += __ldcg(p + up_offset + f);
+            }
+            store(t, finish(v, u));
+          }
+        }
+        if (warp == 2 && lane == 0) counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
+      }
+    }
+  }
+  // ---- common exit: everyone meets, then tensor memory is freed by the warp that allocated it ------------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+std::mutex g_map_mutex;
+std::map<std::tuple<const void*, long, long, int>, CUtensorMap> g_maps;
+
+// A 2-D map over a row-major [rows, cols] bfloat16 matrix with boxes of [box_rows, 64] and the 128-byte swizzle.
+bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto key = std::make_tuple(base, rows, cols, box_rows);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = m;
+  *out = m;
+  return true;
+}
+
+constexpr int SMEM_LIMIT = 220 * 1024;
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
+           int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
+  constexpr int NACC = EPI == EPI_GATED ? 2 : 1;
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
+  const int nkb = (K + BK - 1) / BK;
+  const int kb_per = (nkb + splits - 1) / splits;
+  int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  if (stages > kb_per) stages = kb_per;
+  if (stages > 12) stages = 12;
+  if (stages < 1) return KF_ERR_SIZE;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
+  static bool configured = false;                      // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    configured = true;
+  }
+  const int n_feat = EPI == EPI_GATED ? up_offset : N;
+  dim3 grid(kf_ceil_div(n_feat, BM), kf_ceil_div(T, BN), splits);
+  gemm_tc_kernel<BN, EPI><<<grid, THREADS, smem, stream>>>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
+                                                           partial, counters, error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+template <int EPI>
+int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
+              int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<16, EPI>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, splits, partial, counters, error_flag, s);
+    case 32: return launch<32, EPI>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, splits, partial, counters, error_flag, s);
+    case 64: return launch<64, EPI>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, splits, partial, counters, error_flag, s);
+    case 128: return launch<128, EPI>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, splits, partial, counters, error_flag, s);
+    case 256: return launch<256, EPI>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, splits, partial, counters, error_flag, s);
+  }
+  return KF_ERR_SIZE;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
+KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
+  return (K % 8 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)w & 15) == 0) && encode_fn() != nullptr;
+}
+
+// Choice of token tile and split-K for a launch; also used by the caller to size the partial buffer.
+KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
+  int bn = 16;
+  while (bn < T && bn < 256) bn *= 2;
+  if (gated && bn > 256) bn = 256;
+  const int nkb = (K + BK - 1) / BK;
+  const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
+  int splits = 1;
+  if (tiles < 120) {                                   // fewer tiles than SMs: cut K so that every SM streams weights
+    splits = (int)((148 + tiles - 1) / tiles);
+    if (splits > 16) splits = 16;
+    if (splits > nkb) splits = nkb;
+    const int kb_per = (nkb + splits - 1) / splits;
+    splits = (nkb + kb_per - 1) / kb_per;              // no empty split
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+  return KF_OK;
+}
+
+// mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out, 2 = gated: w = [gate; up] stacked
+// ([2*N, K]), out[T, N] = act(gate) * up in bfloat16.  `partial` must hold splits * T * (gated ? 2N : N) floats when
+// the plan says splits > 1; `counters` one zero-initialised int per output tile (they are left zero).
+KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, float softcap, int act,
+                        int bn, int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return KF_OK;
+  if (K <= 0 || K % 8 != 0) return KF_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return KF_ERR_ALIGN;
+  if (splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
+  const int w_rows = mode == EPI_GATED ? 2 * N : N;
+  CUtensorMap tw, tx;
+  if (!tensor_map(w, w_rows, K, BM, &tw) || !tensor_map(x, T, K, bn, &tx)) return KF_ERR_SETUP;
+  const int up_offset = mode == EPI_GATED ? N : 0;
+  switch (mode) {
+    case EPI_F32: return launch_bn<EPI_F32>(bn, tw, tx, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
+    case EPI_BF16: return launch_bn<EPI_BF16>(bn, tw, tx, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
+    case EPI_GATED: return launch_bn<EPI_GATED>(bn, tw, tx, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
+  }
+  return KF_ERR_SIZE;
+}

@@ -161,13 +161,79 @@ def add(a, x) -> None:
     _check(library().kf_add(_p(a), _p(x), ctypes.c_long(x.numel()), _stream()), "add")
 
 
+# ---- scratch memory of the split-K products and the device error word ---------------------------------------
+
+_scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor, "error": tensor, "retired": [tensors]}
+use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
+
+
+def _dev_scratch(device) -> dict:
+    key = (device.type, device.index)
+    sc = _scratch.get(key)
+    if sc is None:
+        sc = {"partial": torch.empty(1 << 20, dtype=torch.float32, device=device),
+              "counters": torch.zeros(8192, dtype=torch.int32, device=device),
+              "error": torch.zeros(1, dtype=torch.int32, device=device), "retired": []}
+        _scratch[key] = sc
+    return sc
+
+
+def _partial(device, n_floats: int) -> torch.Tensor:
+    sc = _dev_scratch(device)
+    if sc["partial"].numel() < n_floats:
+        sc["retired"].append(sc["partial"])          # a captured graph may still point at it
+        sc["partial"] = torch.empty(max(n_floats, 2 * sc["partial"].numel()), dtype=torch.float32, device=device)
+    return sc["partial"]
+
+
+def device_error(device=None) -> int:
+    """The error word kernels with bounded waits write (0 = none).  Reading it waits for the device."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    sc = _scratch.get((device.type, device.index))
+    return 0 if sc is None else int(sc["error"].item())
+
+
+def raise_on_device_error(device=None) -> None:
+    code = device_error(device)
+    if code:
+        raise KernelError(f"a kernel gave up waiting (code {code}: 1 = operands never arrived, 2 = stage never freed, "
+                          f"3 = accumulator never completed)")
+
+
+def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> bool:
+    """Launch the tcgen05 product if it takes these operands; False if the generic kernel must run."""
+    T, K = x.shape
+    lib = library()
+    if not (use_tensor_cores and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and lib.kf_linear_tc_supported(_p(x), _p(weight), K)):
+        return False
+    bn, splits = ctypes.c_int(0), ctypes.c_int(0)
+    lib.kf_linear_tc_plan(T, N, K, int(mode == 2), ctypes.byref(bn), ctypes.byref(splits))
+    sc = _dev_scratch(x.device)
+    tiles = -(-N // 128) * -(-T // bn.value)
+    partial = None
+    if splits.value > 1:
+        if tiles > sc["counters"].numel():
+            return False
+        partial = _partial(x.device, splits.value * T * (2 * N if mode == 2 else N))
+    _check(lib.kf_linear_tc(_p(x), _p(weight), _p(out), mode, T, N, K, _f(softcap), act, bn.value, splits.value,
+                            _p(partial), _p(sc["counters"]), _p(sc["error"]), _stream()), "linear (tensor cores)")
+    return True
+
+
 @_dispatch("linear")
 def linear(x, weight, out, softcap: float = 0.0) -> None:
-    """out[T, N] = x[T, K] . weight[N, K]^T, 32-bit accumulation; softcap > 0 applies cap*tanh(v/cap)."""
+    """out[T, N] = x[T, K] . weight[N, K]^T, 32-bit accumulation; softcap > 0 applies cap*tanh(v/cap).
+    bfloat16 operands run on the tensor cores (tcgen05) when rows are multiples of 16 bytes; everything else,
+    and the whole 32-bit path, runs the generic 32-bit FMA kernel."""
     T, K = x.shape
     N = weight.shape[0]
     if weight.shape[1] != K or tuple(out.shape) != (T, N):
         raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    if out.dtype == torch.float32 or softcap == 0.0:
+        if _linear_tc(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0):
+            return
     _check(library().kf_linear_simt(_p(x), _dt(x), _p(weight), _dt(weight), _p(out), _dt(out), T, N, K, _f(softcap),
                                     _stream()), "linear")
 
@@ -177,6 +243,8 @@ def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
     """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows."""
     T = x.shape[0]
     I = out.shape[1]
+    if out.dtype == torch.bfloat16 and _linear_tc(x, w_gate_up, out, 2, I, 0.0, _ACT[activation]):
+        return
     gu = ctx.buf("ffn_gate_up", (T, 2 * I), torch.float32)
     linear(x, w_gate_up, gu)
     _check(library().kf_gated_act(_p(gu), _dt(gu), _p(out), _dt(out), T, I, _ACT[activation], _stream()), "gated_act")

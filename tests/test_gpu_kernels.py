@@ -88,6 +88,58 @@ def test_linear(ops, T, N, K, xd, wd):
     assert torch.equal(one[0], out[T - 1])
 
 
+TC_SHAPES = [(1, 256, 64), (8, 2304, 2048), (5, 130, 200), (16, 128, 96), (17, 1000, 120), (40, 4096, 2304), (64, 777, 320),
+             (100, 300, 72), (256, 512, 512), (300, 2304, 9216), (700, 136, 64), (2048, 256, 128)]
+
+
+@pytest.mark.parametrize("T,N,K", TC_SHAPES)
+def test_linear_tensor_cores(ops, T, N, K):
+    """bfloat16 product on tcgen05 against float64, ragged in every dimension, with and without split-K."""
+    g = torch.Generator().manual_seed(T * 7 + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = x.double() @ w.double().T
+    out = torch.full((T, N), float("nan"), device=DEV)
+    ops.linear(x, w, out)
+    ops.raise_on_device_error()
+    bound = 2e-6 * math.sqrt(K) + 1e-6            # 32-bit accumulation over K terms
+    assert rel_err(out, ref) < bound, "32-bit out"
+    capped = torch.empty(T, N, device=DEV)
+    ops.linear(x, w, capped, softcap=0.9)
+    assert rel_err(capped, 0.9 * torch.tanh(ref / 0.9)) < bound
+    half = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, half)
+    assert rel_err(half, ref) < 5e-3
+    # the generic kernel agrees (same operands, 32-bit FMA)
+    ops.use_tensor_cores = False
+    try:
+        slow = torch.empty(T, N, device=DEV)
+        ops.linear(x, w, slow)
+    finally:
+        ops.use_tensor_cores = True
+    assert rel_err(out, slow) < bound
+    # twice the same launch gives the same bits (split-K sums in split order)
+    again = torch.empty(T, N, device=DEV)
+    ops.linear(x, w, again)
+    assert torch.equal(out, again)
+    ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 128, 64), (8, 9216, 2304), (33, 200, 120), (64, 320, 96), (300, 1000, 256), (2048, 384, 128)])
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_linear_gated_tensor_cores(ops, T, I, K, act):
+    from cpu_ops import _act
+    g = torch.Generator().manual_seed(T + I)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_gated(x, w, out, act, None)
+    ops.raise_on_device_error()
+    gu = x.double() @ w.double().T
+    ref = _act(act, gu[:, :I]) * gu[:, I:]
+    assert rel_err(out, ref) < 6e-3
+
+
 @pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
 def test_linear_gated(ops, act):
     from cpu_ops import _act
