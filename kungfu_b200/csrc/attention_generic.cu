@@ -17,14 +17,15 @@ constexpr int WARPS = 4;
 template <typename TQ, typename TKV>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
-                         const int* __restrict__ positions, const int* __restrict__ row_req,
-                         const int* __restrict__ block_table, int table_stride, int page_size,
-                         int nh, int nkv, int d, float scale, float softcap, int window, int T) {
+                         const int* __restrict__ items, const int* __restrict__ positions,
+                         const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
+                         int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int T) {
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * WARPS + warp;
   if (item >= (long)T * nh) return;                       // whole warp leaves together; no block barrier below
-  const int t = (int)(item / nh), h = (int)(item - (long)t * nh);
+  const int it = (int)(item / nh), h = (int)(item - (long)it * nh);
+  const int t = items ? items[it] : it;                    // `items` names the rows this launch handles
   const int req = row_req[t];
   TQ* o = out + ((size_t)t * nh + h) * d;
   if (req < 0) {                                            // padding row
@@ -85,17 +86,18 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
   }
 }
 
+// items: rows of the step to process (null = rows 0..T-1); T is then the number of items.
 KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const void* pages, int kv_dtype,
-                                const int* positions, const int* row_req, const int* block_table, int table_stride,
+                                const int* items, const int* positions, const int* row_req, const int* block_table, int table_stride,
                                 int page_size, int nh, int nkv, int d, float scale, float softcap, int window,
                                 int T, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
   if (d < 1 || d > MAX_D || nkv < 1 || nh % nkv != 0 || page_size < 1) return KF_ERR_SIZE;
-  const long items = (long)T * nh;
-  const int blocks = (int)((items + WARPS - 1) / WARPS);
+  const long n_work = (long)T * nh;
+  const int blocks = (int)((n_work + WARPS - 1) / WARPS);
 #define KF_GO(TQ, TKV)                                                                                     \
   attention_generic_kernel<TQ, TKV><<<blocks, WARPS * 32, 0, stream>>>(                                    \
-      (const TQ*)q, (TQ*)out, (const TKV*)pages, positions, row_req, block_table, table_stride, page_size, \
+      (const TQ*)q, (TQ*)out, (const TKV*)pages, items, positions, row_req, block_table, table_stride, page_size, \
       nh, nkv, d, scale, softcap, window, T)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);

@@ -74,6 +74,9 @@ class StepContext:
         self.n_logits = 0
         self.decode_only = False
         self.max_rows_per_req = 0
+        self.dec_rows = self.pre_rows = None      # rows of single-row requests / of the others (device int32)
+        self.n_dec_rows = self.n_pre_rows = 0
+        self.max_kv_len = 0
         # device views, set by Runner._fill
         self.tokens = self.positions = self.row_req = self.logit_rows = None
         self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
@@ -141,6 +144,7 @@ class Runner:
         o = 0
         sec = {}
         for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", max(n_out, 1)),
+                        ("dec_rows", T), ("pre_rows", T),
                         ("req_row_start", B), ("req_n_rows", B), ("req_kv_len", B), ("req_state_slot", B)):
             sec[name] = (o, n)
             o += _align4(n)
@@ -162,6 +166,8 @@ class Runner:
         r = 0
         k = 0
         max_rows = 0
+        dec_rows, pre_rows = [], []
+        max_kv = 0
         for b, e in enumerate(entries):
             n = len(e.tokens)
             start = cache.length(e.request)
@@ -182,7 +188,14 @@ class Runner:
                 tab = cache.block_table(g, e.request)
                 row[:len(tab)] = tab
             max_rows = max(max_rows, n)
+            max_kv = max(max_kv, start + n)
+            if n == 1:
+                dec_rows.append(r)
+            else:
+                pre_rows.extend(range(r, r + n))
             r += n
+        view("dec_rows")[:len(dec_rows)] = dec_rows
+        view("pre_rows")[:len(pre_rows)] = pre_rows
         dev[:o].copy_(host[:o], non_blocking=True)
         if self.device.type == "cuda":
             if slot[1] is None:
@@ -198,6 +211,9 @@ class Runner:
         ctx.decode_only = max_rows == 1
         ctx.tokens, ctx.positions, ctx.row_req = dview("tokens"), dview("positions"), dview("row_req")
         ctx.logit_rows = dview("logit_rows")[:n_out] if n_out else dview("logit_rows")[:0]
+        ctx.dec_rows, ctx.n_dec_rows = dview("dec_rows"), len(dec_rows)
+        ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), len(pre_rows)
+        ctx.max_kv_len = max_kv
         ctx.req_row_start, ctx.req_n_rows = dview("req_row_start"), dview("req_n_rows")
         ctx.req_kv_len, ctx.req_state_slot = dview("req_kv_len"), dview("req_state_slot")
         ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]

@@ -165,6 +165,7 @@ def add(a, x) -> None:
 
 _scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor, "error": tensor, "retired": [tensors]}
 use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
+use_fast_attention = True    # likewise for the generic attention kernel
 
 
 def _dev_scratch(device) -> dict:
@@ -271,13 +272,37 @@ def rope_kv_append(qkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_
 @_dispatch("paged_attention")
 def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float,
                     window: int | None) -> None:
-    """Causal (optionally windowed, softcapped) attention of every row of the step over its request's pages."""
+    """Causal (optionally windowed, softcapped) attention of every row of the step over its request's pages.
+    bfloat16: rows of single-row requests run the split-KV decode kernel, the rest the prefill kernel, when the
+    head size has an instance of them; the 32-bit path and other head sizes run the generic kernel."""
     T = q.shape[0]
+    lib = library()
     table = ctx.block_tables[cache.group]
-    _check(library().kf_attention_generic(_p(q), _p(out), _dt(q), _p(cache.pages), _dt(cache.pages), _p(ctx.positions),
-                                          _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, n_heads,
-                                          n_kv_heads, head_dim, _f(scale), _f(softcap), int(window or 0), T, _stream()),
-           "paged_attention")
+    pages = cache.pages
+    common = (_p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, n_heads, n_kv_heads, head_dim,
+              _f(scale), _f(softcap), int(window or 0))
+    n_dec = getattr(ctx, "n_dec_rows", 0)
+    fast = (use_fast_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16)
+    if fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
+        ht, splits = ctypes.c_int(0), ctypes.c_int(0)
+        max_keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        lib.kf_attention_decode_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(ht), ctypes.byref(splits))
+        sc = _dev_scratch(q.device)
+        n_counters = n_dec * n_kv_heads * -(-(n_heads // n_kv_heads) // ht.value)
+        if n_counters <= sc["counters"].numel():
+            partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 2)) if splits.value > 1 else None
+            items = None if n_dec == T else ctx.dec_rows
+            _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common[:8], *common[8:], ht.value,
+                                           splits.value, _p(partial), _p(sc["counters"]), _stream()), "attention (decode)")
+            if n_dec == T:
+                return
+            rest, n_rest = ctx.pre_rows, ctx.n_pre_rows
+        else:
+            rest, n_rest = None, T
+    else:
+        rest, n_rest = None, T
+    _check(lib.kf_attention_generic(_p(q), _p(out), _dt(q), _p(pages), _dt(pages), _p(rest), *common, n_rest, _stream()),
+           "attention (generic)")
 
 
 @_dispatch("argmax")

@@ -174,8 +174,13 @@ class _View:
 
 
 class _Ctx:
-    def __init__(self, positions, row_req, table):
+    def __init__(self, positions, row_req, table, dec_rows=None, pre_rows=None):
         self.positions, self.row_req, self.block_tables = positions, row_req, [table]
+        self.n_dec_rows = 0 if dec_rows is None else len(dec_rows)
+        self.n_pre_rows = 0 if pre_rows is None else len(pre_rows)
+        self.dec_rows = None if dec_rows is None else torch.tensor(dec_rows, dtype=torch.int32, device=DEV)
+        self.pre_rows = None if pre_rows is None else torch.tensor(pre_rows or [0], dtype=torch.int32, device=DEV)
+        self.max_kv_len = int(positions.max()) + 1
 
 
 def _paged_setup(dtype, nh, nkv, d, P, lens, seed, scramble=True):
@@ -236,6 +241,30 @@ def test_paged_attention(ops, dtype, nh, nkv, d, P, window, cap):
     assert rel_err(out.view(len(rows), nh, d), ref) < (2e-5 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 1000, 50.0),
+                                                   (5, 5, 64, 32, None, 30.0), (16, 2, 128, 64, 4096, 50.0), (8, 1, 128, 16, None, 0.0)])
+@pytest.mark.parametrize("mixed", [False, True])
+def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed):
+    """The split-KV decode kernel: single rows of requests of very different lengths (one of them long enough for
+    several splits), alone and beside rows of a multi-row request that the other kernel handles."""
+    lens = [1, 37, 3000, 700, 64, 65]
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=11)
+    rows = [(r, n - 1) for r, n in enumerate(lens)]          # the last position of every request
+    dec, pre = list(range(len(rows))), []
+    if mixed:                                               # request 3 brings 5 rows instead of 1
+        rows = rows[:3] + [(3, p) for p in range(695, 700)] + rows[4:]
+        dec, pre = [0, 1, 2, 8, 9], [3, 4, 5, 6, 7]
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn(len(rows), nh, d, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
+    out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
+    ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
+    assert rel_err(out.view(len(rows), nh, d), ref) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_a_far_key(ops, dtype):
     """One key among hundreds carries the answer: its score is made to stand out, on a page of its own."""
@@ -252,7 +281,8 @@ def test_attention_finds_a_far_key(ops, dtype):
             pg = int(table[0, i])
             m = min(P, n - i * P)
             pages[pg, 0, :, :m] = k[i * P:i * P + m].transpose(0, 1).to(dtype)
-        ctx = _Ctx(torch.tensor([n - 1], dtype=torch.int32, device=DEV), torch.tensor([0], dtype=torch.int32, device=DEV), table.to(DEV))
+        ctx = _Ctx(torch.tensor([n - 1], dtype=torch.int32, device=DEV), torch.tensor([0], dtype=torch.int32, device=DEV), table.to(DEV),
+                   dec_rows=[0], pre_rows=[])
         out = torch.empty(1, nh * d, dtype=dtype, device=DEV)
         ops.paged_attention(q.view(1, nh * d).to(dtype).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, 1.0, 0.0, None)
         want = torch.stack([v[far, h // 2] for h in range(nh)]).to(dtype).float()
