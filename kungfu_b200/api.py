@@ -69,7 +69,8 @@ def random_model(config, seed: int = 0, *, dtype="bfloat16", device="cuda:0", on
 
 
 def make_runner(cfg, model, *, dtype, device, page_size: int = DEFAULT_PAGE_SIZE, max_tokens: int | None = None,
-                n_pages: int | None = None, max_requests: int = 64, max_context: int | None = None) -> Runner:
+                n_pages: int | None = None, max_requests: int = 64, max_context: int | None = None,
+                cuda_graphs: bool = True) -> Runner:
     """A step runner with a cache pool for `max_tokens` tokens (rounded up to whole pages) per cache group."""
     dtype = parse_dtype(dtype)
     if max_context is None:
@@ -80,7 +81,9 @@ def make_runner(cfg, model, *, dtype, device, page_size: int = DEFAULT_PAGE_SIZE
         n_pages = -(-int(max_tokens) // page_size)
     cache = CacheManager(model.state_needs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
                          max_context=max_context, dtype=dtype, device=device)
-    return Runner(model, cache, act_dtype=dtype, device=device)
+    runner = Runner(model, cache, act_dtype=dtype, device=device)
+    runner.cuda_graphs = bool(cuda_graphs) and torch.device(device).type == "cuda"
+    return runner
 
 
 class Engine:

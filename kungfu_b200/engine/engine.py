@@ -55,8 +55,8 @@ class Engine:
             page = page_size or api.DEFAULT_PAGE_SIZE
             pool_tokens = max_tokens_in_cache or parallel * (-(-n_ctx // page) * page)
             self.runner = api.make_runner(self.cfg, model, dtype=dtype, device=self.device, page_size=page,
-                                          max_tokens=pool_tokens, max_requests=parallel, max_context=n_ctx)
-            self.runner.cuda_graphs = cuda_graphs
+                                          max_tokens=pool_tokens, max_requests=parallel, max_context=n_ctx,
+                                          cuda_graphs=cuda_graphs)
             if events:
                 emit_event("ready", model=self.cfg.architecture, dtype=str(api.parse_dtype(dtype)).split(".")[-1],
                            weight_bytes=model.weight_bytes(), cache_bytes_per_token=self.runner.cache.bytes_per_token(),

@@ -107,6 +107,7 @@ class Runner:
         self.steps_run = 0
         self.last_meta_ints = 0
         self.cuda_graphs = False
+        self._graphs: dict = {}
         self.launch_count_hint = 0
 
     # ---- metadata -----------------------------------------------------------------------------------
@@ -127,18 +128,25 @@ class Runner:
             slot[1].synchronize()
         return slot, self._meta_dev
 
-    def _fill(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _fill(self, entries: Sequence[StepEntry], bucket: int | None = None) -> StepContext:
+        """Build the step's integer block.  With `bucket` (decode-only steps replayed from a CUDA graph) the
+        layout is the one of `bucket` single-row requests with full-width block tables, whatever the step holds:
+        rows beyond the real ones are padding (request index -1) that every kernel skips."""
         cache = self.cache
         ctx = StepContext(self)
-        B = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        n_out = sum(len(e.want) for e in entries)
+        n_real = len(entries)
+        B = len(entries) if bucket is None else bucket
+        T = sum(len(e.tokens) for e in entries) if bucket is None else bucket
+        n_out = sum(len(e.want) for e in entries) if bucket is None else bucket
         G = len(cache.groups)
         # table width: the most pages any request of this step addresses
         width = 1
-        for e in entries:
-            n_after = cache.length(e.request) + len(e.tokens)
-            width = max(width, -(-n_after // cache.page_size))
+        if bucket is None:
+            for e in entries:
+                n_after = cache.length(e.request) + len(e.tokens)
+                width = max(width, -(-n_after // cache.page_size))
+        else:
+            width = cache.max_pages_per_request
         width = _align4(width)
         # layout (in ints); every section starts on a 16-byte boundary
         o = 0
@@ -163,6 +171,12 @@ class Runner:
         tokens, positions, row_req = view("tokens"), view("positions"), view("row_req")
         logit_rows = view("logit_rows")
         logit_rows[:] = 0
+        if bucket is not None:
+            h[:o] = 0
+            row_req[n_real:] = -1
+            for g in range(G):
+                a, n = sec[f"table{g}"]
+                h[a:a + n] = -1
         r = 0
         k = 0
         max_rows = 0
@@ -194,6 +208,10 @@ class Runner:
             else:
                 pre_rows.extend(range(r, r + n))
             r += n
+        if bucket is not None:
+            dec_rows = list(range(bucket))
+            logit_rows[:] = np.arange(bucket, dtype=np.int32)
+            max_kv = cache.max_context                  # a graph's split plan must not depend on the step
         view("dec_rows")[:len(dec_rows)] = dec_rows
         view("pre_rows")[:len(pre_rows)] = pre_rows
         dev[:o].copy_(host[:o], non_blocking=True)
@@ -258,9 +276,55 @@ class Runner:
             for e in reserved:
                 self.cache.cancel_reservation(e.request)
             raise
-        ctx = self._fill(entries)
-        logits = self.model.forward(ctx)
+        bucket = self._graph_bucket(entries)
+        if bucket is None:
+            ctx = self._fill(entries)
+            logits = self.model.forward(ctx)
+        else:
+            logits = self._step_graphed(entries, bucket)
         for e in entries:
             self.cache.commit(e.request, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
+    def _graph_bucket(self, entries) -> int | None:
+        """The padded batch size whose graph runs this step, or None if the step is not a pure decode step."""
+        if not self.cuda_graphs or self.device.type != "cuda":
+            return None
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        b = 1
+        while b < len(entries):
+            b *= 2
+        return b if b <= max(self.cache.max_requests, 1) * 2 else None
+
+    def _step_graphed(self, entries, bucket: int):
+        """First time a bucket is seen the step runs eagerly (that also sizes every buffer); the second time the
+        launches are captured into a graph; from then on the step is one copy of integers and one replay."""
+        from .. import ops
+        ctx = self._fill(entries, bucket)
+        n = len(entries)
+        state = self._graphs.get(bucket)
+        if state is not None and state["generation"] != self.buffers.generation:
+            state = None                                   # a buffer moved: the old graph points at freed memory
+            self._graphs.pop(bucket)
+        if state is None:
+            self._graphs[bucket] = {"generation": None, "graph": None, "seen": 1}
+            logits = self.model.forward(ctx)
+            self._graphs[bucket]["generation"] = self.buffers.generation
+            return logits[:n]
+        if state["graph"] is None:
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.current_stream().synchronize()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            if self.buffers.generation != state["generation"]:
+                self._graphs.pop(bucket)                   # capture itself grew a buffer: run this step eagerly
+                return self.model.forward(ctx)[:n]
+            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
+            ops.add_launches(-state["kernels"])            # capture launched nothing
+        state["graph"].replay()
+        ops.add_launches(state["kernels"])
+        return state["logits"][:n]
