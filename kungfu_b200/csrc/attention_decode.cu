@@ -13,7 +13,7 @@
 namespace {
 
 constexpr int DEC_WARPS = 8;
-constexpr int UNROLL = 2;
+constexpr int UNROLL = 4;
 
 template <int HT>
 struct State {
@@ -28,6 +28,21 @@ __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
     f[2 * i] = v.x;
     f[2 * i + 1] = v.y;
   }
+}
+
+// 16-byte load that does not linger in L1: every key and value is read once per step
+__device__ __forceinline__ uint4 ld_stream(const __nv_bfloat16* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+// 32-bit exponential and softcap through the hardware's base-2 exponential and reciprocal (relative error ~1e-6,
+// far below the rounding of the bfloat16 operands); the 32-bit path of the engine uses expf/tanhf instead.
+__device__ __forceinline__ float exp_fast(float x) { return exp2f(x * 1.4426950408889634f); }
+__device__ __forceinline__ float softcap_fast(float x, float cap) {
+  if (cap <= 0.f) return x;
+  const float e = exp2f(x * (2.f * 1.4426950408889634f / cap));       // exp(2x/cap)
+  return cap * (1.f - __fdividef(2.f, e + 1.f));                       // cap * tanh(x/cap)
 }
 
 // merge (m2, l2, a2) into (m, l, a)
@@ -114,35 +129,58 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       if (valid[u]) {
         const int page = tab[j / page_size];
         const __nv_bfloat16* kp = pages + ((size_t)page * 2 * nkv + kvh) * head_stride + (size_t)(j % page_size) * D + chunk * 8;
-        kr[u] = *reinterpret_cast<const uint4*>(kp);
-        vr[u] = *reinterpret_cast<const uint4*>(kp + v_off);
+        kr[u] = ld_stream(kp);
+        vr[u] = ld_stream(kp + v_off);
       } else {
         kr[u] = make_uint4(0, 0, 0, 0);
         vr[u] = make_uint4(0, 0, 0, 0);
       }
     }
+    // scores of the UNROLL keys of this lane group, all heads (independent chains)
+    float s[UNROLL][HT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      float kf[8], vf[8];
+      float kf[8];
       unpack8(kr[u], kf);
-      unpack8(vr[u], vf);
 #pragma unroll
       for (int h = 0; h < HT; ++h) {
-        float s = 0.f;
+        float d = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s = fmaf(qf[h][i], kf[i], s);
+        for (int i = 0; i < 8; ++i) d = fmaf(qf[h][i], kf[i], d);
+        s[u][h] = d;
+      }
+    }
 #pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (valid[u]) {                                       // uniform within the lane group
-          s = kf_softcap(s, softcap);
-          const float mn = fmaxf(st.m[h], s);
-          const float c = (st.m[h] == -INFINITY) ? 0.f : expf(st.m[h] - mn);
-          const float p = expf(s - mn);
-          st.l[h] = st.l[h] * c + p;
+    for (int o = LPK / 2; o > 0; o >>= 1)
 #pragma unroll
-          for (int i = 0; i < 8; ++i) st.acc[h][i] = st.acc[h][i] * c + p * vf[i];
-          st.m[h] = mn;
-        }
+      for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+        for (int h = 0; h < HT; ++h) s[u][h] += __shfl_xor_sync(0xffffffffu, s[u][h], o);
+    // one online-softmax update per head for the whole batch of keys
+#pragma unroll
+    for (int h = 0; h < HT; ++h) {
+      float mn = st.m[h];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        s[u][h] = valid[u] ? softcap_fast(s[u][h], softcap) : -INFINITY;
+        mn = fmaxf(mn, s[u][h]);
+      }
+      if (mn == -INFINITY) continue;                          // nothing valid yet for this lane group
+      const float c = exp_fast(st.m[h] - mn);                 // exp(-inf) = 0 on the first batch
+      float lsum = 0.f;
+      float p[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) { p[u] = exp_fast(s[u][h] - mn); lsum += p[u]; }
+      st.l[h] = st.l[h] * c + lsum;
+      st.m[h] = mn;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) st.acc[h][i] *= c;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        float vf[8];
+        unpack8(vr[u], vf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) st.acc[h][i] = fmaf(p[u], vf[i], st.acc[h][i]);
       }
     }
   }

@@ -13,17 +13,8 @@ __device__ __forceinline__ unsigned kf_orderable(float v) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);      // larger float <=> larger unsigned
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  const float* row = logits + (size_t)blockIdx.x * V;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
-  if (bi == 0x7fffffff) bi = V > 0 ? (threadIdx.x < V ? threadIdx.x : 0) : 0;   // all -inf or NaN in this thread's share
+// Block-wide (value, index) maximum with the lower index winning ties; result valid in thread 0.
+__device__ __forceinline__ void block_argmax(float& best, int& bi, float* sv, int* si) {
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
@@ -40,15 +31,63 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (lane == 0) out[blockIdx.x] = bi;
   }
 }
 
-KF_API int kf_argmax(const float* logits, int* out, int rows, int V, cudaStream_t stream) {
+// Stage 1: block (chunk, row) scans its slice of the row.  With one chunk it writes the answer itself.
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int chunks,
+                              float* __restrict__ part_val, int* __restrict__ part_idx) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const float* r = logits + (size_t)row * V;
+  const int per = (V + chunks - 1) / chunks;
+  const int begin = chunk * per, end = min(V, begin + per);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  block_argmax(best, bi, sv, si);
+  if (threadIdx.x == 0) {
+    if (chunks == 1) out[row] = bi == 0x7fffffff ? 0 : bi;
+    else { part_val[row * chunks + chunk] = best; part_idx[row * chunks + chunk] = bi; }
+  }
+}
+
+// Stage 2: one warp per row merges the chunks in index order.
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int* __restrict__ out, int chunks) {
+  const int row = blockIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    const float v = part_val[row * chunks + c];
+    const int i = part_idx[row * chunks + c];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// scratch: rows * 64 floats followed by rows * 64 ints (may be null when V < 16384: one chunk is used).
+KF_API int kf_argmax(const float* logits, int* out, int rows, int V, float* scratch, cudaStream_t stream) {
   if (rows <= 0) return KF_OK;
   if (V <= 0) return KF_ERR_SIZE;
-  argmax_kernel<<<rows, 1024, 0, stream>>>(logits, out, V);
+  int chunks = (scratch && V >= 16384) ? 64 : 1;
+  float* pv = scratch;
+  int* pi = scratch ? (int*)(scratch + (size_t)rows * 64) : nullptr;
+  argmax_kernel<<<dim3(chunks, rows), chunks == 1 ? 1024 : 256, 0, stream>>>(logits, out, V, chunks, pv, pi);
   KF_CHECK_LAUNCH();
+  if (chunks > 1) {
+    argmax_merge_kernel<<<rows, 32, 0, stream>>>(pv, pi, out, chunks);
+    KF_CHECK_LAUNCH();
+  }
   return KF_OK;
 }
 

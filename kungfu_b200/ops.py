@@ -309,7 +309,12 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
 def argmax(logits, out) -> None:
     """out[r] = index of the first maximum of logits[r, :] (int32)."""
     rows, V = logits.shape
-    _check(library().kf_argmax(_p(logits), _p(out), rows, V, _stream()), "argmax")
+    sc = _dev_scratch(logits.device)
+    if "argmax" not in sc or sc["argmax"].numel() < rows * 128:
+        if "argmax" in sc:
+            sc["retired"].append(sc["argmax"])
+        sc["argmax"] = torch.empty(max(rows, 64) * 128, dtype=torch.float32, device=logits.device)
+    _check(library().kf_argmax(_p(logits), _p(out), rows, V, _p(sc["argmax"]), _stream()), "argmax")
 
 
 @_dispatch("topk_lse")
