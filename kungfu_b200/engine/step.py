@@ -77,6 +77,8 @@ class StepContext:
         self.dec_rows = self.pre_rows = None      # rows of single-row requests / of the others (device int32)
         self.n_dec_rows = self.n_pre_rows = 0
         self.max_kv_len = 0
+        self.tile_row0 = self.tile_nrows = None   # prompt-portion tiles: first row and row count (device int32)
+        self.n_tiles = 0
         # device views, set by Runner._fill
         self.tokens = self.positions = self.row_req = self.logit_rows = None
         self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
@@ -152,7 +154,7 @@ class Runner:
         o = 0
         sec = {}
         for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", max(n_out, 1)),
-                        ("dec_rows", T), ("pre_rows", T),
+                        ("dec_rows", T), ("pre_rows", T), ("tile_row0", T // 64 + B + 1), ("tile_nrows", T // 64 + B + 1),
                         ("req_row_start", B), ("req_n_rows", B), ("req_kv_len", B), ("req_state_slot", B)):
             sec[name] = (o, n)
             o += _align4(n)
@@ -180,7 +182,7 @@ class Runner:
         r = 0
         k = 0
         max_rows = 0
-        dec_rows, pre_rows = [], []
+        dec_rows, pre_rows, tiles = [], [], []
         max_kv = 0
         for b, e in enumerate(entries):
             n = len(e.tokens)
@@ -207,6 +209,8 @@ class Runner:
                 dec_rows.append(r)
             else:
                 pre_rows.extend(range(r, r + n))
+                for a0 in range(0, n, 64):               # tiles of up to 64 consecutive rows of one request
+                    tiles.append((r + a0, min(64, n - a0)))
             r += n
         if bucket is not None:
             dec_rows = list(range(bucket))
@@ -214,6 +218,9 @@ class Runner:
             max_kv = cache.max_context                  # a graph's split plan must not depend on the step
         view("dec_rows")[:len(dec_rows)] = dec_rows
         view("pre_rows")[:len(pre_rows)] = pre_rows
+        if tiles:
+            view("tile_row0")[:len(tiles)] = [a for a, _ in tiles]
+            view("tile_nrows")[:len(tiles)] = [b for _, b in tiles]
         dev[:o].copy_(host[:o], non_blocking=True)
         if self.device.type == "cuda":
             if slot[1] is None:
@@ -232,6 +239,7 @@ class Runner:
         ctx.dec_rows, ctx.n_dec_rows = dview("dec_rows"), len(dec_rows)
         ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), len(pre_rows)
         ctx.max_kv_len = max_kv
+        ctx.tile_row0, ctx.tile_nrows, ctx.n_tiles = dview("tile_row0"), dview("tile_nrows"), len(tiles)
         ctx.req_row_start, ctx.req_n_rows = dview("req_row_start"), dview("req_n_rows")
         ctx.req_kv_len, ctx.req_state_slot = dview("req_kv_len"), dview("req_state_slot")
         ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]

@@ -289,7 +289,9 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         lib.kf_attention_decode_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(ht), ctypes.byref(splits))
         sc = _dev_scratch(q.device)
         n_counters = n_dec * n_kv_heads * -(-(n_heads // n_kv_heads) // ht.value)
-        if n_counters <= sc["counters"].numel():
+        if n_counters > sc["counters"].numel():
+            rest, n_rest = None, T
+        else:
             partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 2)) if splits.value > 1 else None
             items = None if n_dec == T else ctx.dec_rows
             _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common[:8], *common[8:], ht.value,
@@ -297,10 +299,15 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
             if n_dec == T:
                 return
             rest, n_rest = ctx.pre_rows, ctx.n_pre_rows
-        else:
-            rest, n_rest = None, T
+    elif fast and n_dec == 0 and getattr(ctx, "n_pre_rows", 0) == T:
+        rest, n_rest = ctx.pre_rows, T
     else:
         rest, n_rest = None, T
+    if (fast and rest is not None and n_rest == ctx.n_pre_rows and getattr(ctx, "n_tiles", 0) > 0
+            and lib.kf_attention_prefill_supported(head_dim)):
+        _check(lib.kf_attention_prefill(_p(q), _p(out), _p(pages), _p(ctx.tile_row0), _p(ctx.tile_nrows), ctx.n_tiles,
+                                        *common, _stream()), "attention (prefill)")
+        return
     _check(lib.kf_attention_generic(_p(q), _p(out), _dt(q), _p(pages), _dt(pages), _p(rest), *common, n_rest, _stream()),
            "attention (generic)")
 

@@ -181,6 +181,18 @@ class _Ctx:
         self.dec_rows = None if dec_rows is None else torch.tensor(dec_rows, dtype=torch.int32, device=DEV)
         self.pre_rows = None if pre_rows is None else torch.tensor(pre_rows or [0], dtype=torch.int32, device=DEV)
         self.max_kv_len = int(positions.max()) + 1
+        # tiles of up to 64 consecutive rows of one request, as the step function builds them
+        tiles = []
+        if pre_rows:
+            req, pos = row_req.tolist(), positions.tolist()
+            start = pre_rows[0]
+            for a, b in zip(pre_rows, pre_rows[1:] + [None]):
+                if b is None or b != a + 1 or req[b] != req[a] or a + 1 - start == 64:
+                    tiles.append((start, a + 1 - start))
+                    start = b
+        self.n_tiles = len(tiles)
+        self.tile_row0 = torch.tensor([t[0] for t in tiles] or [0], dtype=torch.int32, device=DEV)
+        self.tile_nrows = torch.tensor([t[1] for t in tiles] or [0], dtype=torch.int32, device=DEV)
 
 
 def _paged_setup(dtype, nh, nkv, d, P, lens, seed, scramble=True):
@@ -263,6 +275,32 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed):
     ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
     ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
     assert rel_err(out.view(len(rows), nh, d), ref) < 1e-2
+
+
+@pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 100, 50.0),
+                                                   (5, 5, 64, 32, None, 30.0), (16, 2, 128, 64, 70, 50.0), (8, 1, 128, 16, None, 0.0),
+                                                   (2, 1, 256, 8, None, 0.0)])
+def test_prefill_attention(ops, nh, nkv, d, P, window, cap):
+    """The tensor-core prompt kernel: a whole prompt from position 0 (several tiles, the last one ragged), a portion
+    that continues a long request, a two-row portion, beside single rows that the decode kernel takes."""
+    lens = [150, 700, 65, 9, 300]
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=13)
+    rows = ([(0, p) for p in range(150)] + [(1, p) for p in range(570, 700)] + [(2, 64)] + [(3, p) for p in range(7, 9)]
+            + [(4, 299)])
+    pre = list(range(0, 280)) + [281, 282]
+    dec = [280, 283]
+    g = torch.Generator().manual_seed(14)
+    q = torch.randn(len(rows), nh, d, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
+    assert ctx.n_tiles == 3 + 3 + 1
+    out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
+    ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
+    got = out.view(len(rows), nh, d)
+    assert bool(torch.isfinite(got.float()).all())
+    assert rel_err(got, ref) < 1.5e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
