@@ -316,3 +316,65 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
 #undef KF_ARGS
   return KF_ERR_SIZE;
 }
+
+// ---- decode attention for callers that cannot allocate ---------------------------------------------------------
+// See attention_decode_static.h.  The split partials and the arrival counters live in the two file-scope device
+// arrays below instead of caller-provided buffers.
+#include "attention_decode_static.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_partial[KF_DECODE_STATIC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) int g_static_counters[KF_DECODE_STATIC_MAX_COUNTERS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+float* g_static_partial_ptr[MAX_DEVICES] = {};
+int* g_static_counters_ptr[MAX_DEVICES] = {};
+}  // namespace
+
+KF_API int kf_attention_decode_static(const void* q, void* out, const void* pages, int n_rows, const int* positions,
+                                      const int* row_req, const int* table, int table_stride, int page_size, int nh,
+                                      int nkv, int d, float scale, float softcap, int window, int max_keys,
+                                      cudaStream_t stream) {
+  if (n_rows <= 0) return KF_OK;
+  if (nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_attention_decode_supported(d)) return KF_ERR_SIZE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return KF_ERR_SETUP;
+  float* partial = nullptr;
+  int* counters = nullptr;
+  {
+    // One-time set-up per device, with that device current: in host code the arrays' names are host-side
+    // stand-ins, not device addresses, so the addresses the kernel gets are asked for here.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_partial_ptr[dev]) {
+      float* p = nullptr;
+      int* c = nullptr;
+      cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_partial);
+      if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&c, g_static_counters);
+      if (e != cudaSuccess || !p || !c) {
+        kf_record_cuda_error(e);
+        return KF_ERR_SETUP;
+      }
+      g_static_partial_ptr[dev] = p;
+      g_static_counters_ptr[dev] = c;
+    }
+    partial = g_static_partial_ptr[dev];
+    counters = g_static_counters_ptr[dev];
+  }
+  int ht = 1, splits = 1;
+  kf_attention_decode_plan(n_rows, nh, nkv, d, max_keys, &ht, &splits);
+  const long n_counters = (long)n_rows * nkv * kf_ceil_div(nh / nkv, ht);
+  const long n_partial = (long)n_rows * nh * splits * (d + 2);
+  if (n_counters > KF_DECODE_STATIC_MAX_COUNTERS || n_partial > KF_DECODE_STATIC_MAX_PARTIAL_FLOATS) {
+    kf_record_message("kf_attention_decode_static: rows * heads * splits * (head_dim + 2) exceeds the built-in scratch");
+    return KF_ERR_SIZE;
+  }
+  // The arrays keep what the last call left; the counters must start at zero.
+  if (cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream) != cudaSuccess) {
+    kf_record_cuda_error(cudaGetLastError());
+    return KF_ERR_LAUNCH;
+  }
+  return kf_attention_decode(q, out, pages, nullptr, n_rows, positions, row_req, table, table_stride, page_size, nh, nkv,
+                             d, scale, softcap, window, ht, splits, partial, counters, stream);
+}

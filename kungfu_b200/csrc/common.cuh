@@ -20,6 +20,7 @@ enum KfStatus {
 };
 
 extern "C" int kf_record_cuda_error(cudaError_t e);
+extern "C" void kf_record_message(const char* msg);
 
 #define KF_CHECK_LAUNCH()                                   \
   do {                                                      \

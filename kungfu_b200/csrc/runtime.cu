@@ -10,6 +10,8 @@ extern "C" int kf_record_cuda_error(cudaError_t e) {
   return (int)e;
 }
 
+extern "C" void kf_record_message(const char* msg) { snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
+
 KF_API const char* kf_last_cuda_error() { return g_last_error; }
 
 KF_API int kf_abi_version() { return 1; }
