@@ -110,6 +110,7 @@ class Runner:
         self.last_meta_ints = 0
         self.cuda_graphs = False
         self._graphs: dict = {}
+        self._graph_safe = model.all_graph_safe() if hasattr(model, "all_graph_safe") else False
         self.launch_count_hint = 0
 
     # ---- metadata -----------------------------------------------------------------------------------
@@ -298,7 +299,7 @@ class Runner:
     # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
     def _graph_bucket(self, entries) -> int | None:
         """The padded batch size whose graph runs this step, or None if the step is not a pure decode step."""
-        if not self.cuda_graphs or self.device.type != "cuda":
+        if not self.cuda_graphs or self.device.type != "cuda" or not self._graph_safe:
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None

@@ -46,6 +46,13 @@ StateNeed = PagedKV | FixedState
 class Part:
     """Common base: parts report their weight tensors for accounting."""
 
+    # False for a part whose forward does host-side work that depends on the step (loops over requests, reads of
+    # ctx.host): steps of a model holding such a part are never captured into CUDA graphs.
+    graph_safe = True
+
+    def all_graph_safe(self) -> bool:
+        return self.graph_safe and all(c.all_graph_safe() for c in self.children())
+
     def weights(self) -> list[torch.Tensor]:
         return [v for v in vars(self).values() if isinstance(v, torch.Tensor)]
 
