@@ -286,7 +286,8 @@ KF_API int kf_attention_decode_plan(int n_items, int nh, int nkv, int d, int max
   const int G = nh / nkv;
   const int ht = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
   const long blocks = (long)n_items * nkv * kf_ceil_div(G, ht);
-  int splits = (int)((2 * 148 + blocks - 1) / blocks);
+  // two blocks of this kernel are resident per SM: fill one wave of 2 x 148 blocks, never a second partial wave
+  int splits = (int)((2 * 148) / blocks);
   const int by_len = (max_keys + 255) / 256;                  // at least 256 keys per split
   if (splits > by_len) splits = by_len;
   if (splits > 32) splits = 32;

@@ -386,8 +386,8 @@ KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_ou
   const int nkb = (K + BK - 1) / BK;
   const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
   int splits = 1;
-  if (tiles < 120) {                                   // fewer tiles than SMs: cut K so that every SM streams weights
-    splits = (int)((148 + tiles - 1) / tiles);
+  if (tiles <= 74) {                                   // fewer tiles than half the SMs: cut K so that every SM streams
+    splits = (int)(148 / tiles);                       // weights, in ONE wave (one CTA per SM fits)
     if (splits > 16) splits = 16;
     if (splits > nkb) splits = nkb;
     const int kb_per = (nkb + splits - 1) / splits;
