@@ -63,6 +63,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
                    int nh, int nkv, float scale, float softcap, int window, int n_splits,
                    float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   constexpr int LPK = D / 8;                 // lanes per key
   constexpr int KPW = 32 / LPK;              // keys per warp and iteration
   constexpr int PSTRIDE = D + 2;             // partial record: acc[D], m, l
@@ -259,7 +261,7 @@ int launch_decode(const void* q, const void* pages, const int* items, int n_item
                   int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
   const int G = nh / nkv;
   dim3 grid(n_items * nkv, n_splits, kf_ceil_div(G, HT));
-  attn_decode_kernel<D, HT><<<grid, DEC_WARPS * 32, 0, stream>>>(
+  kf_launch(attn_decode_kernel<D, HT>, dim3(grid), dim3(DEC_WARPS * 32), 0, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, items, n_items, positions, row_req, table, table_stride,
       page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();

@@ -20,6 +20,8 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
                          const int* __restrict__ items, const int* __restrict__ positions,
                          const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
                          int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int T) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * WARPS + warp;
@@ -96,7 +98,7 @@ KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const voi
   const long n_work = (long)T * nh;
   const int blocks = (int)((n_work + WARPS - 1) / WARPS);
 #define KF_GO(TQ, TKV)                                                                                     \
-  attention_generic_kernel<TQ, TKV><<<blocks, WARPS * 32, 0, stream>>>(                                    \
+  kf_launch(attention_generic_kernel<TQ, TKV>, dim3(blocks), dim3(WARPS * 32), 0, stream,                                     \
       (const TQ*)q, (TQ*)out, (const TKV*)pages, items, positions, row_req, block_table, table_stride, page_size, \
       nh, nkv, d, scale, softcap, window, T)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);

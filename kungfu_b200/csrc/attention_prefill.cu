@@ -63,6 +63,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ positions, const int* __restrict__ row_req,
                     const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
                     float scale, float softcap, int window, __nv_bfloat16* __restrict__ out) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int NT_S = BNK / 8;                   // n-tiles of S per warp
   constexpr int NT_O = D / 8;                     // n-tiles of O per warp
@@ -246,7 +248,7 @@ int launch_prefill(const void* q, void* out, const void* pages, const int* tile_
     }
     configured = true;
   }
-  attn_prefill_kernel<D, BNK><<<dim3(n_tiles, nh), PF_WARPS * 32, smem, stream>>>(
+  kf_launch(attn_prefill_kernel<D, BNK>, dim3(n_tiles, nh), dim3(PF_WARPS * 32), smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, tile_row0, tile_nrows, positions, row_req, table, table_stride,
       page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();

@@ -28,6 +28,33 @@ extern "C" void kf_record_message(const char* msg);
     if (_e != cudaSuccess) { kf_record_cuda_error(_e); return KF_ERR_LAUNCH; } \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of this library may be launched before its predecessor in the
+// stream has finished (kf_launch below sets the attribute); a kernel therefore calls kf_pdl_wait() before it
+// touches global memory that the predecessor may write or read, and kf_pdl_trigger() as early as it can so that the
+// next kernel's blocks can take free resources and run their own prologue (the tensor-core product prefetches
+// weights there).  Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void kf_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void kf_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern "C" int kf_pdl_enabled();
+
+// Launch with the programmatic-dependent-launch attribute when it is switched on (kf_set_pdl).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kf_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float kf_load(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float kf_load(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ void kf_store(float* p, size_t i, float v) { p[i] = v; }

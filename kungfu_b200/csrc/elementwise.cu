@@ -6,6 +6,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float scale,
                              float* __restrict__ out, int H, int V, int* __restrict__ bad) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool ok = tok >= 0 && tok < V;
@@ -20,9 +22,9 @@ KF_API int kf_embed(const int* tokens, const void* table, int table_dtype, float
   if (T <= 0) return KF_OK;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == KF_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, scale, out, H, V, bad_flag);
+    kf_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, scale, out, H, V, bad_flag);
   else if (table_dtype == KF_BF16)
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, scale, out, H, V, bad_flag);
+    kf_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, scale, out, H, V, bad_flag);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();
@@ -33,6 +35,8 @@ KF_API int kf_embed(const int* tokens, const void* table, int table_dtype, float
 // Reference: crates/kf-backend-cuda/src/kernels/rope.cu:4-14.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   const int t = idx / half, i = idx - t * half;
@@ -47,7 +51,7 @@ KF_API int kf_rope_table(const int* positions, const float* inv_freq, float* cos
                          int T, int half, cudaStream_t stream) {
   if (T <= 0 || half <= 0) return KF_OK;
   const int n = T * half;
-  rope_table_kernel<<<kf_ceil_div(n, 256), 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, T, half);
+  kf_launch(rope_table_kernel, dim3(kf_ceil_div(n, 256)), dim3(256), 0, stream, positions, inv_freq, cos_out, sin_out, T, half);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -56,6 +60,8 @@ KF_API int kf_rope_table(const int* positions, const float* inv_freq, float* cos
 // Reference: crates/kf-backend-cuda/src/kernels/elementwise.cu:42-44.
 template <typename TI, typename TO>
 __global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int I, int act) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   const size_t n = (size_t)T * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I, j = idx - t * I;
@@ -69,11 +75,11 @@ KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, 
   const size_t n = (size_t)T * I;
   const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
   if (in_dtype == KF_F32 && out_dtype == KF_F32)
-    gated_act_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, T, I, act);
+    kf_launch(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, T, I, act);
   else if (in_dtype == KF_F32 && out_dtype == KF_BF16)
-    gated_act_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gu, (__nv_bfloat16*)out, T, I, act);
+    kf_launch(gated_act_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (__nv_bfloat16*)out, T, I, act);
   else if (in_dtype == KF_BF16 && out_dtype == KF_BF16)
-    gated_act_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, act);
+    kf_launch(gated_act_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, act);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();
@@ -81,13 +87,15 @@ KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, 
 }
 
 __global__ void add_kernel(const float* __restrict__ a, float* __restrict__ x, size_t n) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] += a[i];
 }
 
 KF_API int kf_add(const float* a, float* x, long n, cudaStream_t stream) {
   if (n <= 0) return KF_OK;
   const long b = (n + 255) / 256;
-  add_kernel<<<(int)(b > 148 * 16 ? 148 * 16 : b), 256, 0, stream>>>(a, x, (size_t)n);
+  kf_launch(add_kernel, dim3((int)(b > 148 * 16 ? 148 * 16 : b)), dim3(256), 0, stream, a, x, (size_t)n);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -95,6 +103,8 @@ KF_API int kf_add(const float* a, float* x, long n, cudaStream_t stream) {
 // dst = (bf16 or f32) copy of src with conversion; used where a 32-bit weight meets bf16 activations.
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ src, TO* __restrict__ dst, size_t n) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     kf_store(dst, i, kf_load(src, i));
 }
@@ -104,9 +114,9 @@ KF_API int kf_convert(const void* src, int src_dtype, void* dst, int dst_dtype, 
   const long b = (n + 255) / 256;
   const int blocks = (int)(b > 148 * 16 ? 148 * 16 : b);
   if (src_dtype == KF_BF16 && dst_dtype == KF_F32)
-    convert_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (float*)dst, (size_t)n);
+    kf_launch(convert_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)src, (float*)dst, (size_t)n);
   else if (src_dtype == KF_F32 && dst_dtype == KF_BF16)
-    convert_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)src, (__nv_bfloat16*)dst, (size_t)n);
+    kf_launch(convert_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)src, (__nv_bfloat16*)dst, (size_t)n);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();

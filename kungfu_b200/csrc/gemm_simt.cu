@@ -13,6 +13,8 @@ template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                  int T, int N, int K, float softcap) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -67,9 +69,9 @@ template <typename TX, typename TW>
 static int launch(const TX* x, const TW* w, void* out, int out_dtype, int T, int N, int K, float softcap, cudaStream_t s) {
   dim3 grid(kf_ceil_div(N, BN), kf_ceil_div(T, BM));
   if (out_dtype == KF_F32)
-    gemm_simt_kernel<TX, TW, float><<<grid, 256, 0, s>>>(x, w, (float*)out, T, N, K, softcap);
+    kf_launch(gemm_simt_kernel<TX, TW, float>, dim3(grid), dim3(256), 0, s, x, w, (float*)out, T, N, K, softcap);
   else if (out_dtype == KF_BF16)
-    gemm_simt_kernel<TX, TW, __nv_bfloat16><<<grid, 256, 0, s>>>(x, w, (__nv_bfloat16*)out, T, N, K, softcap);
+    kf_launch(gemm_simt_kernel<TX, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, x, w, (__nv_bfloat16*)out, T, N, K, softcap);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();

@@ -105,7 +105,7 @@ struct Tile {
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
                int stages, float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ error_flag) {
@@ -147,13 +147,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  kf_pdl_trigger();                                               // the next kernel may start its own prologue
 
   if (warp == 0) {
     // ---- TMA producer ------------------------------------------------------------------------------------
+    // The weight tiles of the first stages do not depend on the previous kernel of the stream: they are requested
+    // before the grid dependency is waited for, so weight streaming overlaps the predecessor's tail.
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
+      const int pre = nkb < stages ? nkb : stages;
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(st, &tm_w, &full[i], k, f0);
+        if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[i], k, up_offset + f0);
+      }
+      kf_pdl_wait();                                               // activations come from the previous kernel
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % stages;
-        if (i >= stages && !mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
+        if (!mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
           atomicExch(error_flag, ERR_WAIT_EMPTY);
           s_flags[0] = 1;
           break;
@@ -196,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
   } else {
     // ---- epilogue: warps 2..5, each owns the lane quarter (warp % 4) ---------------------------------------------
+    kf_pdl_wait();                                                             // before any global write
     const int quarter = warp & 3;
     const int f = f0 + quarter * 32 + lane;                                    // this thread's output feature
     const bool acc_ok = mbar_wait(acc_full, 0);
@@ -338,6 +353,10 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   const int nkb = (K + BK - 1) / BK;
   const int kb_per = (nkb + splits - 1) / splits;
   int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  if (BN <= 64) {                                       // weight streaming: leave room for a second resident CTA so
+    const int half = (108 * 1024) / STAGE_BYTES;        // that the next product of the stream can prefetch meanwhile
+    if (stages > half) stages = half;
+  }
   if (stages > kb_per) stages = kb_per;
   if (stages > 12) stages = 12;
   if (stages < 1) return KF_ERR_SIZE;
@@ -352,7 +371,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   }
   const int n_feat = EPI == EPI_GATED ? up_offset : N;
   dim3 grid(kf_ceil_div(n_feat, BM), kf_ceil_div(T, BN), splits);
-  gemm_tc_kernel<BN, EPI><<<grid, THREADS, smem, stream>>>(tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
+  kf_launch(gemm_tc_kernel<BN, EPI>, dim3(grid), dim3(THREADS), smem, stream, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
                                                            partial, counters, error_flag);
   KF_CHECK_LAUNCH();
   return KF_OK;

@@ -7,6 +7,8 @@
 template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, float eps, int plus_one,
                                TO* __restrict__ out, const int* __restrict__ rows, int H) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -26,9 +28,9 @@ static int launch_rmsnorm(const float* x, const TW* w, float eps, int plus_one, 
                           const int* rows, int n, int H, cudaStream_t stream) {
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   if (out_dtype == KF_F32)
-    rmsnorm_kernel<TW, float><<<n, threads, 0, stream>>>(x, w, eps, plus_one, (float*)out, rows, H);
+    kf_launch(rmsnorm_kernel<TW, float>, dim3(n), dim3(threads), 0, stream, x, w, eps, plus_one, (float*)out, rows, H);
   else if (out_dtype == KF_BF16)
-    rmsnorm_kernel<TW, __nv_bfloat16><<<n, threads, 0, stream>>>(x, w, eps, plus_one, (__nv_bfloat16*)out, rows, H);
+    kf_launch(rmsnorm_kernel<TW, __nv_bfloat16>, dim3(n), dim3(threads), 0, stream, x, w, eps, plus_one, (__nv_bfloat16*)out, rows, H);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();
@@ -47,6 +49,8 @@ template <typename TW1, typename TW2, typename TO>
 __global__ void add_rmsnorm_kernel(const float* __restrict__ a, const TW1* __restrict__ w1, float eps1, int plus1,
                                    float* __restrict__ x, const TW2* __restrict__ w2, float eps2, int plus2,
                                    TO* __restrict__ out2, int H) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* ar = a + (size_t)r * H;
@@ -77,9 +81,9 @@ static int launch_add_rmsnorm(const float* a, const TW1* w1, float eps1, int plu
                               int plus2, void* out2, int out2_dtype, int T, int H, cudaStream_t stream) {
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   if (out2 == nullptr || out2_dtype == KF_F32)
-    add_rmsnorm_kernel<TW1, TW2, float><<<T, threads, 0, stream>>>(a, w1, eps1, plus1, x, w2, eps2, plus2, (float*)out2, H);
+    kf_launch(add_rmsnorm_kernel<TW1, TW2, float>, dim3(T), dim3(threads), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (float*)out2, H);
   else if (out2_dtype == KF_BF16)
-    add_rmsnorm_kernel<TW1, TW2, __nv_bfloat16><<<T, threads, 0, stream>>>(a, w1, eps1, plus1, x, w2, eps2, plus2, (__nv_bfloat16*)out2, H);
+    kf_launch(add_rmsnorm_kernel<TW1, TW2, __nv_bfloat16>, dim3(T), dim3(threads), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (__nv_bfloat16*)out2, H);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();

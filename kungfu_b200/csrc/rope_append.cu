@@ -14,6 +14,8 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const float
                                       const int* __restrict__ positions, const int* __restrict__ row_req,
                                       const int* __restrict__ block_table, int table_stride, int page_size,
                                       TKV* __restrict__ pages, TQ* __restrict__ q_out, int write_kv) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   const int t = blockIdx.x;
   const int req = row_req[t];
   const int half = rot >> 1;
@@ -61,7 +63,7 @@ KF_API int kf_rope_kv_append(const float* qkv, const float* cos_t, const float* 
   if (rot > 0 && (!cos_t || !sin_t)) return KF_ERR_SIZE;
   const int threads = 256;
 #define KF_GO(TQ, TKV)                                                                                              \
-  rope_kv_append_kernel<TQ, TKV><<<T, threads, 0, stream>>>(qkv, cos_t, sin_t, rot, nh, nkv, d, positions, row_req, \
+  kf_launch(rope_kv_append_kernel<TQ, TKV>, dim3(T), dim3(threads), 0, stream, qkv, cos_t, sin_t, rot, nh, nkv, d, positions, row_req, \
                                                             block_table, table_stride, page_size, (TKV*)pages,      \
                                                             (TQ*)q_out, write_kv)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);

@@ -14,6 +14,11 @@ extern "C" void kf_record_message(const char* msg) { snprintf(g_last_error, size
 
 KF_API const char* kf_last_cuda_error() { return g_last_error; }
 
+static int g_pdl = 0;
+extern "C" int kf_pdl_enabled() { return g_pdl; }
+// Switch programmatic dependent launch on (1) or off (0) for every kernel launched afterwards.
+KF_API void kf_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 KF_API int kf_abi_version() { return 1; }
 
 // Compute capability of the current device as major*10+minor, or -1.

@@ -37,6 +37,8 @@ __device__ __forceinline__ void block_argmax(float& best, int& bi, float* sv, in
 // Stage 1: block (chunk, row) scans its slice of the row.  With one chunk it writes the answer itself.
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int chunks,
                               float* __restrict__ part_val, int* __restrict__ part_idx) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int row = blockIdx.y, chunk = blockIdx.x;
@@ -59,6 +61,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
 // Stage 2: one warp per row merges the chunks in index order.
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     int* __restrict__ out, int chunks) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   const int row = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -82,10 +86,10 @@ KF_API int kf_argmax(const float* logits, int* out, int rows, int V, float* scra
   int chunks = (scratch && V >= 16384) ? 64 : 1;
   float* pv = scratch;
   int* pi = scratch ? (int*)(scratch + (size_t)rows * 64) : nullptr;
-  argmax_kernel<<<dim3(chunks, rows), chunks == 1 ? 1024 : 256, 0, stream>>>(logits, out, V, chunks, pv, pi);
+  kf_launch(argmax_kernel, dim3(chunks, rows), dim3(chunks == 1 ? 1024 : 256), 0, stream, logits, out, V, chunks, pv, pi);
   KF_CHECK_LAUNCH();
   if (chunks > 1) {
-    argmax_merge_kernel<<<rows, 32, 0, stream>>>(pv, pi, out, chunks);
+    kf_launch(argmax_merge_kernel, dim3(rows), dim3(32), 0, stream, pv, pi, out, chunks);
     KF_CHECK_LAUNCH();
   }
   return KF_OK;
@@ -98,6 +102,8 @@ constexpr int TOPK_THREADS = 1024;
 __global__ void __launch_bounds__(TOPK_THREADS)
 topk_lse_kernel(const float* __restrict__ logits, int* __restrict__ out_ids, float* __restrict__ out_vals,
                 float* __restrict__ out_lse, int V, int k) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
   __shared__ unsigned hist[256];
   __shared__ float red[33];
   __shared__ unsigned s_prefix, s_mask;
@@ -206,7 +212,7 @@ KF_API int kf_topk_lse(const float* logits, int* out_ids, float* out_vals, float
                        cudaStream_t stream) {
   if (rows <= 0) return KF_OK;
   if (k < 1 || k > TOPK_MAX || k > V) return KF_ERR_SIZE;
-  topk_lse_kernel<<<rows, TOPK_THREADS, 0, stream>>>(logits, out_ids, out_vals, out_lse, V, k);
+  kf_launch(topk_lse_kernel, dim3(rows), dim3(TOPK_THREADS), 0, stream, logits, out_ids, out_vals, out_lse, V, k);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

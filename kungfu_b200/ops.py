@@ -46,6 +46,9 @@ def library():
                 path = _build.build()
                 lib = ctypes.CDLL(path)
                 lib.kf_last_cuda_error.restype = ctypes.c_char_p
+                # kernels may start before their predecessor in the stream has finished (each waits for it before
+                # touching dependent memory); KUNGFU_PDL=0 switches that off
+                lib.kf_set_pdl(0 if os.environ.get("KUNGFU_PDL", "1") == "0" else 1)
                 _lib = lib
     return _lib
 
