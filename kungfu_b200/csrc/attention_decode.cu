@@ -9,6 +9,7 @@
 // Head sizes 16, 32, 64, 128, 256 (D/8 lanes per key must divide a warp); other sizes use the generic kernel.
 // Reference counterpart: crates/kf-backend-cuda/src/kernels/attention_decode.cuh:93-458 (split-KV, last block merges).
 #include "common.cuh"
+#include "mma_tiles.cuh"
 
 namespace {
 
@@ -255,6 +256,276 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   if (threadIdx.x == 0) counters[cidx] = 0;
 }
 
+// ---- the tensor-core variant -----------------------------------------------------------------------------------
+// Same work split (item, kv head, key split), but the query heads that share the kv head (up to 16) are the rows
+// of one m16n8k16 tile, so a key costs a handful of instructions instead of a warp's worth of shuffles.  Each of the
+// 4 warps walks its own 16-key tiles of the split: the tile's key and value rows are gathered from the pages into
+// warp-private shared memory by cp.async (double-buffered, so the next tile is in flight while this one is used),
+// S = Q K^T (16 heads x 16 keys) and O += P V run on mma.sync with 32-bit accumulators, the online softmax is the
+// one of the prompt kernel.  Warps are merged through shared memory in warp order, splits by the last block.
+constexpr int DM_WARPS = 4;
+constexpr int DM_KEYS = 16;                       // keys per warp tile
+
+template <int D>
+__global__ void __launch_bounds__(DM_WARPS * 32)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
+                       const int* __restrict__ items, int n_items, const int* __restrict__ positions,
+                       const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
+                       int nh, int nkv, float scale, float softcap, int window, int n_splits,
+                       float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+  using namespace kf_mma;
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  constexpr int CH = D / 8;
+  constexpr int NT_O = D / 8;
+  constexpr int KS_QK = D / 16;
+  constexpr int PSTRIDE = D + 2;
+  constexpr int TILE = DM_KEYS * D;                               // elements of one key (or value) tile
+  extern __shared__ __align__(128) uint8_t dm_smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dm_smem);  // [16][D]
+  __nv_bfloat16* sKV = sQ + 16 * D;                               // [warp][stage][K|V][16][D]
+  __shared__ float sm_ml[DM_WARPS][16][2];
+  __shared__ int s_last;
+
+  const int item = blockIdx.x / nkv, kvh = blockIdx.x - item * nkv;
+  const int split = blockIdx.y;
+  const int G = nh / nkv;
+  const int h_first = kvh * G;
+  const int t = items ? items[item] : item;
+  const int req = row_req[t];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  __nv_bfloat16* orow = out + (size_t)t * nh * D;
+  if (req < 0) {
+    if (split == 0)
+      for (int e = tid; e < G * D; e += blockDim.x) orow[(size_t)h_first * D + e] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = positions[t];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos + 1 - lo;
+  int per = (n_keys + n_splits - 1) / n_splits;
+  per = (per + 63) & ~63;
+  const int k_begin = lo + split * per;
+  const int k_end = min(pos + 1, k_begin + per);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + DM_KEYS - 1) / DM_KEYS : 0;
+
+  // ---- Q: the G heads of this kv head are rows 0..G-1, the rest of the 16 rows are zero ----------------------------
+  for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
+    const int r = idx / CH, c = idx - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h_first + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(tile_ptr<D>(sQ, r, c)) = v;
+  }
+  __syncthreads();
+
+  const int* tab = table + (size_t)req * table_stride;
+  const size_t head_stride = (size_t)page_size * D;
+  const size_t v_off = (size_t)nkv * head_stride;
+  __nv_bfloat16* my = sKV + (size_t)warp * 4 * TILE;              // [stage][K|V]
+
+  auto load_tile = [&](int tile, int stage) {
+    const int j0 = k_begin + tile * DM_KEYS;
+    // lanes 0..15 look up the row of key j0 + lane; everyone fetches a row's base by shuffle
+    long base = -1;
+    if (lane < DM_KEYS) {
+      const int j = j0 + lane;
+      if (j < k_end) {
+        const int page = tab[j / page_size];
+        if (page >= 0) base = ((long)page * 2 * nkv + kvh) * (long)head_stride + (long)(j % page_size) * D;
+      }
+    }
+    __nv_bfloat16* dk = my + (size_t)stage * 2 * TILE;
+    __nv_bfloat16* dv = dk + TILE;
+#pragma unroll
+    for (int i = 0; i < (DM_KEYS * CH + 31) / 32; ++i) {
+      const int idx = lane + 32 * i;
+      const int r = idx / CH, c = idx - r * CH;
+      const long b = __shfl_sync(0xffffffffu, base, r & 15);
+      if (idx < DM_KEYS * CH) {
+        const bool ok = b >= 0;
+        const __nv_bfloat16* src = pages + (ok ? b : 0) + c * 8;
+        cp_async16(tile_ptr<D>(dk, r, c), src, ok);
+        cp_async16(tile_ptr<D>(dv, r, c), src + v_off, ok);
+      }
+    }
+  };
+
+  float o_acc[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) { o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
+
+  if (warp < n_tiles) load_tile(warp, 0);
+  cp_async_commit();
+  int it = 0;
+  for (int tile = warp; tile < n_tiles; tile += DM_WARPS, ++it) {
+    const int stage = it & 1;
+    if (tile + DM_WARPS < n_tiles) load_tile(tile + DM_WARPS, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const __nv_bfloat16* k_s = my + (size_t)stage * 2 * TILE;
+    const __nv_bfloat16* v_s = k_s + TILE;
+    const int j0 = k_begin + tile * DM_KEYS;
+
+    float s_acc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KS_QK; ++ks) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, tile_ptr<D>(sQ, lane & 15, ks * 2 + (lane >> 4)));
+      ldmatrix_x4(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(k_s), (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+      mma_bf16(s_acc[0], a, b[0], b[1]);
+      mma_bf16(s_acc[1], a, b[2], b[3]);
+    }
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int j = j0 + n * 8 + tq * 2 + (e & 1);
+        float s = s_acc[n][e] * scale;
+        if (softcap > 0.f) {
+          const float ex = exp2f(s * cap2);
+          s = softcap * (1.f - __fdividef(2.f, ex + 1.f));
+        }
+        s = (j < k_end) ? s * LOG2E : -INFINITY;
+        s_acc[n][e] = s;
+        m_new[r] = fmaxf(m_new[r], s);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+      corr[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+    }
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const float p = (m_new[r] == -INFINITY) ? 0.f : exp2f(s_acc[n][e] - m_new[r]);
+        s_acc[n][e] = p;
+        l_add[r] += p;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + l_add[r];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      o_acc[n][0] *= corr[0]; o_acc[n][1] *= corr[0];
+      o_acc[n][2] *= corr[1]; o_acc[n][3] *= corr[1];
+    }
+    uint32_t a[4];
+    a[0] = pack_bf16(s_acc[0][0], s_acc[0][1]);
+    a[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
+    a[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
+    a[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
+#pragma unroll
+    for (int np = 0; np < NT_O / 2; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(v_s), (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+      mma_bf16(o_acc[2 * np], a, b[0], b[1]);
+      mma_bf16(o_acc[2 * np + 1], a, b[2], b[3]);
+    }
+    __syncwarp();                                                  // this stage is refilled two turns from now
+  }
+  cp_async_wait<0>();
+  // ---- merge the warps through shared memory (the tile buffers are free now) ---------------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  __syncthreads();
+  float* sm_o = reinterpret_cast<float*>(sKV);                     // [warp][G][D]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + r * 8;
+    if (row < G) {
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        float* dst = sm_o + ((size_t)warp * G + row) * D + n * 8 + tq * 2;
+        dst[0] = o_acc[n][2 * r];
+        dst[1] = o_acc[n][2 * r + 1];
+      }
+      if (tq == 0) { sm_ml[warp][row][0] = m_run[r]; sm_ml[warp][row][1] = l_run[r]; }
+    }
+  }
+  __syncthreads();
+  const size_t rec_base = (((size_t)t * nh + h_first) * n_splits + split) * PSTRIDE;
+  for (int e = tid; e < G * D; e += blockDim.x) {
+    const int h = e / D, i = e - h * D;
+    float m = -INFINITY;
+    for (int w = 0; w < DM_WARPS; ++w) m = fmaxf(m, sm_ml[w][h][0]);
+    float l = 0.f, a = 0.f;
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float mw = sm_ml[w][h][0];
+      const float c = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      l += sm_ml[w][h][1] * c;
+      a += sm_o[((size_t)w * G + h) * D + i] * c;
+    }
+    if (n_splits == 1) {
+      orow[(size_t)(h_first + h) * D + i] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+    } else {
+      float* rec = partial + rec_base + (size_t)h * n_splits * PSTRIDE;
+      rec[i] = a;
+      if (i == 0) { rec[D] = m; rec[D + 1] = l; }
+    }
+  }
+  if (n_splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  const int cidx = item * nkv + kvh;
+  if (tid == 0) s_last = (atomicAdd(&counters[cidx], 1) == n_splits - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = tid; e < G * D; e += blockDim.x) {                  // maxima here are base-2 scaled
+    const int h = e / D, i = e - h * D;
+    const float* rec0 = partial + (((size_t)t * nh + h_first + h) * n_splits) * PSTRIDE;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __ldcg(rec0 + (size_t)s * PSTRIDE + D));
+    float l = 0.f, a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = __ldcg(rec0 + (size_t)s * PSTRIDE + D);
+      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      l += __ldcg(rec0 + (size_t)s * PSTRIDE + D + 1) * c;
+      a += __ldcg(rec0 + (size_t)s * PSTRIDE + i) * c;
+    }
+    orow[(size_t)(h_first + h) * D + i] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+  }
+  if (tid == 0) counters[cidx] = 0;
+}
+
+template <int D>
+int launch_decode_mma(const void* q, const void* pages, const int* items, int n_items, const int* positions,
+                      const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
+                      float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
+  const size_t smem = (size_t)(16 * D + DM_WARPS * 4 * DM_KEYS * D) * 2;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    configured = true;
+  }
+  kf_launch(attn_decode_mma_kernel<D>, dim3(n_items * nkv, n_splits), dim3(DM_WARPS * 32), smem, stream,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, items, n_items, positions, row_req, table, table_stride,
+            page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, (__nv_bfloat16*)out);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
 template <int D, int HT>
 int launch_decode(const void* q, const void* pages, const int* items, int n_items, const int* positions, const int* row_req,
                   const int* table, int table_stride, int page_size, int nh, int nkv, float scale, float softcap, int window,
@@ -280,6 +551,23 @@ int launch_decode_d(int ht, const void* q, const void* pages, const int* items, 
 }
 
 }  // namespace
+
+// The tensor-core variant: ht = 0 selects it in kf_attention_decode.  It takes groups of up to 16 query heads.
+KF_API int kf_attention_decode_mma_plan(int n_items, int nh, int nkv, int d, int max_keys, int* splits_out) {
+  const long blocks = (long)n_items * nkv;
+  // shared memory allows 227 KB / (smem per block) blocks per SM; fill one wave
+  const long smem = (long)(16 * d + DM_WARPS * 4 * DM_KEYS * d) * 2 + 1024;
+  long per_sm = (227 * 1024) / smem;
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  int splits = (int)((148 * per_sm) / blocks);
+  const int by_len = (max_keys + 255) / 256;
+  if (splits > by_len) splits = by_len;
+  if (splits > 64) splits = 64;
+  if (splits < 1) splits = 1;
+  *splits_out = splits;
+  return KF_OK;
+}
 
 KF_API int kf_attention_decode_supported(int d) { return d == 16 || d == 32 || d == 64 || d == 128 || d == 256; }
 
@@ -308,6 +596,19 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
   if (n_items <= 0) return KF_OK;
   if (nkv < 1 || nh % nkv != 0 || page_size < 1 || n_splits < 1) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
+  if (ht == 0) {                                     // tensor-core variant
+    if (nh / nkv > 16) return KF_ERR_SIZE;
+#define KF_MMA_ARGS q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+    switch (d) {
+      case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
+      case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
+      case 64: return launch_decode_mma<64>(KF_MMA_ARGS);
+      case 128: return launch_decode_mma<128>(KF_MMA_ARGS);
+      case 256: return launch_decode_mma<256>(KF_MMA_ARGS);
+    }
+#undef KF_MMA_ARGS
+    return KF_ERR_SIZE;
+  }
 #define KF_ARGS ht, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
   switch (d) {
     case 16: return launch_decode_d<16>(KF_ARGS);

@@ -169,6 +169,7 @@ def add(a, x) -> None:
 _scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor, "error": tensor, "retired": [tensors]}
 use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
 use_fast_attention = True    # likewise for the generic attention kernel
+decode_on_tensor_cores = True   # False: the SIMT split-KV decode kernel (kept for groups of more than 16 heads)
 
 
 def _dev_scratch(device) -> dict:
@@ -289,9 +290,14 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
     if fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
         ht, splits = ctypes.c_int(0), ctypes.c_int(0)
         max_keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        lib.kf_attention_decode_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(ht), ctypes.byref(splits))
+        group = n_heads // n_kv_heads
+        if decode_on_tensor_cores and group <= 16:
+            lib.kf_attention_decode_mma_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(splits))
+            n_counters = n_dec * n_kv_heads                      # ht stays 0: the tensor-core variant
+        else:
+            lib.kf_attention_decode_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(ht), ctypes.byref(splits))
+            n_counters = n_dec * n_kv_heads * -(-group // ht.value)
         sc = _dev_scratch(q.device)
-        n_counters = n_dec * n_kv_heads * -(-(n_heads // n_kv_heads) // ht.value)
         if n_counters > sc["counters"].numel():
             rest, n_rest = None, T
         else:

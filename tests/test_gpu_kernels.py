@@ -256,7 +256,8 @@ def test_paged_attention(ops, dtype, nh, nkv, d, P, window, cap):
 @pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 1000, 50.0),
                                                    (5, 5, 64, 32, None, 30.0), (16, 2, 128, 64, 4096, 50.0), (8, 1, 128, 16, None, 0.0)])
 @pytest.mark.parametrize("mixed", [False, True])
-def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed):
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     """The split-KV decode kernel: single rows of requests of very different lengths (one of them long enough for
     several splits), alone and beside rows of a multi-row request that the other kernel handles."""
     lens = [1, 37, 3000, 700, 64, 65]
@@ -272,9 +273,14 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed):
     ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
                torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
     out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
+    ops.decode_on_tensor_cores = tensor_cores
+    try:
+        ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
+    finally:
+        ops.decode_on_tensor_cores = True
     ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
-    assert rel_err(out.view(len(rows), nh, d), ref) < 1e-2
+    assert bool(torch.isfinite(out.float()).all())
+    assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
 @pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 100, 50.0),
