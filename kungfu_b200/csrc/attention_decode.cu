@@ -264,6 +264,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // S = Q K^T (16 heads x 16 keys) and O += P V run on mma.sync with 32-bit accumulators, the online softmax is the
 // one of the prompt kernel.  Warps are merged through shared memory in warp order, splits by the last block.
 constexpr int DM_WARPS = 4;
+constexpr int DM_STAGES = 3;                     // tiles of a warp in shared memory (one in use, the others in flight)
 constexpr int DM_KEYS = 16;                       // keys per warp tile
 
 template <int D>
@@ -322,7 +323,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
   const size_t v_off = (size_t)nkv * head_stride;
-  __nv_bfloat16* my = sKV + (size_t)warp * 4 * TILE;              // [stage][K|V]
+  __nv_bfloat16* my = sKV + (size_t)warp * DM_STAGES * 2 * TILE;  // [stage][K|V]
 
   auto load_tile = [&](int tile, int stage) {
     const int j0 = k_begin + tile * DM_KEYS;
@@ -357,14 +358,18 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
 
-  if (warp < n_tiles) load_tile(warp, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < DM_STAGES - 1; ++s) {
+    if (warp + s * DM_WARPS < n_tiles) load_tile(warp + s * DM_WARPS, s);
+    cp_async_commit();
+  }
   int it = 0;
   for (int tile = warp; tile < n_tiles; tile += DM_WARPS, ++it) {
-    const int stage = it & 1;
-    if (tile + DM_WARPS < n_tiles) load_tile(tile + DM_WARPS, stage ^ 1);
+    const int stage = it % DM_STAGES;
+    const int ahead = tile + (DM_STAGES - 1) * DM_WARPS;
+    if (ahead < n_tiles) load_tile(ahead, (it + DM_STAGES - 1) % DM_STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<DM_STAGES - 1>();
     __syncwarp();
     const __nv_bfloat16* k_s = my + (size_t)stage * 2 * TILE;
     const __nv_bfloat16* v_s = k_s + TILE;
@@ -436,7 +441,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       mma_bf16(o_acc[2 * np], a, b[0], b[1]);
       mma_bf16(o_acc[2 * np + 1], a, b[2], b[3]);
     }
-    __syncwarp();                                                  // this stage is refilled two turns from now
+    __syncwarp();                                                  // this stage is refilled on the next turn
   }
   cp_async_wait<0>();
   // ---- merge the warps through shared memory (the tile buffers are free now) ---------------------------------------
@@ -510,7 +515,7 @@ template <int D>
 int launch_decode_mma(const void* q, const void* pages, const int* items, int n_items, const int* positions,
                       const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
                       float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
-  const size_t smem = (size_t)(16 * D + DM_WARPS * 4 * DM_KEYS * D) * 2;
+  const size_t smem = (size_t)(16 * D + DM_WARPS * DM_STAGES * 2 * DM_KEYS * D) * 2;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -556,7 +561,7 @@ int launch_decode_d(int ht, const void* q, const void* pages, const int* items, 
 KF_API int kf_attention_decode_mma_plan(int n_items, int nh, int nkv, int d, int max_keys, int* splits_out) {
   const long blocks = (long)n_items * nkv;
   // shared memory allows 227 KB / (smem per block) blocks per SM; fill one wave
-  const long smem = (long)(16 * d + DM_WARPS * 4 * DM_KEYS * d) * 2 + 1024;
+  const long smem = (long)(16 * d + DM_WARPS * DM_STAGES * 2 * DM_KEYS * d) * 2 + 1024;
   long per_sm = (227 * 1024) / smem;
   if (per_sm > 8) per_sm = 8;
   if (per_sm < 1) per_sm = 1;
