@@ -108,7 +108,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
-               int stages, float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ error_flag) {
+               int stages, int cluster_reduce, float* __restrict__ partial, int* __restrict__ counters,
+               int* __restrict__ error_flag) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int NACC = GATED ? 2 : 1;
   constexpr int COLS = Tile<BN>::COLS;
@@ -154,6 +155,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // The weight tiles of the first stages do not depend on the previous kernel of the stream: they are requested
     // before the grid dependency is waited for, so weight streaming overlaps the predecessor's tail.
     if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
       const int pre = nkb < stages ? nkb : stages;
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + (size_t)i * STAGE_BYTES;
@@ -231,8 +234,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
     };
 
-    if (good) {
-      if (splits == 1) {
+    if (good && splits == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16], u[16];
+        tmem_ld16(lane_addr + c0, v);
+        if (GATED) tmem_ld16(lane_addr + COLS + c0, u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t < T && f < n_out) store(t, finish(v[j], GATED ? u[j] : 0.f));
+        }
+      }
+    } else if (splits > 1 && cluster_reduce) {
+      // ---- split-K inside a thread-block cluster: partial tiles stay in shared memory ------------------------------
+      // Each CTA of the cluster (one per K split) parks its accumulator in its own shared memory (the pipeline
+      // stages are free by now); after a cluster barrier CTA r sums, in split order, the tokens t with t % splits == r
+      // straight out of its peers' shared memory and stores them.
+      float* red = reinterpret_cast<float*>(smem);                             // [NACC][BN][128]
+      const int fl = quarter * 32 + lane;
+      if (good) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           float v[16], u[16];
@@ -240,11 +261,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if (GATED) tmem_ld16(lane_addr + COLS + c0, u);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < T && f < n_out) store(t, finish(v[j], GATED ? u[j] : 0.f));
+            red[(size_t)(c0 + j) * BM + fl] = v[j];
+            if (GATED) red[(size_t)(BN + c0 + j) * BM + fl] = u[j];
           }
         }
-      } else {
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      const int rank = blockIdx.z;
+      const uint32_t red_addr = smem_u32(red);
+      const int t_hi = min(BN, T - t0);
+      for (int tl = rank; tl < t_hi; tl += splits) {
+        float v = 0.f, u = 0.f;
+        for (int z = 0; z < splits; ++z) {
+          uint32_t remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr), "r"(z));
+          float pv;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote + (uint32_t)(((size_t)tl * BM + fl) * 4)) : "memory");
+          v += pv;
+          if (GATED) {
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote + (uint32_t)(((size_t)(BN + tl) * BM + fl) * 4)) : "memory");
+            u += pv;
+          }
+        }
+        if (f < n_out) store(t0 + tl, finish(v, u));
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // nobody leaves while peers still read
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else if (splits > 1) {
+      if (good) {
         float* mine = partial + (size_t)blockIdx.z * T * pw;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -261,8 +306,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-    }
-    if (splits > 1) {
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
@@ -287,6 +330,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (warp == 2 && lane == 0) counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
       }
     }
+  }
+  if (warp < 2 && splits > 1 && cluster_reduce) {                  // the two non-epilogue warps join both cluster barriers
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
   // ---- common exit: everyone meets, then tensor memory is freed by the warp that allocated it ------------------
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -344,6 +393,7 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 }
 
 constexpr int SMEM_LIMIT = 220 * 1024;
+int g_cluster_reduce = 1;
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
@@ -371,8 +421,32 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   }
   const int n_feat = EPI == EPI_GATED ? up_offset : N;
   dim3 grid(kf_ceil_div(n_feat, BM), kf_ceil_div(T, BN), splits);
-  kf_launch(gemm_tc_kernel<BN, EPI>, dim3(grid), dim3(THREADS), smem, stream, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
-                                                           partial, counters, error_flag);
+  // split-K inside a cluster needs the partial tile to fit the pipeline's shared memory and at most 8 CTAs
+  const bool cluster = splits > 1 && splits <= 8 && g_cluster_reduce &&
+                       (size_t)NACC * BN * BM * 4 <= (size_t)stages * STAGE_BYTES;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (kf_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
+                     cluster ? 1 : 0, partial, counters, error_flag);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -392,6 +466,9 @@ int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
 
 }  // namespace
 
+// 1: split-K partial tiles are reduced through the cluster's shared memory; 0: through global memory and counters.
+KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; }
+
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
 KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
   return (K % 8 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)w & 15) == 0) && encode_fn() != nullptr;
@@ -407,7 +484,7 @@ KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_ou
   int splits = 1;
   if (tiles <= 74) {                                   // fewer tiles than half the SMs: cut K so that every SM streams
     splits = (int)(148 / tiles);                       // weights, in ONE wave (one CTA per SM fits)
-    if (splits > 16) splits = 16;
+    if (splits > 8) splits = 8;                        // a portable thread-block cluster holds 8 CTAs
     if (splits > nkb) splits = nkb;
     const int kb_per = (nkb + splits - 1) / splits;
     splits = (nkb + kb_per - 1) / kb_per;              // no empty split
