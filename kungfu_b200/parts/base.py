@@ -113,6 +113,9 @@ class Block(Part):
     """An arrangement of norms, one mixer and one feed-forward around the residual stream."""
 
     mixer: Mixer
+    # A block that sets this takes forward(x, ctx, cache, normed=None, then=None) and returns (x, normed_for_next):
+    # `normed` is its own first norm computed by the block before it, `then` the next block's first norm.
+    fuses_next_norm = False
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError

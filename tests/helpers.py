@@ -35,6 +35,18 @@ TINY_C = {
 }
 
 
+# Sizes the fast kernels refuse: rows that are no multiple of 16 bytes (hidden 100, inner 150) and a head size of 20,
+# one kv head for five query heads, no softcaps, every layer windowed.
+TINY_D = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 20,
+    "intermediate_size": 150, "vocab_size": 333, "rope_theta": 10000.0, "sliding_window": 12,
+    "attn_logit_softcapping": 0.0, "final_logit_softcapping": 0.0, "query_pre_attn_scalar": 20,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 96,
+    "hidden_activation": "gelu_pytorch_tanh", "layer_types": ["sliding_attention", "sliding_attention"],
+}
+
+
 def write_model(folder: str, cfg_dict: dict, seed: int, dtype=torch.bfloat16, matrix_scale: float = 1.0):
     """A model folder with random weights through the framework's random-weights mode."""
     from kungfu_b200.api import load_config

@@ -29,10 +29,11 @@ def _compare(got, ref, tol):
     assert worst < tol, f"max abs logit difference {worst}"
 
 
-CASES = [(helpers.TINY_A, [5, 17, 23, 40], 4), (helpers.TINY_B, [1, 31, 40, 70], 8), (helpers.TINY_C, [3, 50, 64, 29, 33], 16)]
+CASES = [(helpers.TINY_A, [5, 17, 23, 40], 4), (helpers.TINY_B, [1, 31, 40, 70], 8), (helpers.TINY_C, [3, 50, 64, 29, 33], 16),
+         (helpers.TINY_D, [2, 40, 17, 90], 4)]
 
 
-@pytest.mark.parametrize("cfg_dict,lengths,page", CASES, ids=["A", "B", "C"])
+@pytest.mark.parametrize("cfg_dict,lengths,page", CASES, ids=["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_cpu_modes_match_plain(tmp_path, cpu_ops, cfg_dict, lengths, page, mode):
     folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=11, dtype=torch.float32)

@@ -21,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOL = {"float32": 2e-4, "bfloat16": 2e-2}
 
 CASES = {"A": (helpers.TINY_A, [5, 17, 23, 40], 4), "B": (helpers.TINY_B, [1, 31, 40, 70], 8),
-         "C": (helpers.TINY_C, [3, 50, 64, 29, 120], 16)}
+         "C": (helpers.TINY_C, [3, 50, 64, 29, 120], 16), "D": (helpers.TINY_D, [2, 40, 17, 90], 4)}
 
 
 @pytest.fixture(scope="module")
@@ -53,7 +53,7 @@ def _steps(mode, reqs):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_modes_match_plain(models, name, mode, dtype):
     from kungfu_b200 import api
     folder, cfg, reqs, ref, page = models[name]
@@ -66,6 +66,24 @@ def test_modes_match_plain(models, name, mode, dtype):
     assert len(got) == sum(len(t) for t in reqs.values())
     _check(got, ref, TOL[dtype])
     assert runner.cache.n_live == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_stored_in_32_bit_stay_so(tmp_path, dtype):
+    """A file whose tensors are 32-bit floats: the bfloat16 engine keeps them 32-bit (and multiplies them with the
+    generic product), the 32-bit engine uses them as they are."""
+    from kungfu_b200 import api
+    cfg = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg, seed=23, dtype=torch.float32)
+    reqs = {"r0": helpers.random_tokens(30, cfg["vocab_size"], 1), "r1": helpers.random_tokens(11, cfg["vocab_size"], 2)}
+    tensors = helpers.read_tensors(folder)
+    ref = {rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+    c, model = api.load_model(folder, dtype=dtype, device=DEV)
+    assert model.layers[0].ffn.w_down.dtype == torch.float32 and model.embedding.table.dtype == torch.float32
+    steps = helpers.trace_mixed(reqs, seed=1)
+    runner = api.make_runner(c, model, dtype=dtype, device=DEV, page_size=8, max_tokens=helpers.trace_max_tokens(steps, 8),
+                             max_requests=4, max_context=64)
+    _check(helpers.run_trace_with_runner(runner, steps), ref, TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
