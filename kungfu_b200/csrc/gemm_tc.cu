@@ -271,19 +271,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int rank = blockIdx.z;
       const uint32_t red_addr = smem_u32(red);
       const int t_hi = min(BN, T - t0);
+      uint32_t remote[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[z]) : "r"(red_addr), "r"(z < splits ? z : 0));
       for (int tl = rank; tl < t_hi; tl += splits) {
-        float v = 0.f, u = 0.f;
-        for (int z = 0; z < splits; ++z) {
-          uint32_t remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr), "r"(z));
-          float pv;
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote + (uint32_t)(((size_t)tl * BM + fl) * 4)) : "memory");
-          v += pv;
-          if (GATED) {
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote + (uint32_t)(((size_t)(BN + tl) * BM + fl) * 4)) : "memory");
-            u += pv;
+        // all peers' values are requested before any is added, so the remote latencies overlap; the sum itself
+        // runs in split order
+        float pv[8], pu[8];
+        const uint32_t off = (uint32_t)(((size_t)tl * BM + fl) * 4);
+        const uint32_t off_u = (uint32_t)(((size_t)(BN + tl) * BM + fl) * 4);
+#pragma unroll
+        for (int z = 0; z < 8; ++z) {
+          pv[z] = 0.f;
+          pu[z] = 0.f;
+          if (z < splits) {
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[z]) : "r"(remote[z] + off) : "memory");
+            if (GATED) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pu[z]) : "r"(remote[z] + off_u) : "memory");
           }
         }
+        float v = 0.f, u = 0.f;
+#pragma unroll
+        for (int z = 0; z < 8; ++z) { v += pv[z]; u += pu[z]; }
         if (f < n_out) store(t0 + tl, finish(v, u));
       }
       asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // nobody leaves while peers still read
