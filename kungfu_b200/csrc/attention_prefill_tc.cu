@@ -1,0 +1,441 @@
+// Prompt-portion attention on the 5th-generation tensor cores: S = Q K^T and O += P V as tcgen05.mma with both
+// accumulators in tensor memory, keys and values fetched page by page with TMA.
+//
+// A block is (tile of up to 128 consecutive rows of one request, query head).  Keys are walked in tiles of 64, which
+// is one cache page (or a 64-aligned part of one), so a tile is a handful of TMA boxes [64 keys x 64 elements].
+//   warp 4   : one lane issues the TMA loads: the Q tile once, then K and V tiles into a two-stage ring
+//   warp 5   : allocates tensor memory; one lane issues the MMAs:  S_i = Q K_i^T (M 128, N 64, K = head size) into
+//              one of two S buffers, and O += P_i V_i (M 128, N = head size, K 64) with V as an MN-major operand
+//   warps 0-3: one thread per query row (= tensor-memory lane): read the row of S, scale, cap, mask, exponentiate,
+//              keep the running maximum and sum, round P to bfloat16 into swizzled shared memory for the second MMA,
+//              and at the end read O, divide by the sum and store the row.
+// The running maximum used for the exponentials is only raised when a tile's maximum exceeds it by more than 8
+// (a factor 256, harmless in bfloat16/32-bit accumulators); only then is O in tensor memory rescaled.  All of S, the
+// softmax and the sums are 32-bit.  Every wait is bounded; on a timeout an error code is recorded and the block
+// leaves through the common exit that frees tensor memory.
+// Head sizes 64, 128, 256; page sizes that are multiples of 64.  Everything else runs the mma.sync kernel.
+// Reference counterpart: crates/kf-backend-cuda/src/kernels/flash.cu (Ampere mma.sync on f16).
+#include "common.cuh"
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+constexpr int BMQ = 128;           // query rows per block
+constexpr int BKV = 64;            // keys per tile
+constexpr int THREADS = 192;
+constexpr long WAIT_LIMIT = 20L * 1000 * 1000;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;
+enum { ERR_ATTN_WAIT = 16 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (long i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(const void* smem) {
+  uint64_t d = (uint64_t)((smem_u32(smem) & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand, 128-byte swizzle: a row of 128 bytes holds 64 consecutive N elements of one K index (one key);
+// 8 keys form a 1024-byte group (stride byte offset), the next 64 N elements start `mn_block_bytes` further
+// (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(const void* smem, uint32_t mn_block_bytes) {
+  uint64_t d = (uint64_t)((smem_u32(smem) & 0x3FFFF) >> 4);
+  d |= (uint64_t)(mn_block_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, M = 128, N = n; b_mn = 1 makes B MN-major.
+__device__ __forceinline__ uint32_t idesc(int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t id, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                       const int* __restrict__ tile_row0, const int* __restrict__ tile_nrows,
+                       const int* __restrict__ positions, const int* __restrict__ row_req,
+                       const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
+                       float scale, float softcap, int window, __nv_bfloat16* __restrict__ out,
+                       int* __restrict__ error_flag) {
+  constexpr int NSUB = D / 64;                            // 64-element sub-tiles along the head dimension
+  constexpr int Q_BYTES = BMQ * D * 2;
+  constexpr int KV_BYTES = BKV * D * 2;                   // one K tile (or one V tile)
+  constexpr int P_BYTES = BMQ * BKV * 2;
+  constexpr int S_COLS = 64;
+  constexpr int TMEM_COLS = (2 * S_COLS + D) <= 256 ? 256 : 512;
+  constexpr uint32_t O_COL = 2 * S_COLS;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Q_BYTES;                             // [2][KV_BYTES]
+  uint8_t* sV = sK + 2 * KV_BYTES;                        // [2][KV_BYTES]
+  uint8_t* sP = sV + 2 * KV_BYTES;
+  uint64_t* bars = (uint64_t*)(sP + P_BYTES);
+  uint64_t* q_full = bars;                                // TMA
+  uint64_t* kv_full = bars + 1;                           // [2] TMA
+  uint64_t* kv_free = bars + 3;                           // [2] commit after P V of the tile in that stage
+  uint64_t* s_full = bars + 5;                            // [2] commit after Q K^T
+  uint64_t* p_full = bars + 7;                            // 128 softmax threads
+  uint64_t* pv_done = bars + 8;                           // commit after P V
+  uint32_t* tmem_slot = (uint32_t*)(bars + 9);
+  volatile int* s_abort = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int row0 = tile_row0[tile], nrows = tile_nrows[tile];
+  const int kvh = h / (nh / nkv);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_free[s], 1); mbar_init(&s_full[s], 1); }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  kf_pdl_trigger();
+  kf_pdl_wait();
+
+  const int req = row_req[row0];
+  const int pos0 = positions[row0];
+  const int pos_last = pos0 + nrows - 1;
+  const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int kt_begin = (lo / BKV) * BKV;
+  const int n_tiles = req < 0 ? 0 : (pos_last - kt_begin) / BKV + 1;
+
+  if (warp == 4) {
+    // ---- TMA producer --------------------------------------------------------------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int j = 0; j < NSUB; ++j) tma_load_2d(sQ + j * (BMQ * 128), &tm_q, q_full, h * D + j * 64, row0);
+      const int* tab = table + (size_t)req * table_stride;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i & 1;
+        if (i >= 2 && !mbar_wait(&kv_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
+        const int kt = kt_begin + i * BKV;
+        int page = tab[kt / page_size];
+        if (page < 0) page = 0;                            // a page already given back: every key of it is masked
+        const int krow = ((page * 2 + 0) * nkv + kvh) * page_size + (kt % page_size);
+        const int vrow = krow + nkv * page_size;
+        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+#pragma unroll
+        for (int j = 0; j < NSUB; ++j) {
+          tma_load_2d(sK + s * KV_BYTES + j * (BKV * 128), &tm_kv, &kv_full[s], j * 64, krow);
+          tma_load_2d(sV + s * KV_BYTES + j * (BKV * 128), &tm_kv, &kv_full[s], j * 64, vrow);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---- MMA issuer ----------------------------------------------------------------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t id_s = idesc(BKV, 0), id_o = idesc(D, 1);
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
+      auto issue_s = [&](int i) {                          // S_i = Q K_i^T into S buffer i & 1
+        const int s = i & 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < NSUB; ++j) {
+          const uint64_t da = desc_kmajor(sQ + j * (BMQ * 128));
+          const uint64_t db = desc_kmajor(sK + s * KV_BYTES + j * (BKV * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma(tmem_base + s * S_COLS, da + 2 * k, db + 2 * k, id_s, (j | k) ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+      };
+      if (ok) issue_s(0);
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int s = i & 1;
+        if (i + 1 < n_tiles) {
+          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          if (ok) issue_s(i + 1);
+        }
+        ok = ok && mbar_wait(p_full, i & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {                      // 16 keys per MMA
+          const uint64_t da = desc_kmajor(sP) + 2 * k;
+          const uint64_t db = desc_mnmajor(sV + s * KV_BYTES + k * 2048, BKV * 128);
+          umma(tmem_base + O_COL, da, db, id_o, (i | k) ? 1u : 0u);
+        }
+        umma_commit(&kv_free[s]);
+        umma_commit(pv_done);
+      }
+      if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 2); *s_abort = 1; }
+    }
+  } else {
+    // ---- softmax and epilogue: thread = query row ---------------------------------------------------------------
+    const int r = warp * 32 + lane;                        // row of the tile = tensor-memory lane
+    const int prow = pos0 + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int sb = i & 1;
+      ok = mbar_wait(&s_full[sb], (i >> 1) & 1);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int kt = kt_begin + i * BKV;
+      float sv[64];
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) tmem_ld16(lane_addr + sb * S_COLS + c, sv + c);
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const int j = kt + c;
+        float s = sv[c] * scale;
+        if (softcap > 0.f) {
+          const float ex = exp2f(s * cap2);
+          s = softcap * (1.f - __fdividef(2.f, ex + 1.f));
+        }
+        const bool seen = j <= prow && (window <= 0 || prow - j < window);
+        s = seen ? s * LOG2E : -INFINITY;
+        sv[c] = s;
+        m_tile = fmaxf(m_tile, s);
+      }
+      const bool raise = m_tile > m_used + RESCALE_STEP;   // also true for the first finite maximum
+      const float m_new = raise ? m_tile : m_used;
+      const float corr = raise ? exp2f(m_used - m_new) : 1.f;      // exp2(-inf) = 0 when nothing was accumulated yet
+      float l_add = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = (m_new == -INFINITY) ? 0.f : exp2f(sv[c] - m_new);
+        const float p1 = (m_new == -INFINITY) ? 0.f : exp2f(sv[c + 1] - m_new);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+        // the sum uses the rounded values, so that P V / sum(P) is a true weighted mean of the value rows
+        const float2 rb = __bfloat1622float2(b);
+        l_add += rb.x + rb.y;
+        pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+      l_sum = l_sum * corr + l_add;
+      m_used = m_new;
+      if (i > 0) {                                          // P V of the previous tile must be done: O is at rest, P is free
+        ok = mbar_wait(pv_done, (i - 1) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, raise)) {              // rescale O (all lanes of the warp take part)
+#pragma unroll 1
+          for (int c = 0; c < D; c += 16) {
+            float o[16];
+            tmem_ld16(lane_addr + O_COL + c, o);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] *= corr;
+            tmem_st16(lane_addr + O_COL + c, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      // P row -> shared memory, K-major with the 128-byte swizzle (chunk index XOR row % 8)
+      uint8_t* prow_ptr = sP + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(prow_ptr + ((ch ^ (r & 7)) << 4)) = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(p_full);
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
+    if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 3); *s_abort = 1; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && n_tiles > 0 && *s_abort == 0) {
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* orow = out + ((size_t)(row0 + r) * nh + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 16) {
+        float o[16];
+        tmem_ld16(lane_addr + O_COL + c, o);               // every lane of the warp takes part in the load
+        if (r < nrows) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
+            w[e] = *reinterpret_cast<const uint32_t*>(&b);
+          }
+          *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+std::mutex g_mutex;
+std::map<std::tuple<const void*, long, long, int>, CUtensorMap> g_maps;
+
+// Row-major [rows, cols] bfloat16 with boxes of [box_rows, 64 elements], 128-byte swizzle.
+bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto key = std::make_tuple(base, rows, cols, box_rows);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (g_maps.size() > 1024) g_maps.clear();
+  g_maps[key] = m;
+  *out = m;
+  return true;
+}
+
+template <int D>
+int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
+           const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
+           float scale, float softcap, int window, void* out, int* error_flag, cudaStream_t stream) {
+  const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    configured = true;
+  }
+  kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out,
+            error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+}  // namespace
+
+KF_API int kf_attention_prefill_tc_supported(int d, int page_size, const void* q, const void* pages) {
+  return (d == 64 || d == 128 || d == 256) && page_size % 64 == 0 && (((uintptr_t)q & 15) == 0) &&
+         (((uintptr_t)pages & 15) == 0) && encode_fn() != nullptr;
+}
+KF_API int kf_attention_prefill_tc_tile_rows() { return BMQ; }
+
+// q, out: [T, nh*d] bfloat16; pages: [n_pages, 2, nkv, page_size, d] bfloat16.  tile_row0/tile_nrows: tiles of up to 128
+// consecutive rows of one request (consecutive positions).
+KF_API int kf_attention_prefill_tc(const void* q, void* out, const void* pages, long n_pages, int T, const int* tile_row0,
+                                   const int* tile_nrows, int n_tiles, const int* positions, const int* row_req,
+                                   const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
+                                   float softcap, int window, int* error_flag, cudaStream_t stream) {
+  if (n_tiles <= 0) return KF_OK;
+  if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0) return KF_ERR_SIZE;
+  CUtensorMap tq, tkv;
+  if (!tensor_map(q, T, (long)nh * d, BMQ, &tq)) return KF_ERR_SETUP;
+  if (!tensor_map(pages, n_pages * 2 * nkv * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
+#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, stream
+  switch (d) {
+    case 64: return launch<64>(KF_ARGS);
+    case 128: return launch<128>(KF_ARGS);
+    case 256: return launch<256>(KF_ARGS);
+  }
+#undef KF_ARGS
+  return KF_ERR_SIZE;
+}

@@ -79,6 +79,8 @@ class StepContext:
         self.max_kv_len = 0
         self.tile_row0 = self.tile_nrows = None   # prompt-portion tiles: first row and row count (device int32)
         self.n_tiles = 0
+        self.wide_row0 = self.wide_nrows = None   # the same rows cut into tiles of up to 128
+        self.n_wide = 0
         # device views, set by Runner._fill
         self.tokens = self.positions = self.row_req = self.logit_rows = None
         self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
@@ -156,6 +158,7 @@ class Runner:
         sec = {}
         for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", max(n_out, 1)),
                         ("dec_rows", T), ("pre_rows", T), ("tile_row0", T // 64 + B + 1), ("tile_nrows", T // 64 + B + 1),
+                        ("wide_row0", T // 128 + B + 1), ("wide_nrows", T // 128 + B + 1),
                         ("req_row_start", B), ("req_n_rows", B), ("req_kv_len", B), ("req_state_slot", B)):
             sec[name] = (o, n)
             o += _align4(n)
@@ -183,7 +186,7 @@ class Runner:
         r = 0
         k = 0
         max_rows = 0
-        dec_rows, pre_rows, tiles = [], [], []
+        dec_rows, pre_rows, tiles, wide = [], [], [], []
         max_kv = 0
         for b, e in enumerate(entries):
             n = len(e.tokens)
@@ -212,6 +215,8 @@ class Runner:
                 pre_rows.extend(range(r, r + n))
                 for a0 in range(0, n, 64):               # tiles of up to 64 consecutive rows of one request
                     tiles.append((r + a0, min(64, n - a0)))
+                for a0 in range(0, n, 128):              # and of up to 128 rows, for the tcgen05 kernel
+                    wide.append((r + a0, min(128, n - a0)))
             r += n
         if bucket is not None:
             dec_rows = list(range(bucket))
@@ -222,6 +227,8 @@ class Runner:
         if tiles:
             view("tile_row0")[:len(tiles)] = [a for a, _ in tiles]
             view("tile_nrows")[:len(tiles)] = [b for _, b in tiles]
+            view("wide_row0")[:len(wide)] = [a for a, _ in wide]
+            view("wide_nrows")[:len(wide)] = [b for _, b in wide]
         dev[:o].copy_(host[:o], non_blocking=True)
         if self.device.type == "cuda":
             if slot[1] is None:
@@ -241,6 +248,7 @@ class Runner:
         ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), len(pre_rows)
         ctx.max_kv_len = max_kv
         ctx.tile_row0, ctx.tile_nrows, ctx.n_tiles = dview("tile_row0"), dview("tile_nrows"), len(tiles)
+        ctx.wide_row0, ctx.wide_nrows, ctx.n_wide = dview("wide_row0"), dview("wide_nrows"), len(wide)
         ctx.req_row_start, ctx.req_n_rows = dview("req_row_start"), dview("req_n_rows")
         ctx.req_kv_len, ctx.req_state_slot = dview("req_kv_len"), dview("req_state_slot")
         ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]

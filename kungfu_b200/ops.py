@@ -169,6 +169,7 @@ def add(a, x) -> None:
 _scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor, "error": tensor, "retired": [tensors]}
 use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
 use_fast_attention = True    # likewise for the generic attention kernel
+prefill_on_tcgen05 = True       # False: the mma.sync prompt kernel for every head and page size
 decode_on_tensor_cores = True   # False: the SIMT split-KV decode kernel (kept for groups of more than 16 heads)
 
 
@@ -312,8 +313,15 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         rest, n_rest = ctx.pre_rows, T
     else:
         rest, n_rest = None, T
-    if (fast and rest is not None and n_rest == ctx.n_pre_rows and getattr(ctx, "n_tiles", 0) > 0
-            and lib.kf_attention_prefill_supported(head_dim)):
+    prompt_tiles = fast and rest is not None and n_rest == ctx.n_pre_rows and getattr(ctx, "n_tiles", 0) > 0
+    if (prompt_tiles and prefill_on_tcgen05 and getattr(ctx, "n_wide", 0) > 0
+            and lib.kf_attention_prefill_tc_supported(head_dim, cache.page_size, _p(q), _p(pages))):
+        sc = _dev_scratch(q.device)
+        _check(lib.kf_attention_prefill_tc(_p(q), _p(out), _p(pages), ctypes.c_long(pages.shape[0]), T, _p(ctx.wide_row0),
+                                           _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), _stream()),
+               "attention (prefill, tcgen05)")
+        return
+    if prompt_tiles and lib.kf_attention_prefill_supported(head_dim):
         _check(lib.kf_attention_prefill(_p(q), _p(out), _p(pages), _p(ctx.tile_row0), _p(ctx.tile_nrows), ctx.n_tiles,
                                         *common, _stream()), "attention (prefill)")
         return

@@ -193,6 +193,16 @@ class _Ctx:
         self.n_tiles = len(tiles)
         self.tile_row0 = torch.tensor([t[0] for t in tiles] or [0], dtype=torch.int32, device=DEV)
         self.tile_nrows = torch.tensor([t[1] for t in tiles] or [0], dtype=torch.int32, device=DEV)
+        wide = []
+        if pre_rows:
+            start = pre_rows[0]
+            for a, b in zip(pre_rows, pre_rows[1:] + [None]):
+                if b is None or b != a + 1 or req[b] != req[a] or a + 1 - start == 128:
+                    wide.append((start, a + 1 - start))
+                    start = b
+        self.n_wide = len(wide)
+        self.wide_row0 = torch.tensor([t[0] for t in wide] or [0], dtype=torch.int32, device=DEV)
+        self.wide_nrows = torch.tensor([t[1] for t in wide] or [0], dtype=torch.int32, device=DEV)
 
 
 def _paged_setup(dtype, nh, nkv, d, P, lens, seed, scramble=True):
@@ -285,7 +295,8 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
 
 @pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 100, 50.0),
                                                    (5, 5, 64, 32, None, 30.0), (16, 2, 128, 64, 70, 50.0), (8, 1, 128, 16, None, 0.0),
-                                                   (2, 1, 256, 8, None, 0.0)])
+                                                   (2, 1, 256, 8, None, 0.0), (4, 2, 64, 64, 100, 30.0), (3, 1, 128, 128, None, 0.0),
+                                                   (8, 4, 256, 64, None, 50.0), (8, 8, 128, 64, 200, 20.0)])
 def test_prefill_attention(ops, nh, nkv, d, P, window, cap):
     """The tensor-core prompt kernel: a whole prompt from position 0 (several tiles, the last one ragged), a portion
     that continues a long request, a two-row portion, beside single rows that the decode kernel takes."""
@@ -305,6 +316,7 @@ def test_prefill_attention(ops, nh, nkv, d, P, window, cap):
     ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, window)
     ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, cap, window) for i, (r, p) in enumerate(rows)])
     got = out.view(len(rows), nh, d)
+    ops.raise_on_device_error()
     assert bool(torch.isfinite(got.float()).all())
     assert rel_err(got, ref) < 1.5e-2
 
