@@ -92,6 +92,16 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -102,6 +112,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 64 consecutive columns of this thread's lane, one wait for all four loads
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+  uint32_t r[64];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
+          "=r"(r[16 * q + 15])
+        : "r"(taddr + 16 * q));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
   asm volatile(
@@ -244,7 +270,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int r = warp * 32 + lane;                        // row of the tile = tensor-memory lane
     const int prow = pos0 + r;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
+    const float c0 = scale * LOG2E;                                        // no cap: s2 = s * c0
+    const float c1 = softcap > 0.f ? scale * 2.f * LOG2E / softcap : 0.f;   // exp(2 x / cap) = exp2(s * c1)
+    const float c3 = softcap * LOG2E;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int i = 0; i < n_tiles && ok; ++i) {
@@ -254,35 +282,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int kt = kt_begin + i * BKV;
       float sv[64];
-#pragma unroll
-      for (int c = 0; c < 64; c += 16) tmem_ld16(lane_addr + sb * S_COLS + c, sv + c);
+      tmem_ld64(lane_addr + sb * S_COLS, sv);
+      // Scores in base-2 units: s2 = log2(e) * cap * tanh(scale * s / cap) = c3 - 2 c3 / (exp2(s * c1) + 1), or
+      // s * c0 without a cap.  A tile that every row of this warp sees whole skips the mask.
+      const bool whole = (kt + BKV - 1 <= pos0 + warp * 32) && (window <= 0 || pos0 + warp * 32 + 31 - kt < window);
       float m_tile = -INFINITY;
+      if (softcap > 0.f) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int j = kt + c;
-        float s = sv[c] * scale;
-        if (softcap > 0.f) {
-          const float ex = exp2f(s * cap2);
-          s = softcap * (1.f - __fdividef(2.f, ex + 1.f));
-        }
-        const bool seen = j <= prow && (window <= 0 || prow - j < window);
-        s = seen ? s * LOG2E : -INFINITY;
-        sv[c] = s;
-        m_tile = fmaxf(m_tile, s);
+        for (int c = 0; c < 64; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) sv[c] *= c0;
       }
+      if (!whole) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int j = kt + c;
+          const bool seen = j <= prow && (window <= 0 || prow - j < window);
+          sv[c] = seen ? sv[c] : -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 64; ++c) m_tile = fmaxf(m_tile, sv[c]);
       const bool raise = m_tile > m_used + RESCALE_STEP;   // also true for the first finite maximum
       const float m_new = raise ? m_tile : m_used;
-      const float corr = raise ? exp2f(m_used - m_new) : 1.f;      // exp2(-inf) = 0 when nothing was accumulated yet
+      const float corr = raise ? ex2_fast(m_used - m_new) : 1.f;   // exp2(-inf) = 0 when nothing was accumulated yet
+      const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen nothing yet: exp2(-inf - 0) = 0
       float l_add = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = (m_new == -INFINITY) ? 0.f : exp2f(sv[c] - m_new);
-        const float p1 = (m_new == -INFINITY) ? 0.f : exp2f(sv[c + 1] - m_new);
+        const float p0 = ex2_fast(sv[c] - m_sub);
+        const float p1 = ex2_fast(sv[c + 1] - m_sub);
+        l_add += p0 + p1;
         const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-        // the sum uses the rounded values, so that P V / sum(P) is a true weighted mean of the value rows
-        const float2 rb = __bfloat1622float2(b);
-        l_add += rb.x + rb.y;
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
       }
       l_sum = l_sum * corr + l_add;
