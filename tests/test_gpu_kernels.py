@@ -32,7 +32,7 @@ def test_embed(ops, dtype):
     assert torch.equal(out, ref)
 
 
-@pytest.mark.parametrize("H", [70, 2304, 5000])
+@pytest.mark.parametrize("H", [70, 2304, 5000, 9000])
 @pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)])
 def test_rmsnorm(ops, H, wdtype, odtype):
     g = torch.Generator().manual_seed(1)
@@ -48,7 +48,7 @@ def test_rmsnorm(ops, H, wdtype, odtype):
         assert rel_err(out, ref) < (1e-5 if odtype == torch.float32 else 6e-3)
 
 
-@pytest.mark.parametrize("H", [96, 3584])
+@pytest.mark.parametrize("H", [96, 3584, 9000])
 @pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(ops, H, odtype):
     g = torch.Generator().manual_seed(2)
