@@ -94,6 +94,66 @@ __global__ void add_rmsnorm_reg_kernel(const float* __restrict__ a, const TW1* _
   }
 }
 
+// Many rows (prompt portions): one warp per row, the row in registers as float4, no block barrier.
+// Needs H % 4 == 0 and H <= 128 * NV4.
+template <typename TW>
+__device__ __forceinline__ float4 kf_gain4(const TW* w, int i, int plus_one) {
+  const float p = plus_one ? 1.f : 0.f;
+  return make_float4(kf_load(w, i) + p, kf_load(w, i + 1) + p, kf_load(w, i + 2) + p, kf_load(w, i + 3) + p);
+}
+__device__ __forceinline__ void kf_store4(float* o, int i, float4 v) { *reinterpret_cast<float4*>(o + i) = v; }
+__device__ __forceinline__ void kf_store4(__nv_bfloat16* o, int i, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(o + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename TW1, typename TW2, typename TO, int NV4>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(const float* __restrict__ a, const TW1* __restrict__ w1, float eps1, int plus1,
+                        float* __restrict__ x, const TW2* __restrict__ w2, float eps2, int plus2,
+                        TO* __restrict__ out2, int T, int H) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= T) return;
+  const float* ar = a + (size_t)r * H;
+  float* xr = x + (size_t)r * H;
+  float4 v[NV4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV4; ++k) {
+    const int i = (lane + 32 * k) * 4;
+    v[k] = i < H ? *reinterpret_cast<const float4*>(ar + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  ss = kf_warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps1);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV4; ++k) {
+    const int i = (lane + 32 * k) * 4;
+    if (i < H) {
+      const float4 g = kf_gain4(w1, i, plus1);
+      const float4 xo = *reinterpret_cast<const float4*>(xr + i);
+      v[k] = make_float4(xo.x + v[k].x * inv * g.x, xo.y + v[k].y * inv * g.y, xo.z + v[k].z * inv * g.z, xo.w + v[k].w * inv * g.w);
+      *reinterpret_cast<float4*>(xr + i) = v[k];
+      ss2 += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  if (out2 == nullptr) return;
+  ss2 = kf_warp_sum(ss2);
+  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  TO* o = out2 + (size_t)r * H;
+#pragma unroll
+  for (int k = 0; k < NV4; ++k) {
+    const int i = (lane + 32 * k) * 4;
+    if (i < H) {
+      const float4 g = kf_gain4(w2, i, plus2);
+      kf_store4(o, i, make_float4(v[k].x * inv2 * g.x, v[k].y * inv2 * g.y, v[k].z * inv2 * g.z, v[k].w * inv2 * g.w));
+    }
+  }
+}
+
 template <typename TW>
 static int launch_rmsnorm(const float* x, const TW* w, float eps, int plus_one, void* out, int out_dtype,
                           const int* rows, int n, int H, cudaStream_t stream) {
@@ -164,6 +224,21 @@ template <typename TW1, typename TW2>
 static int launch_add_rmsnorm(const float* a, const TW1* w1, float eps1, int plus1, float* x, const TW2* w2, float eps2,
                               int plus2, void* out2, int out2_dtype, int T, int H, cudaStream_t stream) {
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  const bool aligned = H % 4 == 0 && (((uintptr_t)a | (uintptr_t)x | (uintptr_t)out2) & 15) == 0;
+  if (T >= 256 && aligned && H <= 128 * 40 && H >= 128) {        // many rows: a warp per row
+    const int nv4 = kf_ceil_div(H, 128);
+#define KF_GO(TO, NV4) kf_launch(add_rmsnorm_warp_kernel<TW1, TW2, TO, NV4>, dim3(kf_ceil_div(T, 8)), dim3(256), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (TO*)out2, T, H)
+#define KF_PICK(TO)                                                                         \
+    if (nv4 <= 8) KF_GO(TO, 8); else if (nv4 <= 16) KF_GO(TO, 16); else if (nv4 <= 24) KF_GO(TO, 24); \
+    else if (nv4 <= 32) KF_GO(TO, 32); else KF_GO(TO, 40)
+    if (out2 == nullptr || out2_dtype == KF_F32) { KF_PICK(float); }
+    else if (out2_dtype == KF_BF16) { KF_PICK(__nv_bfloat16); }
+    else return KF_ERR_DTYPE;
+#undef KF_PICK
+#undef KF_GO
+    KF_CHECK_LAUNCH();
+    return KF_OK;
+  }
   if (H <= 16 * threads) {
     const int npt = kf_ceil_div(H, threads);
 #define KF_GO(TO, NPT) kf_launch(add_rmsnorm_reg_kernel<TW1, TW2, TO, NPT>, dim3(T), dim3(threads), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (TO*)out2, H)

@@ -48,12 +48,13 @@ def test_rmsnorm(ops, H, wdtype, odtype):
         assert rel_err(out, ref) < (1e-5 if odtype == torch.float32 else 6e-3)
 
 
-@pytest.mark.parametrize("H", [96, 3584, 9000])
+@pytest.mark.parametrize("H", [96, 2304, 3584, 4608, 9000])
 @pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
-def test_add_rmsnorm(ops, H, odtype):
+@pytest.mark.parametrize("T", [11, 300])
+def test_add_rmsnorm(ops, H, odtype, T):
     g = torch.Generator().manual_seed(2)
-    a = torch.randn(11, H, generator=g).to(DEV)
-    x = torch.randn(11, H, generator=g).to(DEV)
+    a = torch.randn(T, H, generator=g).to(DEV)
+    x = torch.randn(T, H, generator=g).to(DEV)
     w1 = (torch.randn(H, generator=g) * 0.1).to(DEV)
     w2 = (torch.randn(H, generator=g) * 0.1).to(DEV)
     ad, xd = a.double(), x.double()
@@ -63,7 +64,7 @@ def test_add_rmsnorm(ops, H, odtype):
     ops.add_rmsnorm(a, w1, 1e-6, True, x1)
     assert rel_err(x1, x_ref) < 1e-5
     x2 = x.clone()
-    out = torch.empty(11, H, dtype=odtype, device=DEV)
+    out = torch.empty(T, H, dtype=odtype, device=DEV)
     ops.add_rmsnorm(a, w1, 1e-6, True, x2, next_weight=w2, next_eps=1e-4, next_plus_one=False, next_out=out)
     assert torch.equal(x1, x2)
     assert rel_err(out, n_ref) < (1e-5 if odtype == torch.float32 else 6e-3)
