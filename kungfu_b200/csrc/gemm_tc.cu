@@ -39,6 +39,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -95,6 +98,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Activations of the gated epilogue through the hardware exponential and reciprocal (relative error ~1e-6, far below
+// the bfloat16 rounding of the result).  The 32-bit path of the engine uses tanhf/expf in its own kernel.
+__device__ __forceinline__ float act_fast(float x, int act) {
+  if (act == KF_ACT_GELU_TANH) {
+    const float y = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y * 2.885390081777927f));      // exp(2y)
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return 0.5f * x * (2.f - 2.f * r);                                               // 0.5 x (1 + tanh y)
+  }
+  if (act == KF_ACT_SILU) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return x * r;
+  }
+  return kf_act(x, act);
 }
 
 template <int BN>
@@ -225,7 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int pw = GATED ? 2 * up_offset : N;                                  // width of a partial row
 
     auto finish = [&](float v, float u) -> float {
-      if (EPI == EPI_GATED) return kf_act(v, act) * u;
+      if (EPI == EPI_GATED) return act_fast(v, act) * u;
       if (EPI == EPI_F32) return kf_softcap(v, softcap);
       return v;
     };
@@ -355,6 +377,160 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   }
 }
 
+
+// ---- persistent variant for many tokens ------------------------------------------------------------------------------
+// One CTA per SM walks tiles (feature tile fastest, so that CTAs running side by side share the token tile in L2) and
+// keeps TWO accumulators in tensor memory: while the epilogue warps drain one (tcgen05.ld, activation, store), the MMA
+// warp already fills the other, and the TMA warp runs ahead through the stage ring across tile boundaries.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                          void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
+                          int stages, int* __restrict__ error_flag) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int NACC = GATED ? 2 : 1;
+  constexpr int COLS = Tile<BN>::COLS;
+  constexpr int ACC_COLS = COLS * NACC;                           // columns of one accumulator set
+  constexpr int TMEM_COLS = 2 * ACC_COLS <= 256 ? 256 : 512;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit tensor memory");
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;                            // [2]
+  uint64_t* acc_empty = acc_full + 2;                             // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* s_abort = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_feat = GATED ? up_offset : N;
+  const int n_ft = (n_feat + BM - 1) / BM, n_tt = (T + BN - 1) / BN;
+  const int n_tiles = n_ft * n_tt;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  kf_pdl_trigger();
+
+  if (warp == 0) {
+    // ---- TMA producer: one stream of k blocks across all of this CTA's tiles ------------------------------------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
+      kf_pdl_wait();
+      long it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int f0 = (tile % n_ft) * BM, t0 = (tile / n_ft) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          if (it >= stages && !mbar_wait(&empty[s], (uint32_t)((it / stages) - 1) & 1)) {
+            atomicExch(error_flag, ERR_WAIT_EMPTY);
+            *s_abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          const int k = kb * BK;
+          tma_load_2d(st, &tm_w, &full[s], k, f0);
+          if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[s], k, up_offset + f0);
+          tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ------------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BN);
+      long it = 0;
+      int ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
+        const int buf = ti & 1;
+        if (ti >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((ti >> 1) - 1) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem_base + buf * ACC_COLS;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          if (!mbar_wait(&full[s], (uint32_t)(it / stages) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          const uint64_t da = umma_desc(st);
+          const uint64_t db = umma_desc(st + Tile<BN>::A_BYTES * NACC);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+            umma(acc, da + koff, db + koff, idesc, accumulate);
+            if (GATED) umma(acc + COLS, umma_desc(st + Tile<BN>::A_BYTES) + koff, db + koff, idesc, accumulate);
+          }
+          umma_commit(&empty[s]);
+        }
+        umma_commit(&acc_full[buf]);
+      }
+      if (!ok) { atomicExch(error_flag, ERR_WAIT_FULL); *s_abort = 1; }
+    }
+  } else {
+    // ---- epilogue: drains one accumulator set while the other is being filled -----------------------------------------
+    kf_pdl_wait();
+    const int quarter = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int ti = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+      const int buf = ti & 1;
+      const int f0 = (tile % n_ft) * BM, t0 = (tile / n_ft) * BN;
+      const int f = f0 + quarter * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (uint32_t)(ti >> 1) & 1) || *s_abort) {
+        if (lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = lane_addr + buf * ACC_COLS;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16], u[16];
+        tmem_ld16(acc + c0, v);
+        if (GATED) tmem_ld16(acc + COLS + c0, u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t < T && f < n_feat) {
+            float r;
+            if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
+            else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
+            else r = v[j];
+            if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
+            else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -460,6 +636,37 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   return KF_OK;
 }
 
+int g_persistent = 1;
+
+template <int BN, int EPI>
+int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
+                      int act, int up_offset, int* error_flag, cudaStream_t stream) {
+  constexpr int NACC = EPI == EPI_GATED ? 2 : 1;
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
+  int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return KF_ERR_SIZE;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
+  static bool configured = false;
+  static int n_sm = 148;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int n_feat = EPI == EPI_GATED ? up_offset : N;
+  const int n_tiles = kf_ceil_div(n_feat, BM) * kf_ceil_div(T, BN);
+  const int grid = n_tiles < n_sm ? n_tiles : n_sm;
+  kf_launch(gemm_tc_persistent_kernel<BN, EPI>, dim3(grid), dim3(THREADS), smem, stream, tw, tx, out, T, N, K, ld_out,
+            softcap, act, up_offset, stages, error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
 template <int EPI>
 int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
               int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t s) {
@@ -477,6 +684,9 @@ int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
 
 // 1: split-K partial tiles are reduced through the cluster's shared memory; 0: through global memory and counters.
 KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; }
+
+// 1: products over many tokens run the persistent kernel; 0: one tile per CTA for every shape.
+KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
 KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
@@ -516,6 +726,18 @@ KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T
   CUtensorMap tw, tx;
   if (!tensor_map(w, w_rows, K, BM, &tw) || !tensor_map(x, T, K, bn, &tx)) return KF_ERR_SETUP;
   const int up_offset = mode == EPI_GATED ? N : 0;
+  if (g_persistent && splits == 1 && bn >= 128) {
+    // many tokens: the persistent kernel with two accumulator sets.  The gated epilogue needs two accumulators per
+    // set, so its token tile is 128; the token tensor map must match the tile.
+    const int pbn = (mode == EPI_GATED) ? 128 : bn;
+    CUtensorMap txp = tx;
+    if (pbn != bn && !tensor_map(x, T, K, pbn, &txp)) return KF_ERR_SETUP;
+    if (mode == EPI_F32) return pbn == 256 ? launch_persistent<256, EPI_F32>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream)
+                                            : launch_persistent<128, EPI_F32>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+    if (mode == EPI_BF16) return pbn == 256 ? launch_persistent<256, EPI_BF16>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream)
+                                             : launch_persistent<128, EPI_BF16>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+    return launch_persistent<128, EPI_GATED>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+  }
   switch (mode) {
     case EPI_F32: return launch_bn<EPI_F32>(bn, tw, tx, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
     case EPI_BF16: return launch_bn<EPI_BF16>(bn, tw, tx, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
