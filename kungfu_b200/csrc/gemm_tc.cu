@@ -579,6 +579,7 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 
 constexpr int SMEM_LIMIT = 220 * 1024;
 int g_cluster_reduce = 1;
+int g_stage_cap_kb = 108;
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
@@ -588,9 +589,9 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   const int nkb = (K + BK - 1) / BK;
   const int kb_per = (nkb + splits - 1) / splits;
   int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
-  if (BN <= 64) {                                       // weight streaming: leave room for a second resident CTA so
-    const int half = (108 * 1024) / STAGE_BYTES;        // that the next product of the stream can prefetch meanwhile
-    if (stages > half) stages = half;
+  if (BN <= 64 && g_stage_cap_kb > 0) {                 // weight streaming: optionally leave room for a second resident
+    const int cap = (g_stage_cap_kb * 1024) / STAGE_BYTES;   // CTA so that the next product can prefetch meanwhile
+    if (stages > cap) stages = cap;
   }
   if (stages > kb_per) stages = kb_per;
   if (stages > 12) stages = 12;
@@ -637,6 +638,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
 }
 
 int g_persistent = 1;
+int g_gated_wide = 1;      // gated products over >= 256 tokens: one 2 x (128 x 256) tile per CTA (less shared-memory fill per flop)
 
 template <int BN, int EPI>
 int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
@@ -686,7 +688,9 @@ int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
 KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; }
 
 // 1: products over many tokens run the persistent kernel; 0: one tile per CTA for every shape.
+KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
+KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
 KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
@@ -726,7 +730,7 @@ KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T
   CUtensorMap tw, tx;
   if (!tensor_map(w, w_rows, K, BM, &tw) || !tensor_map(x, T, K, bn, &tx)) return KF_ERR_SETUP;
   const int up_offset = mode == EPI_GATED ? N : 0;
-  if (g_persistent && splits == 1 && bn >= 128) {
+  if (g_persistent && splits == 1 && bn >= 128 && !(mode == EPI_GATED && bn == 256 && g_gated_wide)) {
     // many tokens: the persistent kernel with two accumulator sets.  The gated epilogue needs two accumulators per
     // set, so its token tile is 128; the token tensor map must match the tile.
     const int pbn = (mode == EPI_GATED) ? 128 : bn;

@@ -49,6 +49,8 @@ def library():
                 # kernels may start before their predecessor in the stream has finished (each waits for it before
                 # touching dependent memory); KUNGFU_PDL=0 switches that off
                 lib.kf_set_pdl(0 if os.environ.get("KUNGFU_PDL", "1") == "0" else 1)
+                if os.environ.get("KUNGFU_GEMM_STAGE_KB"):           # tuning knob: shared memory per weight-streaming CTA
+                    lib.kf_set_gemm_stage_cap_kb(int(os.environ["KUNGFU_GEMM_STAGE_KB"]))
                 _lib = lib
     return _lib
 
