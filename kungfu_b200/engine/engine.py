@@ -165,6 +165,8 @@ class Engine:
             ev = self.step()
             if not ev and before == sum(len(self.requests[i].output) for i in ids) and self.scheduler.idle:
                 break
+        if self.runner.device.type == "cuda":
+            ops.raise_on_device_error(self.runner.device)
         return [list(self.requests[i].output) for i in ids]
 
     def finish_reason(self, request_id: Hashable) -> str | None:
