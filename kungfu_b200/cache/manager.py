@@ -23,6 +23,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedState, PagedKV
@@ -121,6 +122,9 @@ class CacheManager:
                 self.storage[s] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=self.device)
             elif need is not None:
                 raise TypeError(f"cache slot {s}: unknown state need {need!r}")
+        # host mirror of every block table, one row per state slot, ready to be copied into a step's integer block
+        self._table_np = [np.full((self.max_requests, (self.max_pages_per_request + 3) & ~3), -1, dtype=np.int32)
+                          for _ in self.groups]          # width padded to a multiple of 4, as the step's block is
         self._length: dict = {}                 # request -> tokens committed
         self._reserved: dict = {}               # request -> tokens reserved beyond the committed length
         self._state_slot: dict = {}
@@ -150,9 +154,10 @@ class CacheManager:
         self._state_slot[request] = slot
         self._length[request] = 0
         self._reserved[request] = 0
-        for g in self.groups:
+        for gi, g in enumerate(self.groups):
             g.tables[request] = []
             g.first_live[request] = 0
+            self._table_np[gi][slot, :] = -1
         for s, need in enumerate(self.needs):
             if isinstance(need, FixedState):
                 self.storage[s][slot].zero_()
@@ -179,20 +184,25 @@ class CacheManager:
         for n, g in zip(needed, self.groups):
             if n > g.pool.n_free:
                 raise OutOfPages(f"group with window {g.window}: {n} pages needed, {g.pool.n_free} free")
-        for n, g in zip(needed, self.groups):
+        slot = self._state_slot[request]
+        for gi, (n, g) in enumerate(zip(needed, self.groups)):
             table = g.tables[request]
             for _ in range(n):
-                table.append(g.pool.take())
+                page = g.pool.take()
+                self._table_np[gi][slot, len(table)] = page
+                table.append(page)
         self._reserved[request] += n_new
 
     def cancel_reservation(self, request) -> None:
         """Give back the pages taken for tokens that were reserved but never committed."""
         self._reserved[request] = 0
         keep = -(-self._length[request] // self.page_size)
-        for g in self.groups:
+        slot = self._state_slot[request]
+        for gi, g in enumerate(self.groups):
             table = g.tables[request]
             while len(table) > keep:
                 p = table.pop()
+                self._table_np[gi][slot, len(table)] = -1
                 if p >= 0:
                     g.pool.give_back(p)
 
@@ -203,7 +213,8 @@ class CacheManager:
         self._reserved[request] -= n_new
         self._length[request] += n_new
         n = self._length[request]
-        for g in self.groups:
+        slot = self._state_slot[request]
+        for gi, g in enumerate(self.groups):
             if g.window is None:
                 continue
             # positions < n - window + 1 are out of reach of every later query
@@ -213,17 +224,20 @@ class CacheManager:
                 if table[i] >= 0:
                     g.pool.give_back(table[i])
                     table[i] = -1
+                    self._table_np[gi][slot, i] = -1
             g.first_live[request] = max(g.first_live[request], min(dead_pages, len(table)))
 
     def release(self, request) -> None:
         """The request is finished (or preempted): everything it holds goes back."""
         if request not in self._length:
             raise CacheError(f"request {request!r} is not live")
-        for g in self.groups:
+        slot = self._state_slot[request]
+        for gi, g in enumerate(self.groups):
             for p in g.tables.pop(request):
                 if p >= 0:
                     g.pool.give_back(p)
             g.first_live.pop(request)
+            self._table_np[gi][slot, :] = -1
         self._free_state_slots.append(self._state_slot.pop(request))
         del self._length[request]
         del self._reserved[request]
@@ -231,6 +245,10 @@ class CacheManager:
     # ---- what a step needs ----------------------------------------------------------------------
     def block_table(self, group: int, request) -> list[int]:
         return self.groups[group].tables[request]
+
+    def table_rows(self, group: int, state_slots) -> np.ndarray:
+        """Block-table rows (full width, -1 where no page is held) of the requests in the given state slots."""
+        return self._table_np[group][state_slots]
 
     def group_of(self, cache_slot: int) -> int | None:
         return self._group_of_slot.get(cache_slot)
@@ -265,6 +283,10 @@ class CacheManager:
                     if p in seen:
                         raise CacheError(f"group {gi}: page {p} held by {seen[p]!r} and {req!r}")
                     seen[p] = req
+            for req, table in g.tables.items():
+                row = self._table_np[gi][self._state_slot[req]]
+                if list(row[:len(table)]) != list(table) or (row[len(table):] != -1).any():
+                    raise CacheError(f"group {gi}: host mirror of {req!r}'s block table is stale")
             held = set(g.pool.held_pages())
             if held != set(seen):
                 raise CacheError(f"group {gi}: pool holds {sorted(held)}, tables hold {sorted(seen)}")

@@ -203,10 +203,7 @@ class Runner:
                 k += 1
             for g in range(G):
                 a, _ = sec[f"table{g}"]
-                row = h[a + b * width: a + (b + 1) * width]
-                row[:] = -1
-                tab = cache.block_table(g, e.request)
-                row[:len(tab)] = tab
+                h[a + b * width: a + (b + 1) * width] = cache.table_rows(g, cache.state_slot(e.request))[:width]
             max_rows = max(max_rows, n)
             max_kv = max(max_kv, start + n)
             if n == 1:
@@ -254,7 +251,50 @@ class Runner:
         ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]
         ctx.host = {name: view(name).copy() for name in ("positions", "row_req", "req_row_start", "req_n_rows",
                                                          "req_kv_len", "req_state_slot")}
+        ctx.layout = (sec, o, width)
         return ctx
+
+    def _fill_decode_block(self, entries, bucket: int, layout) -> None:
+        """The integer block of a decode-only step whose graph already exists: same layout as `_fill(entries, bucket)`
+        builds, written with a few vector operations and copied; no context object is needed for a replay."""
+        cache = self.cache
+        sec, o, width = layout
+        n = len(entries)
+        slot, dev = self._meta_buffers(o)
+        self.last_meta_ints = o
+        host = slot[0]
+        h = host.numpy()
+        lengths = np.fromiter((cache._length[e.request] for e in entries), dtype=np.int32, count=n)
+        slots = np.fromiter((cache._state_slot[e.request] for e in entries), dtype=np.int64, count=n)
+        h[:o] = 0
+
+        def put(name, values, fill=None):
+            a, m = sec[name]
+            if fill is not None:
+                h[a:a + m] = fill
+            h[a:a + n] = values
+
+        put("tokens", np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n))
+        put("positions", lengths)
+        put("row_req", np.arange(n, dtype=np.int32), fill=-1)
+        put("req_row_start", np.arange(n, dtype=np.int32))
+        put("req_n_rows", 1)
+        put("req_kv_len", lengths + 1)
+        put("req_state_slot", slots)
+        ar = np.arange(bucket, dtype=np.int32)
+        a, m = sec["logit_rows"]
+        h[a:a + bucket] = ar
+        a, m = sec["dec_rows"]
+        h[a:a + bucket] = ar
+        for g in range(len(cache.groups)):
+            a, m = sec[f"table{g}"]
+            block = h[a:a + m].reshape(bucket, width)
+            block[:] = -1
+            block[:n] = cache.table_rows(g, slots)[:, :width]
+        dev[:o].copy_(host[:o], non_blocking=True)
+        if slot[1] is None:
+            slot[1] = torch.cuda.Event()
+        slot[1].record()
 
     # ---- the step -------------------------------------------------------------------------------------
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -320,12 +360,17 @@ class Runner:
         """First time a bucket is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
-        ctx = self._fill(entries, bucket)
         n = len(entries)
         state = self._graphs.get(bucket)
         if state is not None and state["generation"] != self.buffers.generation:
             state = None                                   # a buffer moved: the old graph points at freed memory
             self._graphs.pop(bucket)
+        if state is not None and state["graph"] is not None:
+            self._fill_decode_block(entries, bucket, state["layout"])
+            state["graph"].replay()
+            ops.add_launches(state["kernels"])
+            return state["logits"][:n]
+        ctx = self._fill(entries, bucket)
         if state is None:
             self._graphs[bucket] = {"generation": None, "graph": None, "seen": 1}
             logits = self.model.forward(ctx)
@@ -340,7 +385,7 @@ class Runner:
             if self.buffers.generation != state["generation"]:
                 self._graphs.pop(bucket)                   # capture itself grew a buffer: run this step eagerly
                 return self.model.forward(ctx)[:n]
-            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
+            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before, layout=ctx.layout)
             ops.add_launches(-state["kernels"])            # capture launched nothing
         state["graph"].replay()
         ops.add_launches(state["kernels"])
