@@ -531,6 +531,202 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   }
 }
 
+
+// ---- CTA-pair variant (cta_group::2) for many tokens -------------------------------------------------------------------
+// Two CTAs of a cluster work on one 256-feature x 256-token tile: each holds its own 128 feature rows of the weights
+// and HALF of the token tile (128 rows) in shared memory; one thread of the leader CTA issues tcgen05.mma.cta_group::2
+// (M 256, N 256), which reads both CTAs' operands and fills 128 lanes x 256 columns of tensor memory in each CTA.
+// Per MMA each SM fetches 4 KB + 4 KB of operands instead of 4 KB + 8 KB, and per k stage TMA fills 32 KB instead of
+// 48 KB, which is what the single-CTA kernel runs out of (shared-memory bandwidth).
+// Barriers: full[s] lives in the leader and counts the bytes of both CTAs' loads (the loads carry .cta_group::2 so
+// that the peer's may signal the leader's barrier); empty[s] and acc_full[b] are signalled in both CTAs by a multicast
+// tcgen05.commit; acc_empty[b] lives in the leader and is arrived at by the 256 epilogue threads of the pair.
+// No TMA load uses multicast.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {     // arrives at `bar` in both CTAs of the pair
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                    void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
+                    int stages, int* __restrict__ error_flag) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int NACC = GATED ? 2 : 1;
+  constexpr int PN = 256;                                         // tokens of the pair's tile = MMA N
+  constexpr int NBUF = GATED ? 1 : 2;                             // accumulator sets in tensor memory
+  constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (PN / 2) * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES * NACC + BH_BYTES;
+  constexpr int TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;                            // [2]
+  uint64_t* acc_empty = acc_full + 2;                             // [2] (used in the leader)
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* s_abort = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int n_feat = GATED ? up_offset : N;
+  const int n_ft = (n_feat + 2 * BM - 1) / (2 * BM), n_tt = (T + PN - 1) / PN;
+  const int n_tiles = n_ft * n_tt;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                             // the peer's barriers exist before anyone signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  kf_pdl_trigger();
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs): own weight rows, own half of the token tile; bytes are counted in the leader --------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
+      kf_pdl_wait();
+      long it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        const int f0 = (tile % n_ft) * 2 * BM + (int)rank * BM;
+        const int t0 = (tile / n_ft) * PN + (int)rank * (PN / 2);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          if (it >= stages && !mbar_wait(&empty[s], (uint32_t)((it / stages) - 1) & 1)) {
+            atomicExch(error_flag, ERR_WAIT_EMPTY);
+            *s_abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          const uint32_t bar = map_to_rank(smem_u32(&full[s]), 0);
+          const int k = kb * BK;
+          tma_load_2d_pair(st, &tm_w, bar, k, f0);
+          if (GATED) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, up_offset + f0);
+          tma_load_2d_pair(st + A_BYTES * NACC, &tm_x, bar, k, t0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader only) ------------------------------------------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      long it = 0;
+      int ti = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++ti) {
+        const int buf = ti % NBUF;
+        if (ti >= NBUF && !mbar_wait(&acc_empty[buf], (uint32_t)((ti / NBUF) - 1) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem_base + buf * PN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          if (!mbar_wait(&full[s], (uint32_t)(it / stages) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          const uint64_t da = umma_desc(st);
+          const uint64_t db = umma_desc(st + A_BYTES * NACC);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+            umma_pair(acc, da + koff, db + koff, idesc, accumulate);
+            if (GATED) umma_pair(acc + PN, umma_desc(st + A_BYTES) + koff, db + koff, idesc, accumulate);
+          }
+          umma_commit_pair(&empty[s]);
+        }
+        umma_commit_pair(&acc_full[buf]);
+      }
+      if (!ok) { atomicExch(error_flag, ERR_WAIT_FULL); *s_abort = 1; }
+    }
+  } else {
+    // ---- epilogue (both CTAs): each drains its own 128 lanes ------------------------------------------------------------
+    kf_pdl_wait();
+    const int quarter = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int ti = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++ti) {
+      const int buf = ti % NBUF;
+      const int f0 = (tile % n_ft) * 2 * BM + (int)rank * BM, t0 = (tile / n_ft) * PN;
+      const int f = f0 + quarter * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (uint32_t)(ti / NBUF) & 1) || *s_abort) {
+        if (lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = lane_addr + buf * PN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < PN; c0 += 16) {
+        float v[16], u[16];
+        tmem_ld16(acc + c0, v);
+        if (GATED) tmem_ld16(acc + PN + c0, u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t < T && f < n_feat) {
+            float r;
+            if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
+            else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
+            else r = v[j];
+            if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
+            else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                             // no MMA of the pair is in flight, nobody signals a CTA that left
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -669,6 +865,55 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
   return KF_OK;
 }
 
+int g_pair = 1;
+
+template <int EPI>
+int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
+                int act, int up_offset, int* error_flag, cudaStream_t stream) {
+  constexpr int NACC = EPI == EPI_GATED ? 2 : 1;
+  constexpr int STAGE_BYTES = BM * BK * 2 * NACC + 128 * BK * 2;
+  int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  if (stages > 8) stages = 8;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
+  static bool configured = false;
+  static int n_sm = 148;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int n_feat = EPI == EPI_GATED ? up_offset : N;
+  const int n_tiles = kf_ceil_div(n_feat, 2 * BM) * kf_ceil_div(T, 256);
+  int pairs = n_sm / 2;
+  if (pairs > n_tiles) pairs = n_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (kf_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages, error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
 template <int EPI>
 int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
               int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t s) {
@@ -690,6 +935,7 @@ KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; 
 // 1: products over many tokens run the persistent kernel; 0: one tile per CTA for every shape.
 KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
+KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
@@ -730,6 +976,14 @@ KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T
   CUtensorMap tw, tx;
   if (!tensor_map(w, w_rows, K, BM, &tw) || !tensor_map(x, T, K, bn, &tx)) return KF_ERR_SETUP;
   const int up_offset = mode == EPI_GATED ? N : 0;
+  if (g_pair && splits == 1 && bn == 256) {
+    // many tokens: CTA pairs; every CTA loads boxes of 128 rows (its weight rows, its half of the token tile)
+    CUtensorMap txp;
+    if (!tensor_map(x, T, K, 128, &txp)) return KF_ERR_SETUP;
+    if (mode == EPI_F32) return launch_pair<EPI_F32>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+    if (mode == EPI_BF16) return launch_pair<EPI_BF16>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+    return launch_pair<EPI_GATED>(tw, txp, out, T, N, K, N, softcap, act, up_offset, error_flag, stream);
+  }
   if (g_persistent && splits == 1 && bn >= 128 && !(mode == EPI_GATED && bn == 256 && g_gated_wide)) {
     // many tokens: the persistent kernel with two accumulator sets.  The gated epilogue needs two accumulators per
     // set, so its token tile is 128; the token tensor map must match the tile.
