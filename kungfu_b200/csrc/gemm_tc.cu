@@ -29,7 +29,7 @@ constexpr int BM = 128;            // output features per tile (tensor-memory la
 constexpr int BK = 64;             // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long WAIT_LIMIT = 40L * 1000 * 1000;
+constexpr int WAIT_LIMIT = 40 * 1000 * 1000;
 
 enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_GATED = 2 };
 enum { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_ACC = 3 };
@@ -48,7 +48,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait: false if the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
-  for (long i = 0; i < WAIT_LIMIT; ++i) {
+  for (int i = 0; i < WAIT_LIMIT; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -210,26 +210,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN);
       bool ok = true;
+      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + Tile<BN>::A_BYTES * NACC);
+      const uint64_t du0 = umma_desc(smem + Tile<BN>::A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % stages;
-        if (!mbar_wait(&full[s], (i / stages) & 1)) {
+        if (!mbar_wait(&full[s], ph)) {
           atomicExch(error_flag, ERR_WAIT_FULL);
           s_flags[0] = 1;
           ok = false;
           break;
         }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-        const uint64_t da = umma_desc(st);
-        const uint64_t db = umma_desc(st + Tile<BN>::A_BYTES * NACC);
+        const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));   // descriptors hold address >> 4
+        const uint64_t da = da0 + so, db = db0 + so, du = du0 + so;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
+        for (int k = 0; k < BK / UMMA_K; ++k) {                                // 32 bytes per K = 16 step
           const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
-          const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);            // 32 bytes per K = 16 step
-          umma(tmem_base, da + koff, db + koff, idesc, accumulate);
-          if (GATED) umma(tmem_base + COLS, umma_desc(st + Tile<BN>::A_BYTES) + koff, db + koff, idesc, accumulate);
+          umma(tmem_base, da + 2 * k, db + 2 * k, idesc, accumulate);
+          if (GATED) umma(tmem_base + COLS, du + 2 * k, db + 2 * k, idesc, accumulate);
         }
         umma_commit(&empty[s]);                                               // frees the stage when the MMAs have read it
+        if (++s == stages) { s = 0; ph ^= 1; }
       }
       umma_commit(acc_full);                                                   // accumulator complete (or abandoned)
     }
@@ -432,13 +433,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
       kf_pdl_wait();
-      long it = 0;
+      int s = 0;                                                   // running stage and the parity its `empty` shows
+      uint32_t ph = 1;                                             // when free: 1 before the first pass (nothing to wait for)
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int f0 = (tile % n_ft) * BM, t0 = (tile / n_ft) * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it % stages);
-          if (it >= stages && !mbar_wait(&empty[s], (uint32_t)((it / stages) - 1) & 1)) {
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[s], ph)) {
             atomicExch(error_flag, ERR_WAIT_EMPTY);
             *s_abort = 1;
             ok = false;
@@ -450,6 +451,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
           tma_load_2d(st, &tm_w, &full[s], k, f0);
           if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[s], k, up_offset + f0);
           tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
+          if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -457,7 +459,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     // ---- MMA issuer ------------------------------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN);
-      long it = 0;
+      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + Tile<BN>::A_BYTES * NACC);
+      const uint64_t du0 = umma_desc(smem + Tile<BN>::A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
       int ti = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
@@ -465,21 +470,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         if (ti >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((ti >> 1) - 1) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + buf * ACC_COLS;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it % stages);
-          if (!mbar_wait(&full[s], (uint32_t)(it / stages) & 1)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          const uint64_t da = umma_desc(st);
-          const uint64_t db = umma_desc(st + Tile<BN>::A_BYTES * NACC);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+          const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));   // descriptors advance by address >> 4
+          const uint64_t da = da0 + so, db = db0 + so, du = du0 + so;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
-            umma(acc, da + koff, db + koff, idesc, accumulate);
-            if (GATED) umma(acc + COLS, umma_desc(st + Tile<BN>::A_BYTES) + koff, db + koff, idesc, accumulate);
+            umma(acc, da + 2 * k, db + 2 * k, idesc, accumulate);
+            if (GATED) umma(acc + COLS, du + 2 * k, db + 2 * k, idesc, accumulate);
           }
           umma_commit(&empty[s]);
+          if (++s == stages) { s = 0; ph ^= 1; }
         }
         umma_commit(&acc_full[buf]);
       }
@@ -625,14 +627,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
       kf_pdl_wait();
-      long it = 0;
+      int s = 0;
+      uint32_t ph = 1;                                             // parity of `empty` when the stage is free
       bool ok = true;
+      const uint32_t full0 = map_to_rank(smem_u32(&full[0]), 0);   // the leader's full[0], as a cluster address
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         const int f0 = (tile % n_ft) * 2 * BM + (int)rank * BM;
         const int t0 = (tile / n_ft) * PN + (int)rank * (PN / 2);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it % stages);
-          if (it >= stages && !mbar_wait(&empty[s], (uint32_t)((it / stages) - 1) & 1)) {
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[s], ph)) {
             atomicExch(error_flag, ERR_WAIT_EMPTY);
             *s_abort = 1;
             ok = false;
@@ -640,11 +643,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
-          const uint32_t bar = map_to_rank(smem_u32(&full[s]), 0);
+          const uint32_t bar = full0 + 8u * (uint32_t)s;
           const int k = kb * BK;
           tma_load_2d_pair(st, &tm_w, bar, k, f0);
           if (GATED) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, up_offset + f0);
           tma_load_2d_pair(st + A_BYTES * NACC, &tm_x, bar, k, t0);
+          if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -652,7 +656,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // ---- MMA issuer (leader only) ------------------------------------------------------------------------------------
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-      long it = 0;
+      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + A_BYTES * NACC), du0 = umma_desc(smem + A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
       int ti = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++ti) {
@@ -660,21 +666,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (ti >= NBUF && !mbar_wait(&acc_empty[buf], (uint32_t)((ti / NBUF) - 1) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + buf * PN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it % stages);
-          if (!mbar_wait(&full[s], (uint32_t)(it / stages) & 1)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          const uint64_t da = umma_desc(st);
-          const uint64_t db = umma_desc(st + A_BYTES * NACC);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+          const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));
+          const uint64_t da = da0 + so, db = db0 + so, du = du0 + so;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
-            umma_pair(acc, da + koff, db + koff, idesc, accumulate);
-            if (GATED) umma_pair(acc + PN, umma_desc(st + A_BYTES) + koff, db + koff, idesc, accumulate);
+            umma_pair(acc, da + 2 * k, db + 2 * k, idesc, accumulate);
+            if (GATED) umma_pair(acc + PN, du + 2 * k, db + 2 * k, idesc, accumulate);
           }
           umma_commit_pair(&empty[s]);
+          if (++s == stages) { s = 0; ph ^= 1; }
         }
         umma_commit_pair(&acc_full[buf]);
       }
