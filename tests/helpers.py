@@ -47,6 +47,18 @@ TINY_D = {
 }
 
 
+# Sizes at which every fast kernel runs: head size 128 (tcgen05 prompt attention, tensor-core decode attention),
+# rows of 512..1536 elements (tcgen05 products, CTA pairs for portions of more than 128 tokens), pages of 64.
+TINY_E = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
+    "intermediate_size": 1536, "vocab_size": 3000, "rope_theta": 10000.0, "sliding_window": 100,
+    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 128,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "hidden_activation": "gelu_pytorch_tanh",
+}
+
+
 def write_model(folder: str, cfg_dict: dict, seed: int, dtype=torch.bfloat16, matrix_scale: float = 1.0):
     """A model folder with random weights through the framework's random-weights mode."""
     from kungfu_b200.api import load_config

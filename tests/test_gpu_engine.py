@@ -69,6 +69,34 @@ def test_modes_match_plain(models, name, mode, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+def test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, dtype):
+    """Configuration E: sizes at which the tcgen05 products (pairs included), the tcgen05 prompt attention and the
+    tensor-core decode attention all run, with pages of 64, prompts longer than the window and than a CTA tile, and a
+    pool small enough that pages come back and are used again."""
+    from kungfu_b200 import api
+    cfg = helpers.TINY_E
+    cache = test_fast_kernel_sizes_match_plain.__dict__.setdefault("cache", {})
+    if "folder" not in cache:
+        folder = helpers.write_model(str(tmp_path_factory.mktemp("E") / "m"), cfg, seed=31, dtype=torch.bfloat16)
+        reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 700 + i) for i, n in enumerate([300, 70, 513, 129, 2])}
+        tensors = helpers.read_tensors(folder)
+        cache.update(folder=folder, reqs=reqs, ref={rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()})
+    folder, reqs, ref = cache["folder"], cache["reqs"], cache["ref"]
+    steps = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 32),
+             "chunks": lambda r: helpers.trace_chunks(r, sizes=(150, 2, 64, 131, 7, 300, 3)),
+             "mixed": lambda r: helpers.trace_mixed(r, seed=8)}[mode](reqs)
+    c, model = api.load_model(folder, dtype=dtype, device=DEV)
+    runner = api.make_runner(c, model, dtype=dtype, device=DEV, page_size=64,
+                             max_tokens=helpers.trace_max_tokens(steps, 64), max_requests=8, max_context=1024)
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _check(got, ref, TOL[dtype])
+    from kungfu_b200 import ops
+    ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_stored_in_32_bit_stay_so(tmp_path, dtype):
     """A file whose tensors are 32-bit floats: the bfloat16 engine keeps them 32-bit (and multiplies them with the
     generic product), the 32-bit engine uses them as they are."""
