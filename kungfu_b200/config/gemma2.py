@@ -88,9 +88,12 @@ class Gemma2Config:
         vocab = k.int("vocab_size", min=1)
         eps = k.float("rms_norm_eps")
         theta = k.float("rope_theta", 10000.0)
+        # a key that is present with the value null switches the feature off (no window, no cap); a key that is
+        # absent takes the reference's default (gemma2.rs:22-27)
+        no_window = "sliding_window" in raw and raw["sliding_window"] is None
         window = k.int("sliding_window", 4096, min=1)
-        attn_cap = k.float("attn_logit_softcapping", 50.0)
-        final_cap = k.float("final_logit_softcapping", 30.0)
+        attn_cap = 0.0 if ("attn_logit_softcapping" in raw and raw["attn_logit_softcapping"] is None) else k.float("attn_logit_softcapping", 50.0)
+        final_cap = 0.0 if ("final_logit_softcapping" in raw and raw["final_logit_softcapping"] is None) else k.float("final_logit_softcapping", 30.0)
         qpas = k.float("query_pre_attn_scalar", float(head_dim))
         max_pos = k.int("max_position_embeddings", 8192, min=1)
         tied = k.bool("tie_word_embeddings", True)
@@ -107,6 +110,8 @@ class Gemma2Config:
             period = k.int("sliding_window_pattern", 2, min=1)
             # reference: swa(l) = (l % n) < n - 1, so with n = 2 even layers slide (hparams.rs:541-554)
             types = [SLIDING if (l % period) < period - 1 else FULL for l in range(layers)]
+        if no_window:
+            types = [FULL] * layers
         if len(types) != layers:
             raise ConfigError(f"{where}: 'layer_types' has {len(types)} entries for {layers} layers")
         for t in types:

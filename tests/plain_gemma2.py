@@ -135,7 +135,7 @@ def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64) -> torch.Tens
                       tensors[p + "self_attn.v_proj.weight"], tensors[p + "self_attn.o_proj.weight"],
                       n_heads=nh, n_kv_heads=nkv, head_dim=d, scale=scale,
                       cap=cfg.get("attn_logit_softcapping", 50.0) or 0.0,
-                      window=cfg.get("sliding_window", 4096) if is_sliding(cfg, l) else None,
+                      window=(cfg.get("sliding_window", 4096) or None) if is_sliding(cfg, l) else None,
                       base=cfg.get("rope_theta", 10000.0))
         x = x + rms_norm(a, tensors[p + "post_attention_layernorm.weight"], eps)
         n = rms_norm(x, tensors[p + "pre_feedforward_layernorm.weight"], eps)

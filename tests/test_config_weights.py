@@ -70,6 +70,13 @@ def test_explicit_layer_types_and_zero_caps():
     assert cfg.window_of(0) is None and cfg.window_of(2) == 16 and cfg.final_logit_softcapping == 0.0
 
 
+def test_null_switches_a_feature_off():
+    raw = dict(helpers.TINY_A, attn_logit_softcapping=None, final_logit_softcapping=None, sliding_window=None)
+    cfg = Gemma2Config.from_dict(raw)
+    assert cfg.attn_logit_softcapping == 0.0 and cfg.final_logit_softcapping == 0.0
+    assert cfg.layer_types == (FULL, FULL) and cfg.window_of(0) is None
+
+
 def test_registry():
     assert "Gemma2ForCausalLM" in registry.names()
     with pytest.raises(registry.UnknownArchitecture) as e:
