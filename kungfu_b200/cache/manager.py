@@ -1,4 +1,4 @@
-"""The cache manager: pages of keys and values with a block table per request, and state slots.
+"""The cache manager: pages of keys and values with a block table for each request, and state slots.
 
 The reference keeps, per layer and per sequence slot, one contiguous ring sized at plan time
 (crates/kf-core/src/plan.rs:59-64, crates/kf-backend-cuda/src/exec.rs:1466-1498) and learns what a layer
@@ -17,16 +17,19 @@ declaration-driven shape but stores tokens in fixed-size pages:
 * every live request also owns one state slot (an index into dense per-request state arrays) for
   mixers that keep a state of fixed size; it is zeroed at admission.
 
-All bookkeeping is on the host; device memory is allocated once at construction.
+The bookkeeping itself (pools, tables, the host mirror of the tables that steps copy from) is native code,
+`csrc/host_runtime.cpp`; this class owns the device storage and turns its status codes into exceptions.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
 
 import numpy as np
 import torch
 
 from ..parts.base import FixedState, PagedKV
+
+_OK, _E_NOT_LIVE, _E_ALREADY_LIVE, _E_NO_SLOT, _E_OUT_OF_PAGES, _E_CONTEXT, _E_COMMIT, _E_PAGE, _E_INCONSISTENT = range(9)
 
 
 class OutOfPages(RuntimeError):
@@ -37,42 +40,101 @@ class CacheError(RuntimeError):
     """Misuse of the manager: unknown request, double release, a page freed twice."""
 
 
+_host = None
+
+
+def host_library():
+    """The native host runtime (compiled with the C++ compiler at first use)."""
+    global _host
+    if _host is None:
+        from ..csrc import build as _build
+        lib = ctypes.CDLL(_build.build_host())
+        lib.kf_pool_create.restype = ctypes.c_void_p
+        lib.kf_cache_create.restype = ctypes.c_void_p
+        lib.kf_cache_mirror.restype = ctypes.POINTER(ctypes.c_int)
+        for name in ("kf_pool_destroy", "kf_pool_take", "kf_pool_give_back", "kf_pool_n_free", "kf_pool_is_held",
+                     "kf_cache_destroy", "kf_cache_width", "kf_cache_n_live", "kf_cache_pool_n_free",
+                     "kf_cache_pool_is_held", "kf_cache_mirror", "kf_cache_check"):
+            getattr(lib, name).argtypes = [ctypes.c_void_p] + [ctypes.c_int] * {"kf_pool_give_back": 1, "kf_pool_is_held": 1,
+                                                                                  "kf_cache_pool_n_free": 1, "kf_cache_pool_is_held": 2,
+                                                                                  "kf_cache_mirror": 1}.get(name, 0)
+        i64 = ctypes.c_int64
+        for name, extra in (("kf_cache_contains", []), ("kf_cache_length", []), ("kf_cache_state_slot", []),
+                            ("kf_cache_add_request", []), ("kf_cache_cancel_reservation", []), ("kf_cache_release", []),
+                            ("kf_cache_reserve", [ctypes.c_int]), ("kf_cache_commit", [ctypes.c_int]),
+                            ("kf_cache_pages_needed", [ctypes.c_int, ctypes.c_void_p])):
+            getattr(lib, name).argtypes = [ctypes.c_void_p, i64] + extra
+        lib.kf_cache_table.argtypes = [ctypes.c_void_p, ctypes.c_int, i64, ctypes.c_void_p, ctypes.c_int]
+        lib.kf_step_layout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                       ctypes.c_int, ctypes.c_void_p]
+        lib.kf_step_fill.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_void_p,
+                                                                                               ctypes.c_void_p]
+        _host = lib
+    return _host
+
+
 class PagePool:
     """Page ids 0..n-1 with a free list; refuses to free a page twice or one it never gave out."""
 
     def __init__(self, n_pages: int):
         self.n_pages = int(n_pages)
-        self._free = list(range(self.n_pages - 1, -1, -1))      # pop() hands out low ids first
-        self._held = [False] * self.n_pages
+        self._lib = host_library()
+        self._h = ctypes.c_void_p(self._lib.kf_pool_create(self.n_pages))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.kf_pool_destroy(self._h)
+            self._h = None
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return self._lib.kf_pool_n_free(self._h)
 
     def take(self) -> int:
-        if not self._free:
+        p = self._lib.kf_pool_take(self._h)
+        if p < 0:
             raise OutOfPages("no free page")
-        p = self._free.pop()
-        self._held[p] = True
         return p
 
     def give_back(self, page: int) -> None:
-        if not (0 <= page < self.n_pages) or not self._held[page]:
+        if self._lib.kf_pool_give_back(self._h, int(page)) != _OK:
             raise CacheError(f"page {page} is not held")
-        self._held[page] = False
-        self._free.append(page)
 
     def held_pages(self) -> list[int]:
-        return [i for i, h in enumerate(self._held) if h]
+        return [i for i in range(self.n_pages) if self._lib.kf_pool_is_held(self._h, i)]
 
 
-@dataclass
+class _GroupPool:
+    """Read-only view of one group's pool inside the native manager."""
+
+    def __init__(self, manager, g: int, n_pages: int):
+        self._m, self._g, self.n_pages = manager, g, n_pages
+
+    @property
+    def n_free(self) -> int:
+        return self._m._lib.kf_cache_pool_n_free(self._m._h, self._g)
+
+    def held_pages(self) -> list[int]:
+        return [i for i in range(self.n_pages) if self._m._lib.kf_cache_pool_is_held(self._m._h, self._g, i)]
+
+
+class _GroupTables:
+    def __init__(self, manager, g: int):
+        self._m, self._g = manager, g
+
+    def __getitem__(self, request) -> list[int]:
+        return self._m.block_table(self._g, request)
+
+    def items(self):
+        return [(r, self._m.block_table(self._g, r)) for r in list(self._m._key)]
+
+
 class _Group:
-    window: int | None
-    pool: PagePool
-    slots: list[int]                                   # cache slots in this group
-    tables: dict = field(default_factory=dict)         # request -> list[int] (absolute page index -> page id or -1)
-    first_live: dict = field(default_factory=dict)     # request -> first page index still held
+    def __init__(self, manager, g: int, window: int | None, n_pages: int):
+        self.window = window
+        self.slots: list[int] = []                       # cache slots in this group
+        self.pool = _GroupPool(manager, g, n_pages)
+        self.tables = _GroupTables(manager, g)
 
 
 class PagedKVView:
@@ -102,10 +164,12 @@ class CacheManager:
         self.max_pages_per_request = -(-self.max_context // self.page_size)
         self.dtype, self.device = dtype, torch.device(device)
         self.needs = list(needs)
+        self._lib = host_library()
         self.groups: list[_Group] = []
         self._group_of_slot: dict[int, int] = {}
         self.storage: dict[int, torch.Tensor] = {}
         by_window: dict = {}
+        pool_sizes: list[int] = []
         for s, need in enumerate(self.needs):
             if isinstance(need, PagedKV):
                 g = by_window.get(need.window)
@@ -113,51 +177,66 @@ class CacheManager:
                     n = n_pages_windowed if (need.window is not None and n_pages_windowed is not None) else n_pages
                     g = len(self.groups)
                     by_window[need.window] = g
-                    self.groups.append(_Group(need.window, PagePool(n), []))
+                    self.groups.append(_Group(self, g, need.window, int(n)))
+                    pool_sizes.append(int(n))
                 self.groups[g].slots.append(s)
                 self._group_of_slot[s] = g
-                self.storage[s] = torch.zeros((self.groups[g].pool.n_pages, 2, need.n_kv_heads, self.page_size,
-                                               need.head_dim), dtype=dtype, device=self.device)
+                self.storage[s] = torch.zeros((pool_sizes[g], 2, need.n_kv_heads, self.page_size, need.head_dim),
+                                              dtype=dtype, device=self.device)
             elif isinstance(need, FixedState):
                 self.storage[s] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=self.device)
             elif need is not None:
                 raise TypeError(f"cache slot {s}: unknown state need {need!r}")
-        # host mirror of every block table, one row per state slot, ready to be copied into a step's integer block
-        self._table_np = [np.full((self.max_requests, (self.max_pages_per_request + 3) & ~3), -1, dtype=np.int32)
-                          for _ in self.groups]          # width padded to a multiple of 4, as the step's block is
-        self._length: dict = {}                 # request -> tokens committed
-        self._reserved: dict = {}               # request -> tokens reserved beyond the committed length
-        self._state_slot: dict = {}
-        self._free_state_slots = list(range(self.max_requests - 1, -1, -1))
+        G = len(self.groups)
+        windows = (ctypes.c_int * max(G, 1))(*[(-1 if g.window is None else int(g.window)) for g in self.groups])
+        sizes = (ctypes.c_int * max(G, 1))(*pool_sizes)
+        self._h = ctypes.c_void_p(self._lib.kf_cache_create(G, windows, sizes, self.page_size, self.max_requests,
+                                                            self.max_context))
+        self.table_width = self._lib.kf_cache_width(self._h)
+        # the native block-table mirrors, [max_requests, table_width] per group, as numpy views (no copy)
+        self._table_np = [np.ctypeslib.as_array(self._lib.kf_cache_mirror(self._h, g), shape=(self.max_requests, self.table_width))
+                          for g in range(G)]
+        self._key: dict = {}                    # request (any hashable) -> the 64-bit key the native side knows it by
+        self._next_key = 1
+        self._scratch = (ctypes.c_int * max(G, 1))()
 
-    # ---- requests ---------------------------------------------------------------------------------
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.kf_cache_destroy(self._h)
+            self._h = None
+
+    # ---- requests ---------------------------------------------------------------------------------------
+    def key_of(self, request) -> int:
+        try:
+            return self._key[request]
+        except KeyError:
+            raise CacheError(f"request {request!r} is not live") from None
+
     def __contains__(self, request) -> bool:
-        return request in self._length
+        return request in self._key
 
     @property
     def n_live(self) -> int:
-        return len(self._length)
+        return len(self._key)
 
     def length(self, request) -> int:
-        return self._length[request]
+        return self._lib.kf_cache_length(self._h, self.key_of(request))
 
     def state_slot(self, request) -> int:
-        return self._state_slot[request]
+        return self._lib.kf_cache_state_slot(self._h, self.key_of(request))
 
     def add_request(self, request) -> int:
         """Admit a request: gives it a state slot (zeroed) and empty block tables."""
-        if request in self._length:
+        if request in self._key:
             raise CacheError(f"request {request!r} is already live")
-        if not self._free_state_slots:
+        key = self._next_key
+        slot = self._lib.kf_cache_add_request(self._h, key)
+        if slot == -_E_NO_SLOT:
             raise CacheError(f"more than {self.max_requests} live requests")
-        slot = self._free_state_slots.pop()
-        self._state_slot[request] = slot
-        self._length[request] = 0
-        self._reserved[request] = 0
-        for gi, g in enumerate(self.groups):
-            g.tables[request] = []
-            g.first_live[request] = 0
-            self._table_np[gi][slot, :] = -1
+        if slot < 0:
+            raise CacheError(f"request {request!r}: native manager refused admission (code {-slot})")
+        self._next_key += 1
+        self._key[request] = key
         for s, need in enumerate(self.needs):
             if isinstance(need, FixedState):
                 self.storage[s][slot].zero_()
@@ -165,86 +244,49 @@ class CacheManager:
 
     def pages_needed(self, request, n_new: int) -> list[int]:
         """Pages each group must still take so the request can hold `n_new` more tokens."""
-        end = self._length[request] + self._reserved[request] + n_new
-        want = -(-end // self.page_size)
-        return [max(0, want - len(g.tables[request])) for g in self.groups]
+        self._lib.kf_cache_pages_needed(self._h, self.key_of(request), int(n_new), self._scratch)
+        return list(self._scratch[:len(self.groups)])
 
     def can_reserve(self, request, n_new: int) -> bool:
-        if self._length[request] + self._reserved[request] + n_new > self.max_context:
+        if self.length(request) + n_new > self.max_context:      # (reservations in flight are counted natively)
             return False
         return all(n <= g.pool.n_free for n, g in zip(self.pages_needed(request, n_new), self.groups))
 
     def reserve(self, request, n_new: int) -> None:
         """Take the pages for `n_new` more tokens in every group, or none at all (raises OutOfPages)."""
-        if request not in self._length:
-            raise CacheError(f"request {request!r} is not live")
-        if self._length[request] + self._reserved[request] + n_new > self.max_context:
+        rc = self._lib.kf_cache_reserve(self._h, self.key_of(request), int(n_new))
+        if rc == _E_CONTEXT:
             raise OutOfPages(f"request {request!r} would exceed the context of {self.max_context} tokens")
-        needed = self.pages_needed(request, n_new)
-        for n, g in zip(needed, self.groups):
-            if n > g.pool.n_free:
-                raise OutOfPages(f"group with window {g.window}: {n} pages needed, {g.pool.n_free} free")
-        slot = self._state_slot[request]
-        for gi, (n, g) in enumerate(zip(needed, self.groups)):
-            table = g.tables[request]
-            for _ in range(n):
-                page = g.pool.take()
-                self._table_np[gi][slot, len(table)] = page
-                table.append(page)
-        self._reserved[request] += n_new
+        if rc == _E_OUT_OF_PAGES:
+            raise OutOfPages(f"request {request!r}: {self.pages_needed(request, n_new)} pages needed, {self.free_pages()} free")
+        if rc != _OK:
+            raise CacheError(f"reserve for {request!r} failed (code {rc})")
 
     def cancel_reservation(self, request) -> None:
         """Give back the pages taken for tokens that were reserved but never committed."""
-        self._reserved[request] = 0
-        keep = -(-self._length[request] // self.page_size)
-        slot = self._state_slot[request]
-        for gi, g in enumerate(self.groups):
-            table = g.tables[request]
-            while len(table) > keep:
-                p = table.pop()
-                self._table_np[gi][slot, len(table)] = -1
-                if p >= 0:
-                    g.pool.give_back(p)
+        if self._lib.kf_cache_cancel_reservation(self._h, self.key_of(request)) != _OK:
+            raise CacheError(f"cancel_reservation for {request!r} failed")
 
     def commit(self, request, n_new: int) -> None:
         """The step that wrote `n_new` reserved tokens succeeded: advance, and give back slid-out pages."""
-        if n_new > self._reserved[request]:
-            raise CacheError(f"commit of {n_new} tokens, only {self._reserved[request]} reserved")
-        self._reserved[request] -= n_new
-        self._length[request] += n_new
-        n = self._length[request]
-        slot = self._state_slot[request]
-        for gi, g in enumerate(self.groups):
-            if g.window is None:
-                continue
-            # positions < n - window + 1 are out of reach of every later query
-            dead_pages = max(0, n - g.window + 1) // self.page_size
-            table = g.tables[request]
-            for i in range(g.first_live[request], min(dead_pages, len(table))):
-                if table[i] >= 0:
-                    g.pool.give_back(table[i])
-                    table[i] = -1
-                    self._table_np[gi][slot, i] = -1
-            g.first_live[request] = max(g.first_live[request], min(dead_pages, len(table)))
+        rc = self._lib.kf_cache_commit(self._h, self.key_of(request), int(n_new))
+        if rc == _E_COMMIT:
+            raise CacheError(f"commit of {n_new} tokens for {request!r}: more than were reserved")
+        if rc != _OK:
+            raise CacheError(f"commit for {request!r} failed (code {rc})")
 
     def release(self, request) -> None:
         """The request is finished (or preempted): everything it holds goes back."""
-        if request not in self._length:
-            raise CacheError(f"request {request!r} is not live")
-        slot = self._state_slot[request]
-        for gi, g in enumerate(self.groups):
-            for p in g.tables.pop(request):
-                if p >= 0:
-                    g.pool.give_back(p)
-            g.first_live.pop(request)
-            self._table_np[gi][slot, :] = -1
-        self._free_state_slots.append(self._state_slot.pop(request))
-        del self._length[request]
-        del self._reserved[request]
+        rc = self._lib.kf_cache_release(self._h, self.key_of(request))
+        del self._key[request]
+        if rc != _OK:
+            raise CacheError(f"release of {request!r} failed (code {rc})")
 
-    # ---- what a step needs ----------------------------------------------------------------------
+    # ---- what a step needs ----------------------------------------------------------------------------
     def block_table(self, group: int, request) -> list[int]:
-        return self.groups[group].tables[request]
+        buf = (ctypes.c_int * self.table_width)()
+        n = self._lib.kf_cache_table(self._h, group, self.key_of(request), buf, self.table_width)
+        return list(buf[:n])
 
     def table_rows(self, group: int, state_slots) -> np.ndarray:
         """Block-table rows (full width, -1 where no page is held) of the requests in the given state slots."""
@@ -261,7 +303,7 @@ class CacheManager:
             return FixedStateView(self.storage[cache_slot], writes)
         return None
 
-    # ---- accounting and self-check -----------------------------------------------------------------
+    # ---- accounting and self-check -----------------------------------------------------------------------
     def free_pages(self) -> list[int]:
         return [g.pool.n_free for g in self.groups]
 
@@ -274,21 +316,5 @@ class CacheManager:
 
     def check(self) -> None:
         """Every page is either free or in exactly one table; raises CacheError otherwise."""
-        for gi, g in enumerate(self.groups):
-            seen: dict[int, object] = {}
-            for req, table in g.tables.items():
-                for p in table:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise CacheError(f"group {gi}: page {p} held by {seen[p]!r} and {req!r}")
-                    seen[p] = req
-            for req, table in g.tables.items():
-                row = self._table_np[gi][self._state_slot[req]]
-                if list(row[:len(table)]) != list(table) or (row[len(table):] != -1).any():
-                    raise CacheError(f"group {gi}: host mirror of {req!r}'s block table is stale")
-            held = set(g.pool.held_pages())
-            if held != set(seen):
-                raise CacheError(f"group {gi}: pool holds {sorted(held)}, tables hold {sorted(seen)}")
-            if len(held) + g.pool.n_free != g.pool.n_pages:
-                raise CacheError(f"group {gi}: {len(held)} held + {g.pool.n_free} free != {g.pool.n_pages}")
+        if self._lib.kf_cache_check(self._h) != _OK:
+            raise CacheError("page accounting is inconsistent: a page is lost, held twice, or a table entry is stale")

@@ -145,5 +145,51 @@ def build(verbose: bool = False, jobs: int | None = None) -> str:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
+HOST_LIB_NAME = "libkungfu_b200_host.so"
+
+
+def build_host() -> str:
+    """Compile the host-side runtime (host_runtime.cpp: page pools, block tables, the step's integer block) with the
+    C++ compiler; it needs neither nvcc nor a GPU.  Returns the path of the shared library."""
+    out = build_dir()
+    src = os.path.join(HERE, "host_runtime.cpp")
+    tag = _file_hash(src, "host-v2")
+    lib = os.path.join(out, HOST_LIB_NAME)
+    stamp_path = os.path.join(out, "host_stamp")
+
+    def fresh() -> bool:
+        try:
+            with open(stamp_path) as fh:
+                return fh.read().strip() == tag and os.path.exists(lib)
+        except OSError:
+            return False
+
+    if fresh():
+        return lib
+    with open(os.path.join(out, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if fresh():
+                return lib
+            cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++") or shutil.which("clang++")
+            tmp = lib + f".tmp{os.getpid()}"
+            if cxx:
+                cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-static-libstdc++", "-static-libgcc",
+                       src, "-o", tmp]
+            else:
+                cmd = [find_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-x", "cu", src, "-o", tmp]
+            _say(f"compiling the host runtime with {cmd[0]}")
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise BuildError(f"compiling host_runtime.cpp failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp, lib)
+            with open(stamp_path, "w") as fh:
+                fh.write(tag)
+            return lib
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 if __name__ == "__main__":
+    print(build_host())
     print(build(verbose="-v" in sys.argv))

@@ -133,107 +133,62 @@ class Runner:
             slot[1].synchronize()
         return slot, self._meta_dev
 
-    def _fill(self, entries: Sequence[StepEntry], bucket: int | None = None) -> StepContext:
-        """Build the step's integer block.  With `bucket` (decode-only steps replayed from a CUDA graph) the
-        layout is the one of `bucket` single-row requests with full-width block tables, whatever the step holds:
-        rows beyond the real ones are padding (request index -1) that every kernel skips."""
+    _SECTIONS = ("tokens", "positions", "row_req", "logit_rows", "dec_rows", "pre_rows", "tile_row0", "tile_nrows",
+                 "wide_row0", "wide_nrows", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot")
+
+    def _build_block(self, entries: Sequence[StepEntry], bucket: int | None):
+        """The step's integer block, built by the native host runtime (`kf_step_layout` / `kf_step_fill` in
+        csrc/host_runtime.cpp) straight into a pinned staging block, and its copy to the device.
+        Returns (info, device block): info[0] total ints, [1] rows, [2] requests, [3] wanted rows, [4] table width,
+        [5] decode rows, [6] prompt rows, [7] tiles of 64, [8] tiles of 128, [9] longest kv length, [10] most rows of
+        one request, then the offset of every section."""
         cache = self.cache
-        ctx = StepContext(self)
-        n_real = len(entries)
-        B = len(entries) if bucket is None else bucket
-        T = sum(len(e.tokens) for e in entries) if bucket is None else bucket
-        n_out = sum(len(e.want) for e in entries) if bucket is None else bucket
-        G = len(cache.groups)
-        # table width: the most pages any request of this step addresses
-        width = 1
-        if bucket is None:
-            for e in entries:
-                n_after = cache.length(e.request) + len(e.tokens)
-                width = max(width, -(-n_after // cache.page_size))
+        lib = cache._lib
+        n = len(entries)
+        reqs = np.fromiter((cache.key_of(e.request) for e in entries), dtype=np.int64, count=n)
+        n_tokens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=n)
+        n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n)
+        if bucket is not None or int(n_tokens.max(initial=0)) == 1:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
         else:
-            width = cache.max_pages_per_request
-        width = _align4(width)
-        # layout (in ints); every section starts on a 16-byte boundary
-        o = 0
-        sec = {}
-        for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", max(n_out, 1)),
-                        ("dec_rows", T), ("pre_rows", T), ("tile_row0", T // 64 + B + 1), ("tile_nrows", T // 64 + B + 1),
-                        ("wide_row0", T // 128 + B + 1), ("wide_nrows", T // 128 + B + 1),
-                        ("req_row_start", B), ("req_n_rows", B), ("req_kv_len", B), ("req_state_slot", B)):
-            sec[name] = (o, n)
-            o += _align4(n)
-        for g in range(G):
-            sec[f"table{g}"] = (o, B * width)
-            o += _align4(B * width)
-        slot, dev = self._meta_buffers(o)
-        self.last_meta_ints = o
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]) if n else np.zeros(0, np.int32)
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(n_want.sum()))
+        info = np.zeros(32 + len(cache.groups), dtype=np.int32)
+        b = int(bucket or 0)
+        total = lib.kf_step_layout(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, n_want.ctypes.data, b, info.ctypes.data)
+        if total < 0:
+            raise StepError("a request of the step is not live")
+        slot, dev = self._meta_buffers(total)
+        self.last_meta_ints = total
         host = slot[0]
-        h = host.numpy()
-
-        def view(name):
-            a, n = sec[name]
-            return h[a:a + n]
-
-        tokens, positions, row_req = view("tokens"), view("positions"), view("row_req")
-        logit_rows = view("logit_rows")
-        logit_rows[:] = 0
-        if bucket is not None:
-            h[:o] = 0
-            row_req[n_real:] = -1
-            for g in range(G):
-                a, n = sec[f"table{g}"]
-                h[a:a + n] = -1
-        r = 0
-        k = 0
-        max_rows = 0
-        dec_rows, pre_rows, tiles, wide = [], [], [], []
-        max_kv = 0
-        for b, e in enumerate(entries):
-            n = len(e.tokens)
-            start = cache.length(e.request)
-            tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int64)
-            positions[r:r + n] = np.arange(start, start + n, dtype=np.int32)
-            row_req[r:r + n] = b
-            view("req_row_start")[b] = r
-            view("req_n_rows")[b] = n
-            view("req_kv_len")[b] = start + n
-            view("req_state_slot")[b] = cache.state_slot(e.request)
-            for w in e.want:
-                logit_rows[k] = r + int(w)
-                k += 1
-            for g in range(G):
-                a, _ = sec[f"table{g}"]
-                h[a + b * width: a + (b + 1) * width] = cache.table_rows(g, cache.state_slot(e.request))[:width]
-            max_rows = max(max_rows, n)
-            max_kv = max(max_kv, start + n)
-            if n == 1:
-                dec_rows.append(r)
-            else:
-                pre_rows.extend(range(r, r + n))
-                for a0 in range(0, n, 64):               # tiles of up to 64 consecutive rows of one request
-                    tiles.append((r + a0, min(64, n - a0)))
-                for a0 in range(0, n, 128):              # and of up to 128 rows, for the tcgen05 kernel
-                    wide.append((r + a0, min(128, n - a0)))
-            r += n
-        if bucket is not None:
-            dec_rows = list(range(bucket))
-            logit_rows[:] = np.arange(bucket, dtype=np.int32)
-            max_kv = cache.max_context                  # a graph's split plan must not depend on the step
-        view("dec_rows")[:len(dec_rows)] = dec_rows
-        view("pre_rows")[:len(pre_rows)] = pre_rows
-        if tiles:
-            view("tile_row0")[:len(tiles)] = [a for a, _ in tiles]
-            view("tile_nrows")[:len(tiles)] = [b for _, b in tiles]
-            view("wide_row0")[:len(wide)] = [a for a, _ in wide]
-            view("wide_nrows")[:len(wide)] = [b for _, b in wide]
-        dev[:o].copy_(host[:o], non_blocking=True)
+        rc = lib.kf_step_fill(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data, n_want.ctypes.data,
+                              wants.ctypes.data, b, info.ctypes.data, host.data_ptr())
+        if rc != 0:
+            raise StepError(f"building the step's integer block failed (code {rc})")
+        dev[:total].copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
             if slot[1] is None:
                 slot[1] = torch.cuda.Event()
             slot[1].record()
+        return info, dev, host
+
+    def _fill(self, entries: Sequence[StepEntry], bucket: int | None = None) -> StepContext:
+        """Build the step's integer block and the context that names its sections.  With `bucket` (decode-only
+        steps replayed from a CUDA graph) the layout is the one of `bucket` single-row requests with full-width
+        block tables, whatever the step holds: rows beyond the real ones are padding (request index -1) that every
+        kernel skips."""
+        info, dev, host = self._build_block(entries, bucket)
+        ctx = StepContext(self)
+        total, T, B, n_out, width, n_dec, n_pre, n_tiles, n_wide, max_kv, max_rows = (int(v) for v in info[:11])
+        off = info[11:]
+        h = host.numpy()
+        sizes = {"tokens": T, "positions": T, "row_req": T, "logit_rows": max(n_out, 1), "dec_rows": T, "pre_rows": T,
+                 "tile_row0": T // 64 + B + 1, "tile_nrows": T // 64 + B + 1, "wide_row0": T // 128 + B + 1,
+                 "wide_nrows": T // 128 + B + 1, "req_row_start": B, "req_n_rows": B, "req_kv_len": B, "req_state_slot": B}
+        where = {name: (int(off[i]), sizes[name]) for i, name in enumerate(self._SECTIONS)}
 
         def dview(name):
-            a, n = sec[name]
+            a, n = where[name]
             return dev[a:a + n]
 
         ctx.n_rows, ctx.n_reqs, ctx.n_logits = T, B, n_out
@@ -241,60 +196,19 @@ class Runner:
         ctx.decode_only = max_rows == 1
         ctx.tokens, ctx.positions, ctx.row_req = dview("tokens"), dview("positions"), dview("row_req")
         ctx.logit_rows = dview("logit_rows")[:n_out] if n_out else dview("logit_rows")[:0]
-        ctx.dec_rows, ctx.n_dec_rows = dview("dec_rows"), len(dec_rows)
-        ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), len(pre_rows)
+        ctx.dec_rows, ctx.n_dec_rows = dview("dec_rows"), n_dec
+        ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), n_pre
         ctx.max_kv_len = max_kv
-        ctx.tile_row0, ctx.tile_nrows, ctx.n_tiles = dview("tile_row0"), dview("tile_nrows"), len(tiles)
-        ctx.wide_row0, ctx.wide_nrows, ctx.n_wide = dview("wide_row0"), dview("wide_nrows"), len(wide)
+        ctx.tile_row0, ctx.tile_nrows, ctx.n_tiles = dview("tile_row0"), dview("tile_nrows"), n_tiles
+        ctx.wide_row0, ctx.wide_nrows, ctx.n_wide = dview("wide_row0"), dview("wide_nrows"), n_wide
         ctx.req_row_start, ctx.req_n_rows = dview("req_row_start"), dview("req_n_rows")
         ctx.req_kv_len, ctx.req_state_slot = dview("req_kv_len"), dview("req_state_slot")
-        ctx.block_tables = [dview(f"table{g}").view(B, width) for g in range(G)]
-        ctx.host = {name: view(name).copy() for name in ("positions", "row_req", "req_row_start", "req_n_rows",
-                                                         "req_kv_len", "req_state_slot")}
-        ctx.layout = (sec, o, width)
+        n_sec = len(self._SECTIONS)
+        ctx.block_tables = [dev[int(off[n_sec + g]):int(off[n_sec + g]) + B * width].view(B, width)
+                            for g in range(len(self.cache.groups))]
+        ctx.host = {name: h[where[name][0]:where[name][0] + where[name][1]].copy()
+                    for name in ("positions", "row_req", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot")}
         return ctx
-
-    def _fill_decode_block(self, entries, bucket: int, layout) -> None:
-        """The integer block of a decode-only step whose graph already exists: same layout as `_fill(entries, bucket)`
-        builds, written with a few vector operations and copied; no context object is needed for a replay."""
-        cache = self.cache
-        sec, o, width = layout
-        n = len(entries)
-        slot, dev = self._meta_buffers(o)
-        self.last_meta_ints = o
-        host = slot[0]
-        h = host.numpy()
-        lengths = np.fromiter((cache._length[e.request] for e in entries), dtype=np.int32, count=n)
-        slots = np.fromiter((cache._state_slot[e.request] for e in entries), dtype=np.int64, count=n)
-        h[:o] = 0
-
-        def put(name, values, fill=None):
-            a, m = sec[name]
-            if fill is not None:
-                h[a:a + m] = fill
-            h[a:a + n] = values
-
-        put("tokens", np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n))
-        put("positions", lengths)
-        put("row_req", np.arange(n, dtype=np.int32), fill=-1)
-        put("req_row_start", np.arange(n, dtype=np.int32))
-        put("req_n_rows", 1)
-        put("req_kv_len", lengths + 1)
-        put("req_state_slot", slots)
-        ar = np.arange(bucket, dtype=np.int32)
-        a, m = sec["logit_rows"]
-        h[a:a + bucket] = ar
-        a, m = sec["dec_rows"]
-        h[a:a + bucket] = ar
-        for g in range(len(cache.groups)):
-            a, m = sec[f"table{g}"]
-            block = h[a:a + m].reshape(bucket, width)
-            block[:] = -1
-            block[:n] = cache.table_rows(g, slots)[:, :width]
-        dev[:o].copy_(host[:o], non_blocking=True)
-        if slot[1] is None:
-            slot[1] = torch.cuda.Event()
-        slot[1].record()
 
     # ---- the step -------------------------------------------------------------------------------------
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -366,7 +280,7 @@ class Runner:
             state = None                                   # a buffer moved: the old graph points at freed memory
             self._graphs.pop(bucket)
         if state is not None and state["graph"] is not None:
-            self._fill_decode_block(entries, bucket, state["layout"])
+            self._build_block(entries, bucket)            # same layout as at capture; a replay needs no context object
             state["graph"].replay()
             ops.add_launches(state["kernels"])
             return state["logits"][:n]
@@ -385,7 +299,7 @@ class Runner:
             if self.buffers.generation != state["generation"]:
                 self._graphs.pop(bucket)                   # capture itself grew a buffer: run this step eagerly
                 return self.model.forward(ctx)[:n]
-            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before, layout=ctx.layout)
+            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
             ops.add_launches(-state["kernels"])            # capture launched nothing
         state["graph"].replay()
         ops.add_launches(state["kernels"])
