@@ -172,7 +172,8 @@ def cmd_score(args) -> int:
     prefix = len(ids) if args.prefix is None else max(1, min(args.prefix, len(ids)))
     runner.cache.add_request("score")
     rows = []
-    chunks = [ids[i:i + args.batch] for i in range(0, prefix, args.batch)] + [[t] for t in ids[prefix:]]
+    head = ids[:prefix]
+    chunks = [head[i:i + args.batch] for i in range(0, prefix, args.batch)] + [[t] for t in ids[prefix:]]
     eos = set(getattr(eng.cfg, "eos_token_id", ()) or ())
     for chunk in chunks:
         logits = runner.step([StepEntry("score", chunk, list(range(len(chunk))))]).clone()
