@@ -226,6 +226,26 @@ def cmd_bench(args) -> int:
         m = sum(x) / len(x)
         return m, math.sqrt(sum((v - m) ** 2 for v in x) / len(x))
 
+    if args.trace:
+        # one more prompt pass and one more decode step with every kernel timed (CUDA events, launches serialised)
+        from . import ops
+        runner.cache.add_request("trace")
+        ops.trace_begin()
+        runner.step([StepEntry("trace", toks[:min(args.pp, args.batch)], [0])])
+        pp_trace = ops.trace_end()
+        ops.trace_begin()
+        runner.step([StepEntry("trace", [toks[0]], [0])])
+        tg_trace = ops.trace_end()
+        runner.cache.release("trace")
+        for title, rec in (("prompt pass", pp_trace), ("decode step", tg_trace)):
+            agg: dict = {}
+            for name, ms in rec:
+                n, t = agg.get(name, (0, 0.0))
+                agg[name] = (n + 1, t + ms)
+            total = sum(t for _, t in agg.values())
+            print(f"kernel times, {title} ({len(rec)} operations, {total:.3f} ms):", file=sys.stderr)
+            for name, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+                print(f"  {name:18s} x{n:<4d} {t * 1e3:10.1f} us  {100 * t / total:5.1f} %", file=sys.stderr)
     print("| model | dtype | test | t/s |")
     print("|---|---|---|---|")
     for name, rates in ((f"pp{args.pp}", pp_rates), (f"tg{args.tg}", tg_rates)):
@@ -282,6 +302,7 @@ def main(argv=None) -> int:
     p.add_argument("--pp", type=int, default=512)
     p.add_argument("--tg", type=int, default=128)
     p.add_argument("--reps", type=int, default=3)
+    p.add_argument("--trace", action="store_true", help="also print per-kernel times of one prompt pass and one decode step")
     _common(p)
     p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("random-weights", help="write a model folder from a config.json and a seed")

@@ -263,6 +263,9 @@ class Runner:
         """The padded batch size whose graph runs this step, or None if the step is not a pure decode step."""
         if not self.cuda_graphs or self.device.type != "cuda" or not self._graph_safe:
             return None
+        from .. import ops
+        if ops.tracing():                                  # per-kernel timing needs eager launches
+            return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None
         b = 1

@@ -109,11 +109,41 @@ def _f(x: float):
     return ctypes.c_float(x)
 
 
+# ---- per-kernel timing (the reference's KF_TRACE_KERNELS, crates/kf-backend-cuda/src/exec.rs:2836-2853) -----------
+_trace: list | None = None
+
+
+def trace_begin() -> None:
+    """Start timing every operation of this module with CUDA events (steps then run eagerly, not from graphs)."""
+    global _trace
+    _trace = []
+
+
+def trace_end() -> list[tuple[str, float]]:
+    """Stop timing; returns (operation, milliseconds) in launch order."""
+    global _trace
+    rec, _trace = _trace or [], None
+    if rec:
+        torch.cuda.synchronize()
+    return [(name, e0.elapsed_time(e1)) for name, e0, e1 in rec]
+
+
+def tracing() -> bool:
+    return _trace is not None
+
+
 def _dispatch(name):
     def deco(fn):
         def wrapper(*a, **k):
             if _override is not None:
                 return getattr(_override, name)(*a, **k)
+            if _trace is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = fn(*a, **k)
+                e1.record()
+                _trace.append((name, e0, e1))
+                return out
             return fn(*a, **k)
         wrapper.__name__ = name
         wrapper.__doc__ = fn.__doc__

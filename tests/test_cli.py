@@ -77,9 +77,10 @@ def test_generate_score_bench(model_dir):
     p = run(["score", "--model", model_dir, "--ids", json.dumps(ids), "--topk", "3", "--dtype", "float32", "--ctx", "128"])
     top3 = json.loads(p.stdout.strip().split("\n")[-1])["predictions"]
     assert [t[0] for t in top3] == want and all(len(t) == 3 for t in top3)
-    p = run(["bench", "--model", model_dir, "--pp", "32", "--tg", "8", "--reps", "2", "--ctx", "128", "--batch", "16"])
+    p = run(["bench", "--model", model_dir, "--pp", "32", "--tg", "8", "--reps", "2", "--ctx", "128", "--batch", "16", "--trace"])
     assert p.returncode == 0, p.stderr[-2000:]
     assert "pp32" in p.stdout and "tg8" in p.stdout
+    assert "kernel times, decode step" in p.stderr and "paged_attention" in p.stderr
     # temperature sampling with events
     p = run(["generate", "--model", model_dir, "--ids", json.dumps(ids), "--max-tokens", "5", "--temperature", "0.8", "--seed", "3",
              "--ctx", "128", "--events"])
