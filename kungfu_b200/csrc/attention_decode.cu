@@ -57,6 +57,74 @@ __device__ __forceinline__ void merge1(float& m, float& l, float* a, float m2, f
   m = mn;
 }
 
+
+// Partial record of one (row, head, split): acc[D], m, l and two floats of padding, so that records start on 16 bytes.
+#define KF_PSTRIDE(D) ((D) + 4)
+constexpr int MERGE_MAX_HEADS = 16;
+constexpr int MERGE_MAX_SPLITS = 64;
+
+// The block that arrived last merges the splits of its heads.  Loads from L2 are the whole cost here, so they are
+// made independent of one another: first every (head, split) pair's maximum is fetched by a thread of its own, a
+// warp per head turns them into weights exp(m_s - m) / l in shared memory, and then every thread sums four
+// elements over the splits with eight 16-byte loads in flight.  Splits are summed in index order.
+template <int D, bool BASE2>
+__device__ __forceinline__ void merge_splits(const float* __restrict__ partial, size_t first_record, int n_heads,
+                                             int n_splits, __nv_bfloat16* __restrict__ o_first) {
+  constexpr int PS = KF_PSTRIDE(D);
+  __shared__ float s_w[MERGE_MAX_HEADS][MERGE_MAX_SPLITS];
+  const float* rec0 = partial + first_record * PS;              // record (h, s) at rec0 + (h * n_splits + s) * PS
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
+  for (int idx = tid; idx < n_heads * n_splits; idx += blockDim.x) {
+    const int h = idx / n_splits, sp = idx - h * n_splits;
+    s_w[h][sp] = __ldcg(rec0 + (size_t)idx * PS + D);
+  }
+  __syncthreads();
+  for (int h = warp; h < n_heads; h += n_warps) {
+    float m = -INFINITY;
+    for (int sp = lane; sp < n_splits; sp += 32) m = fmaxf(m, s_w[h][sp]);
+    m = kf_warp_max(m);
+    float l = 0.f;
+    for (int sp = lane; sp < n_splits; sp += 32) {
+      const float ms = s_w[h][sp];
+      const float c = (ms == -INFINITY) ? 0.f : (BASE2 ? exp2f(ms - m) : expf(ms - m));
+      l += __ldcg(rec0 + ((size_t)h * n_splits + sp) * PS + D + 1) * c;
+      s_w[h][sp] = c;
+    }
+    // the sum over splits in a fixed order: lanes hold interleaved splits, the butterfly adds them the same way each time
+    l = kf_warp_sum(l);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __syncwarp();
+    for (int sp = lane; sp < n_splits; sp += 32) s_w[h][sp] *= inv;
+  }
+  __syncthreads();
+  for (int e = tid; e < n_heads * (D / 4); e += blockDim.x) {
+    const int h = e / (D / 4), i4 = e - h * (D / 4);
+    const float* src = rec0 + (size_t)h * n_splits * PS + i4 * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    int sp = 0;
+    for (; sp + 8 <= n_splits; sp += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * PS));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float c = s_w[h][sp + u];
+        a.x += v[u].x * c; a.y += v[u].y * c; a.z += v[u].z * c; a.w += v[u].w * c;
+      }
+    }
+    for (; sp < n_splits; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * PS));
+      const float c = s_w[h][sp];
+      a.x += v.x * c; a.y += v.y * c; a.z += v.z * c; a.w += v.w * c;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(o_first + (size_t)h * D + i4 * 4) = packed;
+  }
+}
+
 template <int D, int HT>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
@@ -68,7 +136,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   kf_pdl_wait();
   constexpr int LPK = D / 8;                 // lanes per key
   constexpr int KPW = 32 / LPK;              // keys per warp and iteration
-  constexpr int PSTRIDE = D + 2;             // partial record: acc[D], m, l
+  constexpr int PSTRIDE = KF_PSTRIDE(D);
   __shared__ float sm_acc[DEC_WARPS][HT][D];
   __shared__ float sm_ml[DEC_WARPS][HT][2];
   __shared__ int s_last;
@@ -239,20 +307,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int e = threadIdx.x; e < h_count * D; e += blockDim.x) {
-    const int h = e / D, i = e - h * D;
-    const float* rec0 = partial + (((size_t)t * nh + h_first + h) * n_splits) * PSTRIDE;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __ldcg(rec0 + (size_t)s * PSTRIDE + D));
-    float l = 0.f, a = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = __ldcg(rec0 + (size_t)s * PSTRIDE + D);
-      const float c = (ms == -INFINITY) ? 0.f : expf(ms - m);
-      l += __ldcg(rec0 + (size_t)s * PSTRIDE + D + 1) * c;
-      a += __ldcg(rec0 + (size_t)s * PSTRIDE + i) * c;
-    }
-    orow[(size_t)(h_first + h) * D + i] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
-  }
+  merge_splits<D, false>(partial, ((size_t)t * nh + h_first) * n_splits, h_count, n_splits, orow + (size_t)h_first * D);
   if (threadIdx.x == 0) counters[cidx] = 0;
 }
 
@@ -280,7 +335,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   constexpr int CH = D / 8;
   constexpr int NT_O = D / 8;
   constexpr int KS_QK = D / 16;
-  constexpr int PSTRIDE = D + 2;
+  constexpr int PSTRIDE = KF_PSTRIDE(D);
   constexpr int TILE = DM_KEYS * D;                               // elements of one key (or value) tile
   extern __shared__ __align__(128) uint8_t dm_smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dm_smem);  // [16][D]
@@ -493,21 +548,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   if (tid == 0) s_last = (atomicAdd(&counters[cidx], 1) == n_splits - 1);
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
-  for (int e = tid; e < G * D; e += blockDim.x) {                  // maxima here are base-2 scaled
-    const int h = e / D, i = e - h * D;
-    const float* rec0 = partial + (((size_t)t * nh + h_first + h) * n_splits) * PSTRIDE;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __ldcg(rec0 + (size_t)s * PSTRIDE + D));
-    float l = 0.f, a = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = __ldcg(rec0 + (size_t)s * PSTRIDE + D);
-      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      l += __ldcg(rec0 + (size_t)s * PSTRIDE + D + 1) * c;
-      a += __ldcg(rec0 + (size_t)s * PSTRIDE + i) * c;
-    }
-    orow[(size_t)(h_first + h) * D + i] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
-  }
+  __threadfence();                                               // maxima here are base-2 scaled
+  merge_splits<D, true>(partial, ((size_t)t * nh + h_first) * n_splits, G, n_splits, orow + (size_t)h_first * D);
   if (tid == 0) counters[cidx] = 0;
 }
 
@@ -593,7 +635,7 @@ KF_API int kf_attention_decode_plan(int n_items, int nh, int nkv, int d, int max
 }
 
 // q, out: [T, nh*d] bfloat16.  items: rows of the step this launch handles (null = rows 0..n_items-1).
-// partial: n_rows_total * nh * splits * (d + 2) floats; counters: n_items * nkv * ceil(G/ht) zeroed ints (left zero).
+// partial: n_rows_total * nh * splits * (d + 4) floats; counters: n_items * nkv * ceil(G/ht) zeroed ints (left zero).
 KF_API int kf_attention_decode(const void* q, void* out, const void* pages, const int* items, int n_items,
                                const int* positions, const int* row_req, const int* table, int table_stride,
                                int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int ht,
@@ -601,6 +643,7 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
   if (n_items <= 0) return KF_OK;
   if (nkv < 1 || nh % nkv != 0 || page_size < 1 || n_splits < 1) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
+  if (n_splits > MERGE_MAX_SPLITS || ht > MERGE_MAX_HEADS) return KF_ERR_SIZE;
   if (ht == 0) {                                     // tensor-core variant
     if (nh / nkv > 16) return KF_ERR_SIZE;
 #define KF_MMA_ARGS q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
@@ -674,9 +717,9 @@ KF_API int kf_attention_decode_static(const void* q, void* out, const void* page
   int ht = 1, splits = 1;
   kf_attention_decode_plan(n_rows, nh, nkv, d, max_keys, &ht, &splits);
   const long n_counters = (long)n_rows * nkv * kf_ceil_div(nh / nkv, ht);
-  const long n_partial = (long)n_rows * nh * splits * (d + 2);
+  const long n_partial = (long)n_rows * nh * splits * (d + 4);
   if (n_counters > KF_DECODE_STATIC_MAX_COUNTERS || n_partial > KF_DECODE_STATIC_MAX_PARTIAL_FLOATS) {
-    kf_record_message("kf_attention_decode_static: rows * heads * splits * (head_dim + 2) exceeds the built-in scratch");
+    kf_record_message("kf_attention_decode_static: rows * heads * splits * (head_dim + 4) exceeds the built-in scratch");
     return KF_ERR_SIZE;
   }
   // The arrays keep what the last call left; the counters must start at zero.

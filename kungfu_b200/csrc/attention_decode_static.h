@@ -10,7 +10,7 @@
 //     KF_DECODE_STATIC_MAX_PARTIAL_FLOATS floats (8 MiB) and KF_DECODE_STATIC_MAX_COUNTERS ints (16 KiB).
 //
 // Every GPU that loads the library holds these arrays until the process exits.  A call whose
-// rows * heads * splits * (head_dim + 2) or rows * kv_heads * head_groups exceeds them is refused with
+// rows * heads * splits * (head_dim + 4) or rows * kv_heads * head_groups exceeds them is refused with
 // KF_ERR_SIZE (2) and touches nothing.  The function calls no cudaMalloc, cudaFree or other allocating routine.
 //
 // Set-up: the first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, once per

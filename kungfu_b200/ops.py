@@ -146,6 +146,7 @@ def _dispatch(name):
                 return out
             return fn(*a, **k)
         wrapper.__name__ = name
+        wrapper.__wrapped__ = fn
         wrapper.__doc__ = fn.__doc__
         return wrapper
     return deco
@@ -334,7 +335,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         if n_counters > sc["counters"].numel():
             rest, n_rest = None, T
         else:
-            partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 2)) if splits.value > 1 else None
+            partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 4)) if splits.value > 1 else None
             items = None if n_dec == T else ctx.dec_rows
             _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common[:8], *common[8:], ht.value,
                                            splits.value, _p(partial), _p(sc["counters"]), _stream()), "attention (decode)")
