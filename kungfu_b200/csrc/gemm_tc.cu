@@ -119,6 +119,144 @@ __device__ __forceinline__ float act_fast(float x, int act) {
   return kf_act(x, act);
 }
 
+// The activation operand can come from a norm that is still pending: the previous product left its 32-bit output
+// `branch`, and the rows this product reads are  n = rmsnorm(y; w_next)  with  y = res_in + rmsnorm(branch; w_post).
+// Then every CTA computes the rows itself (the sums need whole rows, a few KB each) and writes its K range of n
+// straight into shared memory in the layout the tensor core reads; the CTAs of feature tile 0 also store their K range
+// of y to `res_out` (a buffer other than res_in: other CTAs still read res_in).  This saves the norm's own kernel.
+struct NormIn {
+  const float* branch;
+  const float* res_in;
+  float* res_out;
+  const __nv_bfloat16* w_post;
+  const __nv_bfloat16* w_next;
+  float eps_post, eps_next;
+  int plus_post, plus_next;
+};
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& r, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(p[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+
+// Called by the 128 epilogue threads (w4 = 0..3 is the warp among them, tid = w4 * 32 + lane); red: 2 * 4 * BN floats
+// of shared memory.  xs: [nkb][BN rows][128 bytes], 128-byte swizzle.  Work is split by columns, every thread walks
+// all rows of its columns with the rows' loads independent of one another, so the latency of L2 is paid once per
+// pass and not once per row: pass 1 sums branch^2, pass 2 sums y^2, pass 3 writes this CTA's K range.
+template <int BN>
+__device__ __forceinline__ void normed_rows_to_smem(const NormIn& ni, int T, int K, int kb_begin, int nkb, uint8_t* xs,
+                                                    bool write_residual, int w4, int lane, float* red) {
+  const int tid = w4 * 32 + lane;
+  const int n4 = K >> 2;                                          // groups of 4 columns
+  const float gp = ni.plus_post ? 1.f : 0.f, gn = ni.plus_next ? 1.f : 0.f;
+  const float inv_k = 1.f / (float)K;
+  float acc[BN];
+  auto block_sums = [&](float* slot) {                            // acc[r] summed over the 128 threads -> acc[r]
+#pragma unroll
+    for (int r = 0; r < BN; ++r) acc[r] = kf_warp_sum(acc[r]);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < BN; ++r) slot[w4 * BN + r] = acc[r];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+    for (int r = 0; r < BN; ++r) acc[r] = slot[r] + slot[BN + r] + slot[2 * BN + r] + slot[3 * BN + r];
+  };
+  // ---- pass 1: sum of squares of the branch rows ---------------------------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < BN; ++r) acc[r] = 0.f;
+  for (int c = tid; c < n4; c += 128) {
+    float4 v[BN];
+#pragma unroll
+    for (int r = 0; r < BN; ++r)
+      v[r] = r < T ? *reinterpret_cast<const float4*>(ni.branch + (size_t)r * K + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < BN; ++r) acc[r] += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
+  }
+  block_sums(red);
+  float inv1[BN];
+#pragma unroll
+  for (int r = 0; r < BN; ++r) inv1[r] = 1.f / sqrtf(acc[r] * inv_k + ni.eps_post);
+  // ---- pass 2: sum of squares of y = residual + branch * inv1 * g ------------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < BN; ++r) acc[r] = 0.f;
+  for (int c = tid; c < n4; c += 128) {
+    const uint2 gw = *reinterpret_cast<const uint2*>(ni.w_post + c * 4);
+    const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw.x));
+    const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw.y));
+    float4 va[BN], vx[BN];
+#pragma unroll
+    for (int r = 0; r < BN; ++r) {
+      va[r] = r < T ? *reinterpret_cast<const float4*>(ni.branch + (size_t)r * K + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      vx[r] = r < T ? *reinterpret_cast<const float4*>(ni.res_in + (size_t)r * K + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int r = 0; r < BN; ++r) {
+      const float y0 = vx[r].x + va[r].x * inv1[r] * (g01.x + gp), y1 = vx[r].y + va[r].y * inv1[r] * (g01.y + gp);
+      const float y2 = vx[r].z + va[r].z * inv1[r] * (g23.x + gp), y3 = vx[r].w + va[r].w * inv1[r] * (g23.y + gp);
+      acc[r] += y0 * y0 + y1 * y1 + y2 * y2 + y3 * y3;
+    }
+  }
+  block_sums(red + 4 * BN);
+  float inv2[BN];
+#pragma unroll
+  for (int r = 0; r < BN; ++r) inv2[r] = 1.f / sqrtf(acc[r] * inv_k + ni.eps_next);
+  // ---- pass 3: this CTA's K range, 8 columns (16 bytes of bfloat16) at a time ----------------------------------------
+  for (int cc = tid; cc < nkb * 8; cc += 128) {
+    const int c8 = kb_begin * 8 + cc;
+    const bool in_k = c8 * 8 < K;
+    float g1[8], g2[8];
+    if (in_k) {
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(ni.w_post + c8 * 8), g1);
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(ni.w_next + c8 * 8), g2);
+    }
+    uint8_t* tile = xs + (size_t)(cc >> 3) * (BN * 128);
+#pragma unroll
+    for (int r0 = 0; r0 < BN; r0 += 4) {                           // four rows' loads in flight
+      float4 a0[4], a1[4], x0[4], x1[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = r0 + q;
+        if (in_k && r < T) {
+          const float* a = ni.branch + (size_t)r * K + c8 * 8;
+          const float* x = ni.res_in + (size_t)r * K + c8 * 8;
+          a0[q] = *reinterpret_cast<const float4*>(a); a1[q] = *reinterpret_cast<const float4*>(a + 4);
+          x0[q] = *reinterpret_cast<const float4*>(x); x1[q] = *reinterpret_cast<const float4*>(x + 4);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = r0 + q;
+        uint4 packed = make_uint4(0, 0, 0, 0);
+        if (in_k && r < T) {
+          const float av[8] = {a0[q].x, a0[q].y, a0[q].z, a0[q].w, a1[q].x, a1[q].y, a1[q].z, a1[q].w};
+          const float xv[8] = {x0[q].x, x0[q].y, x0[q].z, x0[q].w, x1[q].x, x1[q].y, x1[q].z, x1[q].w};
+          float y[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] = xv[i] + av[i] * inv1[r] * (g1[i] + gp);
+          if (write_residual) {
+            float* o = ni.res_out + (size_t)r * K + c8 * 8;
+            *reinterpret_cast<float4*>(o) = make_float4(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(y[4], y[5], y[6], y[7]);
+          }
+          __nv_bfloat162 h[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            h[i] = __floats2bfloat162_rn(y[2 * i] * inv2[r] * (g2[2 * i] + gn), y[2 * i + 1] * inv2[r] * (g2[2 * i + 1] + gn));
+          packed = make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                              *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+        }
+        *reinterpret_cast<uint4*>(tile + (size_t)(r >> 3) * 1024 + (size_t)(r & 7) * 128 + (((cc & 7) ^ (r & 7)) << 4)) = packed;
+      }
+    }
+  }
+}
+
 template <int BN>
 struct Tile {
   static constexpr int COLS = BN < 32 ? 32 : BN;                 // tensor-memory columns per accumulator
@@ -126,25 +264,19 @@ struct Tile {
   static constexpr int B_BYTES = BN * BK * 2;
 };
 
-template <int BN, int EPI>
+// XN: the activation rows come from a pending norm (NormIn) instead of the tm_x map; they are written once into a
+// shared-memory region of their own ([k block][BN][128 bytes], before the stage ring), so a stage holds weights only.
+template <int BN, int EPI, bool XN = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
                int stages, int cluster_reduce, float* __restrict__ partial, int* __restrict__ counters,
-               int* __restrict__ error_flag) {
+               int* __restrict__ error_flag, const NormIn norm_in) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int NACC = GATED ? 2 : 1;
   constexpr int COLS = Tile<BN>::COLS;
   constexpr int TMEM_COLS = COLS * NACC;
-  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
-  uint64_t* empty = full + stages;
-  uint64_t* acc_full = empty + stages;
-  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
-  int* s_flags = (int*)(tmem_slot + 1);                           // [0] abort, [1] arrival order of this CTA
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + (XN ? 0 : Tile<BN>::B_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
@@ -155,9 +287,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int kb_end = min(nkb_total, kb_begin + kb_per);
   const int nkb = kb_end - kb_begin;                              // >= 1 by the host's choice of splits
 
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem_x = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_x + (XN ? (size_t)kb_per * (BN * 128) : 0);    // the stage ring
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;
+  uint64_t* x_ready = acc_full + 1;
+  uint32_t* tmem_slot = (uint32_t*)(x_ready + 1);
+  int* s_flags = (int*)(tmem_slot + 1);                           // [0] abort, [1] arrival order of this CTA
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
+    mbar_init(x_ready, 128);
     s_flags[0] = 0;
     s_flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -187,9 +330,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tma_load_2d(st, &tm_w, &full[i], k, f0);
         if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[i], k, up_offset + f0);
       }
-      kf_pdl_wait();                                               // activations come from the previous kernel
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
+      if (!XN) {
+        kf_pdl_wait();                                             // activations come from the previous kernel
+        for (int i = 0; i < pre; ++i)
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
+      }
       for (int i = pre; i < nkb; ++i) {
         const int s = i % stages;
         if (!mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
@@ -202,7 +347,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int k = (kb_begin + i) * BK;
         tma_load_2d(st, &tm_w, &full[s], k, f0);
         if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[s], k, up_offset + f0);
-        tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
+        if (!XN) tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
       }
     }
   } else if (warp == 1) {
@@ -210,10 +355,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN);
       bool ok = true;
-      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + Tile<BN>::A_BYTES * NACC);
+      const uint64_t da0 = umma_desc(smem), db0 = XN ? umma_desc(smem_x) : umma_desc(smem + Tile<BN>::A_BYTES * NACC);
       const uint64_t du0 = umma_desc(smem + Tile<BN>::A_BYTES);
       int s = 0;
       uint32_t ph = 0;
+      if (XN) {
+        if (!mbar_wait(x_ready, 0)) {
+          atomicExch(error_flag, ERR_WAIT_FULL);
+          s_flags[0] = 1;
+          ok = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
       for (int i = 0; i < nkb && ok; ++i) {
         if (!mbar_wait(&full[s], ph)) {
           atomicExch(error_flag, ERR_WAIT_FULL);
@@ -222,7 +375,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           break;
         }
         const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));   // descriptors hold address >> 4
-        const uint64_t da = da0 + so, db = db0 + so, du = du0 + so;
+        const uint64_t da = da0 + so, du = du0 + so;
+        const uint64_t db = XN ? db0 + (uint64_t)((uint32_t)i * (uint32_t)((BN * 128) >> 4)) : db0 + so;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {                                // 32 bytes per K = 16 step
           const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
@@ -238,6 +392,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ---- epilogue: warps 2..5, each owns the lane quarter (warp % 4) ---------------------------------------------
     kf_pdl_wait();                                                             // before any global write
     const int quarter = warp & 3;
+    if (XN) {
+      normed_rows_to_smem<BN>(norm_in, T, K, kb_begin, nkb, smem_x, blockIdx.x == 0 && blockIdx.y == 0, quarter, lane,
+                              reinterpret_cast<float*>(s_flags + 2));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");             // generic writes -> the tensor core's reads
+      mbar_arrive(x_ready);
+    }
     const int f = f0 + quarter * 32 + lane;                                    // this thread's output feature
     const bool acc_ok = mbar_wait(acc_full, 0);
     if (!acc_ok && lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
@@ -274,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // Each CTA of the cluster (one per K split) parks its accumulator in its own shared memory (the pipeline
       // stages are free by now); after a cluster barrier CTA r sums, in split order, the tokens t with t % splits == r
       // straight out of its peers' shared memory and stores them.
-      float* red = reinterpret_cast<float*>(smem);                             // [NACC][BN][128]
+      float* red = reinterpret_cast<float*>(smem_x);                           // [NACC][BN][128]
       const int fl = quarter * 32 + lane;
       if (good) {
 #pragma unroll 1
@@ -779,6 +939,25 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 constexpr int SMEM_LIMIT = 220 * 1024;
 int g_cluster_reduce = 1;
 int g_stage_cap_kb = 108;
+// Choice of token tile and split-K for a launch.
+int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
+  int bn = 16;
+  while (bn < T && bn < 256) bn *= 2;
+  if (gated && bn > 256) bn = 256;
+  const int nkb = (K + BK - 1) / BK;
+  const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
+  int splits = 1;
+  if (tiles <= 74) {                                   // fewer tiles than half the SMs: cut K so that every SM streams
+    splits = (int)(148 / tiles);                       // weights, in ONE wave (one CTA per SM fits)
+    if (splits > 8) splits = 8;                        // a portable thread-block cluster holds 8 CTAs
+    if (splits > nkb) splits = nkb;
+    const int kb_per = (nkb + splits - 1) / splits;
+    splits = (nkb + kb_per - 1) / kb_per;              // no empty split
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+  return KF_OK;
+}
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
@@ -831,7 +1010,70 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   cfg.attrs = attr;
   cfg.numAttrs = na;
   cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
-                     cluster ? 1 : 0, partial, counters, error_flag);
+                     cluster ? 1 : 0, partial, counters, error_flag, NormIn{});
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// The decode tile (16 tokens) with the activation rows taken from a pending norm.  K % 64 == 0, T <= 16.
+constexpr int NORMED_BN = 16;
+constexpr int NORMED_X_LIMIT = 64 * 1024;             // shared memory for the rows of one CTA's K range
+
+template <int EPI>
+int launch_normed(const CUtensorMap& tw, const NormIn& ni, void* out, int T, int N, int K, int ld_out, float softcap,
+                  int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
+  constexpr int BN = NORMED_BN;
+  constexpr int NACC = EPI == EPI_GATED ? 2 : 1;
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC;
+  const int nkb = K / BK;
+  const int kb_per = (nkb + splits - 1) / splits;
+  const int x_bytes = kb_per * BN * 128;
+  if (x_bytes > NORMED_X_LIMIT) return KF_ERR_SIZE;
+  int stages = (SMEM_LIMIT - 2560 - x_bytes) / STAGE_BYTES;
+  if (g_stage_cap_kb > 0) {
+    const int cap = (g_stage_cap_kb * 1024) / STAGE_BYTES;
+    if (stages > cap) stages = cap;
+  }
+  if (stages > kb_per) stages = kb_per;
+  if (stages > 12) stages = 12;
+  if (stages < 1) return KF_ERR_SIZE;
+  const size_t smem = (size_t)stages * STAGE_BYTES + x_bytes + 1024 + 1024;
+  static bool configured = false;                      // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    configured = true;
+  }
+  const int n_feat = EPI == EPI_GATED ? up_offset : N;
+  dim3 grid(kf_ceil_div(n_feat, BM), 1, splits);
+  const bool cluster = splits > 1 && splits <= 8 && g_cluster_reduce &&
+                       (size_t)NACC * BN * BM * 4 <= (size_t)stages * STAGE_BYTES + x_bytes;
+  if (splits > 1 && !cluster && (!partial || !counters)) return KF_ERR_SIZE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (kf_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, true>, tw, tw, out, T, N, K, ld_out, softcap, act, up_offset, stages,
+                     cluster ? 1 : 0, partial, counters, error_flag, ni);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -948,22 +1190,45 @@ KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
 
 // Choice of token tile and split-K for a launch; also used by the caller to size the partial buffer.
 KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
-  int bn = 16;
-  while (bn < T && bn < 256) bn *= 2;
-  if (gated && bn > 256) bn = 256;
-  const int nkb = (K + BK - 1) / BK;
-  const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
-  int splits = 1;
-  if (tiles <= 74) {                                   // fewer tiles than half the SMs: cut K so that every SM streams
-    splits = (int)(148 / tiles);                       // weights, in ONE wave (one CTA per SM fits)
-    if (splits > 8) splits = 8;                        // a portable thread-block cluster holds 8 CTAs
-    if (splits > nkb) splits = nkb;
-    const int kb_per = (nkb + splits - 1) / splits;
-    splits = (nkb + kb_per - 1) / kb_per;              // no empty split
+  return plan_linear(T, N_features, K, gated, bn_out, splits_out);
+}
+
+// Whether kf_linear_tc_normed takes this shape (with the split count kf_linear_tc_plan gives for it).
+KF_API int kf_linear_tc_normed_supported(int T, int N_features, int K, int gated) {
+  if (T < 1 || T > NORMED_BN || K < BK || K % BK != 0 || encode_fn() == nullptr) return 0;
+  int bn = 0, splits = 1;
+  kf_linear_tc_plan(T, N_features, K, gated, &bn, &splits);
+  const int nkb = K / BK;
+  const int kb_per = (nkb + splits - 1) / splits;
+  return kb_per * NORMED_BN * 128 <= NORMED_X_LIMIT ? 1 : 0;
+}
+
+// The product of kf_linear_tc over rows that a pending norm defines (see NormIn):
+//   y = res_in + rmsnorm(branch; w_post);  res_out = y;  x = rmsnorm(y; w_next) in bfloat16;  out = x . w^T (mode as below).
+// branch, res_in, res_out: [T, K] 32-bit, res_out distinct from res_in; w_post, w_next: [K] bfloat16.
+KF_API int kf_linear_tc_normed(const float* branch, const float* res_in, float* res_out, const void* w_post, float eps_post,
+                               int plus_post, const void* w_next, float eps_next, int plus_next, const void* w, void* out,
+                               int mode, int T, int N, int K, float softcap, int act, int splits, float* partial,
+                               int* counters, int* error_flag, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return KF_OK;
+  if (!kf_linear_tc_normed_supported(T, N, K, mode == EPI_GATED)) return KF_ERR_SIZE;
+  if (!branch || !res_in || !res_out || res_in == res_out || !w_post || !w_next) return KF_ERR_SIZE;
+  if (((uintptr_t)w & 15) || ((uintptr_t)branch & 15) || ((uintptr_t)res_in & 15) || ((uintptr_t)res_out & 15) ||
+      ((uintptr_t)w_post & 15) || ((uintptr_t)w_next & 15)) return KF_ERR_ALIGN;
+  const int w_rows = mode == EPI_GATED ? 2 * N : N;
+  CUtensorMap tw;
+  if (!tensor_map(w, w_rows, K, BM, &tw)) return KF_ERR_SETUP;
+  NormIn ni;
+  ni.branch = branch; ni.res_in = res_in; ni.res_out = res_out;
+  ni.w_post = (const __nv_bfloat16*)w_post; ni.w_next = (const __nv_bfloat16*)w_next;
+  ni.eps_post = eps_post; ni.eps_next = eps_next; ni.plus_post = plus_post; ni.plus_next = plus_next;
+  const int up_offset = mode == EPI_GATED ? N : 0;
+  switch (mode) {
+    case EPI_F32: return launch_normed<EPI_F32>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
+    case EPI_BF16: return launch_normed<EPI_BF16>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
+    case EPI_GATED: return launch_normed<EPI_GATED>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
   }
-  *bn_out = bn;
-  *splits_out = splits;
-  return KF_OK;
+  return KF_ERR_SIZE;
 }
 
 // mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out, 2 = gated: w = [gate; up] stacked

@@ -261,6 +261,61 @@ def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> b
     return True
 
 
+# True: a norm between two products of few rows is computed inside the second product's kernel (one launch fewer).  Off by
+# default: in the one-kernel-per-product path the rows' sums stall the weight stream longer than the norm's own kernel
+# takes (measured at Gemma 2 2B sizes, batch 8: 3.76 ms per step against 2.76 ms).  KUNGFU_FUSE_NORMS=1 switches it on.
+fuse_pending_norms = os.environ.get("KUNGFU_FUSE_NORMS", "0") == "1"
+
+
+class PendingNorm:
+    """Rows that are not computed yet: y = residual + rmsnorm(branch; post), rows = rmsnorm(y; then).
+    `linear` and `linear_gated` take one in place of their activation rows and compute the norm inside the product's
+    kernel; that kernel also writes y to `residual_out` (a buffer other than `residual`).  Only made for shapes that
+    `linear_fuses_norm` accepts."""
+    __slots__ = ("branch", "residual", "residual_out", "post_weight", "post_eps", "post_plus_one", "next_weight",
+                 "next_eps", "next_plus_one")
+
+    def __init__(self, branch, residual, residual_out, post_weight, post_eps, post_plus_one, next_weight, next_eps,
+                 next_plus_one):
+        self.branch, self.residual, self.residual_out = branch, residual, residual_out
+        self.post_weight, self.post_eps, self.post_plus_one = post_weight, float(post_eps), bool(post_plus_one)
+        self.next_weight, self.next_eps, self.next_plus_one = next_weight, float(next_eps), bool(next_plus_one)
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+
+def linear_fuses_norm(T: int, weight, gated: bool, act_dtype) -> bool:
+    """Whether a product of T rows with `weight` can take a PendingNorm (few rows, bfloat16, on the tensor cores)."""
+    if _override is not None or not (fuse_pending_norms and use_tensor_cores):
+        return False
+    if weight.dtype != torch.bfloat16 or act_dtype != torch.bfloat16 or not weight.is_cuda:
+        return False
+    N = weight.shape[0] // 2 if gated else weight.shape[0]
+    return bool(library().kf_linear_tc_normed_supported(int(T), int(N), int(weight.shape[1]), int(gated)))
+
+
+def _linear_normed(p: PendingNorm, weight, out, mode: int, N: int, softcap: float, act: int) -> None:
+    T, K = p.residual.shape
+    lib = library()
+    if (p.branch.dtype != torch.float32 or p.residual.dtype != torch.float32 or p.post_weight.dtype != torch.bfloat16
+            or p.next_weight.dtype != torch.bfloat16 or weight.shape[1] != K):
+        raise KernelError("linear over a pending norm: 32-bit branch and residual and bfloat16 norm weights are required")
+    bn, splits = ctypes.c_int(0), ctypes.c_int(0)
+    lib.kf_linear_tc_plan(T, N, K, int(mode == 2), ctypes.byref(bn), ctypes.byref(splits))
+    sc = _dev_scratch(weight.device)
+    partial = None
+    if splits.value > 1:
+        if -(-N // 128) > sc["counters"].numel():
+            raise KernelError("linear over a pending norm: too many output tiles for the split counters")
+        partial = _partial(weight.device, splits.value * T * (2 * N if mode == 2 else N))
+    _check(lib.kf_linear_tc_normed(_p(p.branch), _p(p.residual), _p(p.residual_out), _p(p.post_weight), _f(p.post_eps),
+                                   int(p.post_plus_one), _p(p.next_weight), _f(p.next_eps), int(p.next_plus_one),
+                                   _p(weight), _p(out), mode, T, N, K, _f(softcap), act, splits.value, _p(partial),
+                                   _p(sc["counters"]), _p(sc["error"]), _stream()), "linear over a pending norm")
+
+
 @_dispatch("linear")
 def linear(x, weight, out, softcap: float = 0.0) -> None:
     """out[T, N] = x[T, K] . weight[N, K]^T, 32-bit accumulation; softcap > 0 applies cap*tanh(v/cap).
@@ -270,6 +325,11 @@ def linear(x, weight, out, softcap: float = 0.0) -> None:
     N = weight.shape[0]
     if weight.shape[1] != K or tuple(out.shape) != (T, N):
         raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    if isinstance(x, PendingNorm):
+        if out.dtype != torch.float32 and softcap != 0.0:
+            raise KernelError("linear over a pending norm: a softcap needs a 32-bit output")
+        _linear_normed(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0)
+        return
     if out.dtype == torch.float32 or softcap == 0.0:
         if _linear_tc(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0):
             return
@@ -282,6 +342,11 @@ def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
     """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows."""
     T = x.shape[0]
     I = out.shape[1]
+    if isinstance(x, PendingNorm):
+        if out.dtype != torch.bfloat16:
+            raise KernelError("gated product over a pending norm: the output must be bfloat16")
+        _linear_normed(x, w_gate_up, out, 2, I, 0.0, _ACT[activation])
+        return
     if out.dtype == torch.bfloat16 and _linear_tc(x, w_gate_up, out, 2, I, 0.0, _ACT[activation]):
         return
     gu = ctx.buf("ffn_gate_up", (T, 2 * I), torch.float32)

@@ -96,6 +96,19 @@ def test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, dtype):
     ops.raise_on_device_error()
 
 
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+def test_norms_computed_inside_the_next_product_match_plain(tmp_path_factory, mode):
+    """The same configuration with the switch on that lets a product of few rows compute the norm before it in its own
+    kernel (decode steps then run two kernels fewer per layer, and the residual alternates between two buffers)."""
+    from kungfu_b200 import ops
+    was = ops.fuse_pending_norms
+    ops.fuse_pending_norms = True
+    try:
+        test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, "bfloat16")
+    finally:
+        ops.fuse_pending_norms = was
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_stored_in_32_bit_stay_so(tmp_path, dtype):
     """A file whose tensors are 32-bit floats: the bfloat16 engine keeps them 32-bit (and multiplies them with the

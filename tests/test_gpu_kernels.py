@@ -141,6 +141,64 @@ def test_linear_gated_tensor_cores(ops, T, I, K, act):
     assert rel_err(out, ref) < 6e-3
 
 
+@pytest.mark.parametrize("T,N,K,gated", [(1, 256, 64, False), (8, 4096, 2304, False), (5, 130, 192, False), (16, 1000, 512, False),
+                                         (8, 9216, 2304, True), (3, 200, 128, True), (16, 320, 1024, True), (7, 136, 4608, False)])
+@pytest.mark.parametrize("plus_one", [True, False])
+def test_linear_over_pending_norm(ops, T, N, K, gated, plus_one):
+    """The product whose activation rows are a norm not yet run: y = x + rmsnorm(a; w1), rows = rmsnorm(y; w2), computed
+    inside the tcgen05 kernel; the kernel also leaves y in a second buffer.  Against float64, with and without split-K."""
+    from cpu_ops import _act
+    g = torch.Generator().manual_seed(T * 13 + N + K)
+    a = (torch.randn(T, K, generator=g) * 3.0).to(DEV)
+    x = torch.randn(T, K, generator=g).to(DEV)
+    x[:, 5] *= 40.0                                            # one large residual element: the sums must be 32-bit
+    w1 = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    w2 = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    eps1, eps2 = 1e-6, 3e-5
+    rows_w = 2 * N if gated else N
+    w = (torch.randn(rows_w, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    was, ops.fuse_pending_norms = ops.fuse_pending_norms, True
+    try:
+        assert ops.linear_fuses_norm(T, w, gated, torch.bfloat16)
+    finally:
+        ops.fuse_pending_norms = was
+    p1 = 1.0 if plus_one else 0.0
+
+    def rms(v, wt, eps):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * (wt.double() + p1)
+
+    y = x.double() + rms(a.double(), w1, eps1)
+    rows = rms(y, w2, eps2).to(torch.bfloat16).double()          # the kernel rounds the rows to bfloat16 too
+    full = rows @ w.double().T
+    ref = _act("gelu_tanh", full[:, :N]) * full[:, N:] if gated else full
+    y_out = torch.full((T, K), float("nan"), device=DEV)
+    pend = ops.PendingNorm(a, x, y_out, w1, eps1, plus_one, w2, eps2, plus_one)
+    out = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
+    x_before = x.clone()
+    if gated:
+        ops.linear_gated(pend, w, out, "gelu_tanh", None)
+    else:
+        ops.linear(pend, w, out)
+    ops.raise_on_device_error()
+    assert torch.equal(x, x_before), "the old residual is left as it was"
+    assert rel_err(y_out, y) < 1e-6
+    # a row element that sits near a bfloat16 rounding boundary may round the other way than in the reference
+    assert rel_err(out, ref) < (6e-3 if gated else 2e-3)
+    again = torch.empty_like(out)
+    y2 = torch.empty_like(y_out)
+    pend2 = ops.PendingNorm(a, x, y2, w1, eps1, plus_one, w2, eps2, plus_one)
+    (ops.linear_gated(pend2, w, again, "gelu_tanh", None) if gated else ops.linear(pend2, w, again))
+    assert torch.equal(out, again) and torch.equal(y_out, y2)
+    # and it agrees with the unfused kernels run one after the other
+    xs = x.clone()
+    rows_dev = torch.empty(T, K, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(a, w1, eps1, plus_one, xs, next_weight=w2, next_eps=eps2, next_plus_one=plus_one, next_out=rows_dev)
+    sep = torch.empty_like(out)
+    (ops.linear_gated(rows_dev, w, sep, "gelu_tanh", None) if gated else ops.linear(rows_dev, w, sep))
+    assert rel_err(y_out, xs) < 1e-6
+    assert rel_err(out, sep) < (6e-3 if gated else 2e-3)
+
+
 @pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
 def test_linear_gated(ops, act):
     from cpu_ops import _act
