@@ -250,7 +250,7 @@ class Runner:
         bucket = self._graph_bucket(entries)
         if bucket is None:
             ctx = self._fill(entries)
-            logits = self.model.forward(ctx)
+            logits = self._forward(ctx)
         else:
             logits = self._step_graphed(entries, bucket)
         for e in entries:
@@ -273,6 +273,20 @@ class Runner:
             b *= 2
         return b if b <= max(self.cache.max_requests, 1) * 2 else None
 
+    def _forward(self, ctx):
+        """The model's pass over the step.  Steps of few rows queue their products, so that products that follow one
+        another run as one kernel (ops.chain_begin); the queue is emptied before this returns."""
+        from .. import ops
+        chain = (self.device.type == "cuda" and 0 < ctx.n_rows <= 16 and ctx.act_dtype == torch.bfloat16
+                 and not ops.tracing())
+        if chain:
+            ops.chain_begin()
+        try:
+            return self.model.forward(ctx)
+        finally:
+            if chain:
+                ops.chain_end()
+
     def _step_graphed(self, entries, bucket: int):
         """First time a bucket is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
@@ -290,7 +304,7 @@ class Runner:
         ctx = self._fill(entries, bucket)
         if state is None:
             self._graphs[bucket] = {"generation": None, "graph": None, "seen": 1}
-            logits = self.model.forward(ctx)
+            logits = self._forward(ctx)
             self._graphs[bucket]["generation"] = self.buffers.generation
             return logits[:n]
         if state["graph"] is None:
@@ -298,10 +312,10 @@ class Runner:
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
             with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx)
+                logits = self._forward(ctx)
             if self.buffers.generation != state["generation"]:
                 self._graphs.pop(bucket)                   # capture itself grew a buffer: run this step eagerly
-                return self.model.forward(ctx)[:n]
+                return self._forward(ctx)[:n]
             state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
             ops.add_launches(-state["kernels"])            # capture launched nothing
         state["graph"].replay()

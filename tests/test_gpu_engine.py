@@ -97,16 +97,18 @@ def test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, dtype):
 
 
 @pytest.mark.parametrize("mode", ["tail", "mixed"])
-def test_norms_computed_inside_the_next_product_match_plain(tmp_path_factory, mode):
+@pytest.mark.parametrize("chain", [False, True])
+def test_norms_computed_inside_the_next_product_match_plain(tmp_path_factory, mode, chain):
     """The same configuration with the switch on that lets a product of few rows compute the norm before it in its own
-    kernel (decode steps then run two kernels fewer per layer, and the residual alternates between two buffers)."""
+    kernel (decode steps then run two kernels fewer per layer, and the residual alternates between two buffers); and
+    with the switch that runs the products of such a step as phases of one persistent kernel."""
     from kungfu_b200 import ops
-    was = ops.fuse_pending_norms
-    ops.fuse_pending_norms = True
+    was = ops.fuse_pending_norms, ops.chain_products
+    ops.fuse_pending_norms, ops.chain_products = True, chain
     try:
         test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, "bfloat16")
     finally:
-        ops.fuse_pending_norms = was
+        ops.fuse_pending_norms, ops.chain_products = was
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

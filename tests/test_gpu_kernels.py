@@ -199,6 +199,79 @@ def test_linear_over_pending_norm(ops, T, N, K, gated, plus_one):
     assert rel_err(out, sep) < (6e-3 if gated else 2e-3)
 
 
+@pytest.mark.parametrize("T,H,Q,I", [(8, 2304, 2048, 9216), (1, 128, 64, 320), (5, 512, 768, 1536), (16, 192, 320, 200), (3, 1024, 64, 4608)])
+def test_chain_of_products(ops, T, H, Q, I):
+    """Products queued between chain_begin and chain_end run as ONE persistent kernel: output projection, gated pair over
+    a pending norm, down projection, and the next projection over a second pending norm, as a decode layer strings them.
+    Against float64 and against the same products launched one by one; twice for the same bits."""
+    from cpu_ops import _act
+    g = torch.Generator().manual_seed(T + H + I)
+    bf = torch.bfloat16
+    attn = torch.randn(T, Q, generator=g).to(bf).to(DEV)
+    resid = torch.randn(T, H, generator=g).to(DEV)
+    wo = (torch.randn(H, Q, generator=g) * 0.05).to(bf).to(DEV)
+    wgu = (torch.randn(2 * I, H, generator=g) * 0.05).to(bf).to(DEV)
+    wd = (torch.randn(H, I, generator=g) * 0.05).to(bf).to(DEV)
+    wq = (torch.randn(Q + 128, H, generator=g) * 0.05).to(bf).to(DEV)
+    norms = [(torch.randn(H, generator=g) * 0.3).to(bf).to(DEV) for _ in range(4)]
+    eps = 1e-6
+
+    def run(chained):
+        a = torch.full((T, H), float("nan"), device=DEV)
+        h = torch.full((T, I), float("nan"), device=DEV, dtype=bf)
+        f = torch.full((T, H), float("nan"), device=DEV)
+        q = torch.full((T, Q + 128), float("nan"), device=DEV)
+        r1 = torch.full((T, H), float("nan"), device=DEV)
+        r2 = torch.full((T, H), float("nan"), device=DEV)
+        was, was_chain = ops.fuse_pending_norms, ops.chain_products
+        ops.fuse_pending_norms = True
+        if chained:
+            ops.chain_products = True
+            ops.chain_begin()
+            assert ops.chaining()
+        try:
+            ops.linear(attn, wo, a)
+            ops.linear_gated(ops.PendingNorm(a, resid, r1, norms[0], eps, True, norms[1], eps, True), wgu, h, "gelu_tanh", None)
+            ops.linear(h, wd, f)
+            ops.linear(ops.PendingNorm(f, r1, r2, norms[2], eps, True, norms[3], eps, True), wq, q)
+        finally:
+            if chained:
+                ops.chain_end()
+            ops.fuse_pending_norms, ops.chain_products = was, was_chain
+        ops.raise_on_device_error()
+        return a, h, f, q, r1, r2
+
+    def rms(v, wt):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * (wt.double() + 1.0)
+
+    before = ops.launch_count()
+    got = run(True)
+    if I % 64 == 0:
+        assert ops.launch_count() - before == 1, "four products, one launch"
+    else:                                                      # a product the chain kernel refuses runs on its own
+        assert ops.launch_count() - before > 1
+    a, h, f, q, r1, r2 = got
+    a_ref = attn.double() @ wo.double().T
+    assert rel_err(a, a_ref) < 2e-6 * math.sqrt(Q) + 1e-6
+    # later stages are checked against their own inputs as the kernel produced them (rounding does not pile up)
+    y1 = resid.double() + rms(a.double(), norms[0])
+    assert rel_err(r1, y1) < 1e-6
+    n1 = rms(y1, norms[1]).to(bf).double()
+    gu = n1 @ wgu.double().T
+    assert rel_err(h, _act("gelu_tanh", gu[:, :I]) * gu[:, I:]) < 6e-3
+    assert rel_err(f, h.double() @ wd.double().T) < 2e-6 * math.sqrt(I) + 1e-6
+    y2 = r1.double() + rms(f.double(), norms[2])
+    assert rel_err(r2, y2) < 1e-6
+    assert rel_err(q, rms(y2, norms[3]).to(bf).double() @ wq.double().T) < 2e-3
+    again = run(True)
+    for x1, x2 in zip(got, again):
+        assert torch.equal(x1, x2)
+    # one by one: the same up to the bfloat16 roundings of h, which fall differently where the split sums differ in order
+    single = run(False)
+    for x1, x2, tol in zip(got, single, (1e-5, 8e-3, 2e-3, 3e-3, 1e-5, 2e-3)):
+        assert rel_err(x1, x2) < tol
+
+
 @pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
 def test_linear_gated(ops, act):
     from cpu_ops import _act
