@@ -322,16 +322,21 @@ constexpr int DM_WARPS = 4;
 constexpr int DM_STAGES = 3;                     // tiles of a warp in shared memory (one in use, the others in flight)
 constexpr int DM_KEYS = 16;                       // keys per warp tile
 
+// With `qkv` given (the 32-bit q|k|v rows of the step, a row = [nh*D | nkv*D | nkv*D]) the kernel also does what the
+// rotate-and-append kernel would: it rotates its query heads itself, and the block whose key range holds the row's own
+// position rotates the new key, writes key and value into the page (if `write_kv`) and then reads them like any other.
+// What does not depend on earlier kernels of the step (the step's integers, keys of earlier steps) is requested
+// before the grid dependency is waited for.
 template <int D>
 __global__ void __launch_bounds__(DM_WARPS * 32)
-attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int rot, int write_kv, __nv_bfloat16* pages,
                        const int* __restrict__ items, int n_items, const int* __restrict__ positions,
                        const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
                        int nh, int nkv, float scale, float softcap, int window, int n_splits,
                        float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
   using namespace kf_mma;
   kf_pdl_trigger();
-  kf_pdl_wait();
   constexpr int CH = D / 8;
   constexpr int NT_O = D / 8;
   constexpr int KS_QK = D / 16;
@@ -343,6 +348,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   __shared__ float sm_ml[DM_WARPS][16][2];
   __shared__ int s_last;
 
+  // ---- the step's integers: written before the step's first kernel, so readable at once -------------------------------
   const int item = blockIdx.x / nkv, kvh = blockIdx.x - item * nkv;
   const int split = blockIdx.y;
   const int G = nh / nkv;
@@ -353,6 +359,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int g = lane >> 2, tq = lane & 3;
   __nv_bfloat16* orow = out + (size_t)t * nh * D;
   if (req < 0) {
+    kf_pdl_wait();
     if (split == 0)
       for (int e = tid; e < G * D; e += blockDim.x) orow[(size_t)h_first * D + e] = __float2bfloat16_rn(0.f);
     return;
@@ -365,15 +372,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int k_begin = lo + split * per;
   const int k_end = min(pos + 1, k_begin + per);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + DM_KEYS - 1) / DM_KEYS : 0;
-
-  // ---- Q: the G heads of this kv head are rows 0..G-1, the rest of the 16 rows are zero ----------------------------
-  for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
-    const int r = idx / CH, c = idx - r * CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h_first + r) * D + c * 8);
-    *reinterpret_cast<uint4*>(tile_ptr<D>(sQ, r, c)) = v;
-  }
-  __syncthreads();
+  // the tile that holds the row's own key: an earlier kernel of this step writes that key (or this block does)
+  const int own_tile = (pos >= k_begin && pos < k_end) ? (pos - k_begin) / DM_KEYS : -1;
 
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
@@ -407,17 +407,81 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
   };
 
+  // first tiles of this warp, except the one with the row's own key: keys of earlier steps
+#pragma unroll
+  for (int s = 0; s < DM_STAGES - 1; ++s) {
+    const int tile = warp + s * DM_WARPS;
+    if (tile < n_tiles && tile != own_tile) load_tile(tile, s);
+  }
+  kf_pdl_wait();
+
+  if (qkv != nullptr) {
+    // ---- Q: rotated here; rows 0..G-1 are the heads of this kv head, the rest of the 16 rows are zero ---------------------
+    const float* in = qkv + (size_t)t * (nh + 2 * nkv) * D;
+    const int half = rot >> 1;
+    const float* cs = cos_t + (size_t)t * half;
+    const float* sn = sin_t + (size_t)t * half;
+    auto rotated8 = [&](const float* head, int c8) -> uint4 {
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int i = c8 * 8 + e;
+        float x = head[i];
+        if (i < half) x = x * cs[i] - head[i + half] * sn[i];
+        else if (i < rot) x = head[i - half] * sn[i - half] + x * cs[i - half];
+        v[e] = x;
+      }
+      return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    };
+    for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
+      const int r = idx / CH, c = idx - r * CH;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < G) v = rotated8(in + (size_t)(h_first + r) * D, c);
+      *reinterpret_cast<uint4*>(tile_ptr<D>(sQ, r, c)) = v;
+    }
+    // ---- the row's own key and value: rotated, written to the page by the block that will read them ---------------------
+    if (write_kv && own_tile >= 0) {
+      const int page = tab[pos / page_size];
+      if (page >= 0) {
+        __nv_bfloat16* kdst = pages + ((long)page * 2 * nkv + kvh) * (long)head_stride + (long)(pos % page_size) * D;
+        const float* kin = in + (size_t)(nh + kvh) * D;
+        const float* vin = in + (size_t)(nh + nkv + kvh) * D;
+        for (int c = tid; c < CH; c += blockDim.x) {
+          *reinterpret_cast<uint4*>(kdst + c * 8) = rotated8(kin, c);
+          const float* vv = vin + c * 8;
+          *reinterpret_cast<uint4*>(kdst + v_off + c * 8) =
+              make_uint4(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]), pack_bf16(vv[4], vv[5]), pack_bf16(vv[6], vv[7]));
+        }
+      }
+    }
+  } else {
+    // ---- Q as the rotate-and-append kernel left it ---------------------------------------------------------------------
+    for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
+      const int r = idx / CH, c = idx - r * CH;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h_first + r) * D + c * 8);
+      *reinterpret_cast<uint4*>(tile_ptr<D>(sQ, r, c)) = v;
+    }
+  }
+  __syncthreads();                                                // Q in place; the new key and value are in the page
+  {
+    // the own-key tile, if it is one of this warp's first tiles; then all of them are one group, and empty groups keep
+    // the count of groups per stage that the loop below relies on
+#pragma unroll
+    for (int s = 0; s < DM_STAGES - 1; ++s) {
+      const int tile = warp + s * DM_WARPS;
+      if (tile < n_tiles && tile == own_tile) load_tile(tile, s);
+    }
+#pragma unroll
+    for (int s = 0; s < DM_STAGES - 1; ++s) cp_async_commit();
+  }
+
   float o_acc[NT_O][4];
 #pragma unroll
   for (int n = 0; n < NT_O; ++n) { o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
 
-#pragma unroll
-  for (int s = 0; s < DM_STAGES - 1; ++s) {
-    if (warp + s * DM_WARPS < n_tiles) load_tile(warp + s * DM_WARPS, s);
-    cp_async_commit();
-  }
   int it = 0;
   for (int tile = warp; tile < n_tiles; tile += DM_WARPS, ++it) {
     const int stage = it % DM_STAGES;
@@ -554,7 +618,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 }
 
 template <int D>
-int launch_decode_mma(const void* q, const void* pages, const int* items, int n_items, const int* positions,
+int launch_decode_mma(const float* qkv, const float* cos_t, const float* sin_t, int rot, int write_kv,
+                      const void* q, const void* pages, const int* items, int n_items, const int* positions,
                       const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
                       float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
   const size_t smem = (size_t)(16 * D + DM_WARPS * DM_STAGES * 2 * DM_KEYS * D) * 2;
@@ -567,8 +632,9 @@ int launch_decode_mma(const void* q, const void* pages, const int* items, int n_
     configured = true;
   }
   kf_launch(attn_decode_mma_kernel<D>, dim3(n_items * nkv, n_splits), dim3(DM_WARPS * 32), smem, stream,
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, items, n_items, positions, row_req, table, table_stride,
-            page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, (__nv_bfloat16*)out);
+            (const __nv_bfloat16*)q, qkv, cos_t, sin_t, rot, write_kv, (__nv_bfloat16*)const_cast<void*>(pages), items, n_items,
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters,
+            (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -646,7 +712,7 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
   if (n_splits > MERGE_MAX_SPLITS || ht > MERGE_MAX_HEADS) return KF_ERR_SIZE;
   if (ht == 0) {                                     // tensor-core variant
     if (nh / nkv > 16) return KF_ERR_SIZE;
-#define KF_MMA_ARGS q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+#define KF_MMA_ARGS nullptr, nullptr, nullptr, 0, 0, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
     switch (d) {
       case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
       case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
@@ -666,6 +732,31 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
     case 256: return launch_decode_d<256>(KF_ARGS);
   }
 #undef KF_ARGS
+  return KF_ERR_SIZE;
+}
+
+// The tensor-core decode kernel with the rotation of q and k and the append of k and v done inside it: `qkv` is the
+// 32-bit [T, (nh + 2 nkv) d] result of the stacked product, cos_t / sin_t the step's [T, rot/2] tables (null when rot is
+// 0).  Every row handled must be the only row of its request at the request's last position (a decode row).
+KF_API int kf_attention_decode_fused(const float* qkv, const float* cos_t, const float* sin_t, int rot, int write_kv, void* out,
+                                     void* pages, const int* items, int n_items, const int* positions, const int* row_req,
+                                     const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
+                                     float softcap, int window, int n_splits, float* partial, int* counters,
+                                     cudaStream_t stream) {
+  if (n_items <= 0) return KF_OK;
+  if (!qkv || nkv < 1 || nh % nkv != 0 || nh / nkv > 16 || page_size < 1 || n_splits < 1) return KF_ERR_SIZE;
+  if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && (!cos_t || !sin_t))) return KF_ERR_SIZE;
+  if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
+  if (n_splits > MERGE_MAX_SPLITS) return KF_ERR_SIZE;
+#define KF_MMA_ARGS qkv, cos_t, sin_t, rot, write_kv, nullptr, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+  switch (d) {
+    case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
+    case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
+    case 64: return launch_decode_mma<64>(KF_MMA_ARGS);
+    case 128: return launch_decode_mma<128>(KF_MMA_ARGS);
+    case 256: return launch_decode_mma<256>(KF_MMA_ARGS);
+  }
+#undef KF_MMA_ARGS
   return KF_ERR_SIZE;
 }
 

@@ -532,6 +532,42 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
            "attention (generic)")
 
 
+fuse_rope_into_decode = os.environ.get("KUNGFU_FUSE_ROPE", "1") != "0"   # False: rotation and append always run as their own kernel
+
+
+def decode_attention_takes_qkv(ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether `rope_append_attend` can run this step's attention: every row is the single row of its request (a decode
+    step), bfloat16 pages, and the tensor-core decode kernel has an instance for the head size and group."""
+    if _override is not None or not (fuse_rope_into_decode and use_fast_attention and decode_on_tensor_cores):
+        return False
+    T = ctx.n_rows
+    if T <= 0 or getattr(ctx, "n_dec_rows", 0) != T or cache is None or cache.pages.dtype != torch.bfloat16:
+        return False
+    if n_heads // n_kv_heads > 16 or not library().kf_attention_decode_supported(head_dim):
+        return False
+    return T * n_kv_heads <= _dev_scratch(cache.pages.device)["counters"].numel()
+
+
+@_dispatch("rope_append_attend")
+def rope_append_attend(qkv, cos, sin, rot: int, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int,
+                       scale: float, softcap: float, window: int | None) -> None:
+    """For a decode step: rotate q and k, append k and v to the pages and attend, in the split-KV decode kernel itself
+    (one launch instead of two).  qkv: 32-bit [T, (n_heads + 2 n_kv_heads) * head_dim]; out: bfloat16 [T, n_heads * head_dim]."""
+    T = qkv.shape[0]
+    lib = library()
+    table = ctx.block_tables[cache.group]
+    max_keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+    splits = ctypes.c_int(0)
+    lib.kf_attention_decode_mma_plan(T, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(splits))
+    sc = _dev_scratch(qkv.device)
+    partial = _partial(qkv.device, T * n_heads * splits.value * (head_dim + 4)) if splits.value > 1 else None
+    _check(lib.kf_attention_decode_fused(_p(qkv), _p(cos), _p(sin), int(rot), int(cache.writes), _p(out), _p(cache.pages),
+                                         None, T, _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1],
+                                         cache.page_size, n_heads, n_kv_heads, head_dim, _f(scale), _f(softcap),
+                                         int(window or 0), splits.value, _p(partial), _p(sc["counters"]), _stream()),
+           "attention (decode, rotation and append inside)")
+
+
 @_dispatch("argmax")
 def argmax(logits, out) -> None:
     """out[r] = index of the first maximum of logits[r, :] (int32)."""

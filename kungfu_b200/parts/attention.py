@@ -44,16 +44,20 @@ class PagedAttention(Mixer):
         nh, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = ctx.buf("attn_qkv", (T, (nh + 2 * nkv) * d), torch.float32)
         ops.linear(x, self.wqkv, qkv)
-        q = ctx.buf("attn_q", (T, nh * d), ctx.act_dtype)
         if self.position is not None:
             cos, sin = self.position.rotation(ctx)
             rot = 2 * cos.shape[1]
         else:
             cos = sin = None
             rot = 0
-        ops.rope_kv_append(qkv, cos, sin, rot, nh, nkv, d, ctx, cache, q)
         o = ctx.buf("attn_o", (T, nh * d), ctx.act_dtype)
-        ops.paged_attention(q, o, ctx, cache, nh, nkv, d, self.scale, self.softcap, self.window)
+        if ops.decode_attention_takes_qkv(ctx, cache, nh, nkv, d):
+            # a decode step: the attention kernel rotates, appends and attends in one launch
+            ops.rope_append_attend(qkv, cos, sin, rot, o, ctx, cache, nh, nkv, d, self.scale, self.softcap, self.window)
+        else:
+            q = ctx.buf("attn_q", (T, nh * d), ctx.act_dtype)
+            ops.rope_kv_append(qkv, cos, sin, rot, nh, nkv, d, ctx, cache, q)
+            ops.paged_attention(q, o, ctx, cache, nh, nkv, d, self.scale, self.softcap, self.window)
         y = ctx.buf("branch_out", (T, self.width), torch.float32)
         ops.linear(o, self.wo, y)
         return y

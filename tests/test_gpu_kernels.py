@@ -425,6 +425,48 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("nh,nkv,d,P,window,rot", [(8, 4, 256, 64, 1000, 256), (4, 2, 16, 4, 8, 16), (6, 2, 32, 16, None, 16),
+                                                   (16, 2, 128, 64, 4096, 128), (5, 5, 64, 32, None, 0), (8, 1, 128, 16, 33, 64)])
+@pytest.mark.parametrize("writes", [True, False])
+def test_decode_attention_with_rotation_and_append_inside(ops, nh, nkv, d, P, window, rot, writes):
+    """A decode step's attention as one launch (the kernel rotates q and k, appends k and v, attends) against the two
+    launches it replaces: same bits out and in the pages.  Lengths put the new key at a page's first slot, its last, in
+    the middle, and alone in a request."""
+    lens = [1, P + 1, 2 * P, 3000, 700, 65]
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=21)
+    T = len(lens)
+    g = torch.Generator().manual_seed(22)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    if rot:
+        inv = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
+        cos = torch.empty(T, rot // 2, device=DEV)
+        sin = torch.empty(T, rot // 2, device=DEV)
+        ops.rope_table(pos, inv, cos, sin)
+    else:
+        cos = sin = None
+    ctx = _Ctx(pos, torch.arange(T, dtype=torch.int32, device=DEV), table.to(DEV), list(range(T)), [])
+    ctx.n_rows = T
+    scale, cap = 1.0 / math.sqrt(d), 50.0
+    # the two launches
+    pages_a = pages.to(DEV).clone()
+    view_a = _View(pages_a, P, writes)
+    q = torch.empty(T, nh * d, dtype=torch.bfloat16, device=DEV)
+    ops.rope_kv_append(qkv, cos, sin, rot, nh, nkv, d, ctx, view_a, q)
+    out_a = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q, out_a, ctx, view_a, nh, nkv, d, scale, cap, window)
+    # the one launch
+    pages_b = pages.to(DEV).clone()
+    view_b = _View(pages_b, P, writes)
+    assert ops.decode_attention_takes_qkv(ctx, view_b, nh, nkv, d)
+    out_b = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.rope_append_attend(qkv, cos, sin, rot, out_b, ctx, view_b, nh, nkv, d, scale, cap, window)
+    assert bool(torch.isfinite(out_b.float()).all())
+    assert torch.equal(pages_a, pages_b)
+    assert torch.equal(pages_b, pages.to(DEV)) != writes or T == 0      # the append happened exactly when asked for
+    assert torch.equal(out_a, out_b)
+
+
 @pytest.mark.parametrize("nh,nkv,d,P,window,cap", [(4, 2, 16, 4, 8, 50.0), (6, 2, 32, 16, None, 20.0), (8, 4, 256, 64, 100, 50.0),
                                                    (5, 5, 64, 32, None, 30.0), (16, 2, 128, 64, 70, 50.0), (8, 1, 128, 16, None, 0.0),
                                                    (2, 1, 256, 8, None, 0.0), (4, 2, 64, 64, 100, 30.0), (3, 1, 128, 128, None, 0.0),
