@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--context C] [--size 2b|9b|27b]
+    python bench.py --micro attention|gemm      (one kernel alone, JSON lines; used for the summaries in profiles/)
 
 A "step" is one decode step: every live request gets one token.  Default: the layer sizes of Gemma 2 2B,
 random bfloat16 weights, 8 requests at a context of 8192 tokens.  `value` is decoded tokens per second timed
@@ -285,6 +286,93 @@ def run_ours(args) -> dict:
             "roofline": roofline, "points": points, "impl": "ours"}
 
 
+def micro_attention() -> int:
+    """Decode attention alone: eight launches over distinct pages replayed from a CUDA graph, per batch size; one JSON
+    line each with microseconds per launch and bytes of keys and values over that time."""
+    import torch
+    from kungfu_b200 import api, ops
+
+    class View:
+        def __init__(self, pages, page_size):
+            self.pages, self.page_size, self.group, self.writes = pages, page_size, 0, False
+
+    class Ctx:
+        pass
+
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    nh, nkv, d, page, ctx_len, launches = 8, 4, 256, 64, 8192, 8
+    for batch in (1, 2, 4, 8, 16, 64):
+        per_req = ctx_len // page
+        pages = torch.randn(launches * batch * per_req + 1, 2, nkv, page, d, device=device, dtype=torch.bfloat16)
+        ctxs = []
+        for l in range(launches):
+            c = Ctx()
+            c.positions = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=device)
+            c.row_req = torch.arange(batch, dtype=torch.int32, device=device)
+            c.block_tables = [(torch.arange(batch * per_req, dtype=torch.int32, device=device) + l * batch * per_req)
+                              .view(batch, per_req).contiguous()]
+            c.n_rows = c.n_dec_rows = batch
+            c.n_pre_rows = c.n_tiles = c.n_wide = 0
+            c.dec_rows = c.pre_rows = None
+            c.max_kv_len = ctx_len
+            ctxs.append(c)
+        q = torch.randn(batch, nh * d, device=device, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        view = View(pages, page)
+        for window in (None, 4096):
+            def run():
+                for c in ctxs:
+                    ops.paged_attention(q, out, c, view, nh, nkv, d, 1.0 / 16.0, 50.0, window)
+            run()
+            torch.cuda.synchronize()
+            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                run()
+                with torch.cuda.graph(graph, stream=side):
+                    run()
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 10 / launches * 1e3
+            n_bytes = batch * min(ctx_len, window or ctx_len) * nkv * d * 2 * 2
+            print(json.dumps({"micro": "decode attention", "batch": batch, "keys": min(ctx_len, window or ctx_len),
+                              "us_per_launch": round(us, 1), "gb_per_s": round(n_bytes / us / 1e3, 1)}))
+        del pages
+    return 0
+
+
+def micro_gemm() -> int:
+    """One square bfloat16 product (8192 cubed) on the tensor-core kernel, timed with CUDA events; one JSON line."""
+    import torch
+    from kungfu_b200 import api, ops
+    device = api.require_cuda("cuda:0")
+    n = 8192
+    x = torch.randn(n, n, device=device).bfloat16()
+    w = torch.randn(n, n, device=device).bfloat16()
+    out = torch.empty(n, n, device=device)
+    for _ in range(3):
+        ops.linear(x, w, out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        ops.linear(x, w, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 5
+    ops.raise_on_device_error()
+    print(json.dumps({"micro": "product 8192^3 bf16", "ms": round(ms, 4), "tflops": round(2.0 * n ** 3 / ms / 1e9, 1)}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -297,7 +385,12 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--micro", choices=["attention", "gemm"], help="time one kernel alone instead of the model step")
     args = ap.parse_args()
+    if args.micro == "attention":
+        return micro_attention()
+    if args.micro == "gemm":
+        return micro_gemm()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built"}))
