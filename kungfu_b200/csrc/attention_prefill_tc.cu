@@ -3,12 +3,15 @@
 //
 // A block is (tile of up to 128 consecutive rows of one request, query head).  Keys are walked in tiles of 64, which
 // is one cache page (or a 64-aligned part of one), so a tile is a handful of TMA boxes [64 keys x 64 elements].
-//   warp 4   : one lane issues the TMA loads: the Q tile once, then K and V tiles into a two-stage ring
-//   warp 5   : allocates tensor memory; one lane issues the MMAs:  S_i = Q K_i^T (M 128, N 64, K = head size) into
+//   warp 8   : one lane issues the TMA loads: the Q tile once, then K and V tiles into a two-stage ring
+//   warp 9   : allocates tensor memory; one lane issues the MMAs:  S_i = Q K_i^T (M 128, N 64, K = head size) into
 //              one of two S buffers, and O += P_i V_i (M 128, N = head size, K 64) with V as an MN-major operand
-//   warps 0-3: one thread per query row (= tensor-memory lane): read the row of S, scale, cap, mask, exponentiate,
-//              keep the running maximum and sum, round P to bfloat16 into swizzled shared memory for the second MMA,
-//              and at the end read O, divide by the sum and store the row.
+//   warps 0-7: two threads per query row (= tensor-memory lane), warps 0-3 the first 32 keys of a tile and warps 4-7
+//              the other 32: read their half of the row of S, scale, cap, mask, agree on the row's maximum through
+//              shared memory, exponentiate, keep the running maximum and their half of the sum, round P to bfloat16
+//              into swizzled shared memory for the second MMA, and at the end read their half of O's columns, divide
+//              by the sum and store.  Two warps per scheduler hide each other's tensor-memory and barrier latencies;
+//              the exponentials (three per score with the cap) are what bounds the tile.
 // The running maximum used for the exponentials is only raised when a tile's maximum exceeds it by more than 8
 // (a factor 256, harmless in bfloat16/32-bit accumulators); only then is O in tensor memory rescaled.  All of S, the
 // softmax and the sums are 32-bit.  Every wait is bounded; on a timeout an error code is recorded and the block
@@ -25,7 +28,8 @@ namespace {
 
 constexpr int BMQ = 128;           // query rows per block
 constexpr int BKV = 64;            // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
 constexpr long WAIT_LIMIT = 20L * 1000 * 1000;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;
@@ -129,6 +133,22 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 32 consecutive columns of this thread's lane, one wait for both loads
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
+          "=r"(r[16 * q + 15])
+        : "r"(taddr + 16 * q));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -163,13 +183,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint8_t* sP = sV + 2 * KV_BYTES;
   uint64_t* bars = (uint64_t*)(sP + P_BYTES);
   uint64_t* q_full = bars;                                // TMA
-  uint64_t* kv_full = bars + 1;                           // [2] TMA
-  uint64_t* kv_free = bars + 3;                           // [2] commit after P V of the tile in that stage
-  uint64_t* s_full = bars + 5;                            // [2] commit after Q K^T
-  uint64_t* p_full = bars + 7;                            // 128 softmax threads
-  uint64_t* pv_done = bars + 8;                           // commit after P V
-  uint32_t* tmem_slot = (uint32_t*)(bars + 9);
+  uint64_t* k_full = bars + 1;                            // [2] TMA; keys and values have rings of their own, so that the
+  uint64_t* v_full = bars + 3;                            // [2] next keys can load as soon as Q K^T has read the stage,
+  uint64_t* k_free = bars + 5;                            // [2] commit after Q K^T of the tile in that stage
+  uint64_t* v_free = bars + 7;                            // [2] commit after P V of the tile in that stage
+  uint64_t* s_full = bars + 9;                            // [2] commit after Q K^T
+  uint64_t* p_full = bars + 11;                           // all softmax threads
+  uint64_t* pv_done = bars + 12;                          // commit after P V
+  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
   volatile int* s_abort = (volatile int*)(tmem_slot + 1);
+  float* s_max = (float*)(tmem_slot + 2);                 // [2 tile parities][2 halves][128 rows]; later [2][128] sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -178,13 +201,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_free[s], 1); mbar_init(&s_full[s], 1); }
-    mbar_init(p_full, 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_free[s], 1); mbar_init(&v_free[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
+    mbar_init(p_full, SOFTMAX_THREADS);
     mbar_init(pv_done, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -202,7 +228,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int kt_begin = (lo / BKV) * BKV;
   const int n_tiles = req < 0 ? 0 : (pos_last - kt_begin) / BKV + 1;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---- TMA producer --------------------------------------------------------------------------------------
     if (lane == 0 && n_tiles > 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
@@ -213,25 +239,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const int* tab = table + (size_t)req * table_stride;
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i & 1;
-        if (i >= 2 && !mbar_wait(&kv_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
         const int kt = kt_begin + i * BKV;
         int page = tab[kt / page_size];
         if (page < 0) page = 0;                            // a page already given back: every key of it is masked
         const int krow = ((page * 2 + 0) * nkv + kvh) * page_size + (kt % page_size);
         const int vrow = krow + nkv * page_size;
-        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+        if (i >= 2 && !mbar_wait(&k_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
+        mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
-        for (int j = 0; j < NSUB; ++j) {
-          tma_load_2d(sK + s * KV_BYTES + j * (BKV * 128), &tm_kv, &kv_full[s], j * 64, krow);
-          tma_load_2d(sV + s * KV_BYTES + j * (BKV * 128), &tm_kv, &kv_full[s], j * 64, vrow);
-        }
+        for (int j = 0; j < NSUB; ++j) tma_load_2d(sK + s * KV_BYTES + j * (BKV * 128), &tm_kv, &k_full[s], j * 64, krow);
+        if (i >= 2 && !mbar_wait(&v_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
+        mbar_expect_tx(&v_full[s], KV_BYTES);
+#pragma unroll
+        for (int j = 0; j < NSUB; ++j) tma_load_2d(sV + s * KV_BYTES + j * (BKV * 128), &tm_kv, &v_full[s], j * 64, vrow);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---- MMA issuer ----------------------------------------------------------------------------------------
     if (lane == 0 && n_tiles > 0) {
       const uint32_t id_s = idesc(BKV, 0), id_o = idesc(D, 1);
-      bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
       auto issue_s = [&](int i) {                          // S_i = Q K_i^T into S buffer i & 1
         const int s = i & 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -243,15 +270,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           for (int k = 0; k < 4; ++k) umma(tmem_base + s * S_COLS, da + 2 * k, db + 2 * k, id_s, (j | k) ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
+        umma_commit(&k_free[s]);
       };
       if (ok) issue_s(0);
       for (int i = 0; i < n_tiles && ok; ++i) {
         const int s = i & 1;
         if (i + 1 < n_tiles) {
-          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
           if (ok) issue_s(i + 1);
         }
-        ok = ok && mbar_wait(p_full, i & 1);
+        ok = ok && mbar_wait(&v_full[s], (i >> 1) & 1) && mbar_wait(p_full, i & 1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -260,58 +288,65 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           const uint64_t db = desc_mnmajor(sV + s * KV_BYTES + k * 2048, BKV * 128);
           umma(tmem_base + O_COL, da, db, id_o, (i | k) ? 1u : 0u);
         }
-        umma_commit(&kv_free[s]);
+        umma_commit(&v_free[s]);
         umma_commit(pv_done);
       }
       if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 2); *s_abort = 1; }
     }
   } else {
-    // ---- softmax and epilogue: thread = query row ---------------------------------------------------------------
-    const int r = warp * 32 + lane;                        // row of the tile = tensor-memory lane
+    // ---- softmax and epilogue: two threads per query row, each with half of a tile's keys and half of O's columns ----------
+    const int half = warp >> 2, wq = warp & 3;             // warps 0-3: keys 0..31 of a tile; warps 4-7: keys 32..63
+    const int r = wq * 32 + lane;                          // row of the tile = tensor-memory lane
     const int prow = pos0 + r;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     const float c0 = scale * LOG2E;                                        // no cap: s2 = s * c0
     const float c1 = softcap > 0.f ? scale * 2.f * LOG2E / softcap : 0.f;   // exp(2 x / cap) = exp2(s * c1)
     const float c3 = softcap * LOG2E;
-    float m_used = -INFINITY, l_sum = 0.f;
+    constexpr int HC = D / 2;                              // O columns of this thread
+    float m_used = -INFINITY, l_sum = 0.f;                 // the maximum is the row's; the sum is this half's
     bool ok = true;
-    for (int i = 0; i < n_tiles && ok; ++i) {
+    // Every softmax thread runs every turn of this loop and meets the others at its barrier, also after a wait has run
+    // out (the waits are then skipped and the numbers are garbage that nobody stores): nobody is left at a barrier.
+    for (int i = 0; i < n_tiles; ++i) {
       const int sb = i & 1;
-      ok = mbar_wait(&s_full[sb], (i >> 1) & 1);
-      if (!ok) break;
+      ok = ok && mbar_wait(&s_full[sb], (i >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kt = kt_begin + i * BKV;
-      float sv[64];
-      tmem_ld64(lane_addr + sb * S_COLS, sv);
+      const int kt = kt_begin + i * BKV + half * 32;       // first key of this thread's half
+      float sv[32];
+      tmem_ld32(lane_addr + sb * S_COLS + half * 32, sv);
       // Scores in base-2 units: s2 = log2(e) * cap * tanh(scale * s / cap) = c3 - 2 c3 / (exp2(s * c1) + 1), or
-      // s * c0 without a cap.  A tile that every row of this warp sees whole skips the mask.
-      const bool whole = (kt + BKV - 1 <= pos0 + warp * 32) && (window <= 0 || pos0 + warp * 32 + 31 - kt < window);
+      // s * c0 without a cap.  A half tile that every row of this warp sees whole skips the mask.
+      const bool whole = (kt + 31 <= pos0 + wq * 32) && (window <= 0 || pos0 + wq * 32 + 31 - kt < window);
       float m_tile = -INFINITY;
       if (softcap > 0.f) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
+        for (int c = 0; c < 32; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
       } else {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) sv[c] *= c0;
+        for (int c = 0; c < 32; ++c) sv[c] *= c0;
       }
       if (!whole) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int j = kt + c;
           const bool seen = j <= prow && (window <= 0 || prow - j < window);
           sv[c] = seen ? sv[c] : -INFINITY;
         }
       }
 #pragma unroll
-      for (int c = 0; c < 64; ++c) m_tile = fmaxf(m_tile, sv[c]);
+      for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, sv[c]);
+      // the row's maximum over both halves (slots alternate with the tile's parity, so one barrier per tile is enough)
+      s_max[(sb * 2 + half) * BMQ + r] = m_tile;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      m_tile = fmaxf(m_tile, s_max[(sb * 2 + (half ^ 1)) * BMQ + r]);
       const bool raise = m_tile > m_used + RESCALE_STEP;   // also true for the first finite maximum
       const float m_new = raise ? m_tile : m_used;
       const float corr = raise ? ex2_fast(m_used - m_new) : 1.f;   // exp2(-inf) = 0 when nothing was accumulated yet
       const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen nothing yet: exp2(-inf - 0) = 0
       float l_add = 0.f;
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < 32; c += 2) {
         const float p0 = ex2_fast(sv[c] - m_sub);
         const float p1 = ex2_fast(sv[c + 1] - m_sub);
         l_add += p0 + p1;
@@ -321,26 +356,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       l_sum = l_sum * corr + l_add;
       m_used = m_new;
       if (i > 0) {                                          // P V of the previous tile must be done: O is at rest, P is free
-        ok = mbar_wait(pv_done, (i - 1) & 1);
-        if (!ok) break;
+        ok = ok && mbar_wait(pv_done, (i - 1) & 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, raise)) {              // rescale O (all lanes of the warp take part)
+        if (__any_sync(0xffffffffu, raise)) {              // rescale this thread's half of O (all lanes of the warp take part)
 #pragma unroll 1
-          for (int c = 0; c < D; c += 16) {
+          for (int c = 0; c < HC; c += 16) {
             float o[16];
-            tmem_ld16(lane_addr + O_COL + c, o);
+            tmem_ld16(lane_addr + O_COL + half * HC + c, o);
 #pragma unroll
             for (int e = 0; e < 16; ++e) o[e] *= corr;
-            tmem_st16(lane_addr + O_COL + c, o);
+            tmem_st16(lane_addr + O_COL + half * HC + c, o);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // P row -> shared memory, K-major with the 128-byte swizzle (chunk index XOR row % 8)
+      // this half of the P row -> shared memory, K-major with the 128-byte swizzle (chunk index XOR row % 8)
       uint8_t* prow_ptr = sP + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      for (int q = 0; q < 4; ++q) {
+        const int ch = half * 4 + q;
+        const uint4 v = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         *reinterpret_cast<uint4*>(prow_ptr + ((ch ^ (r & 7)) << 4)) = v;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -350,13 +385,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (ok && n_tiles > 0) ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
     if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 3); *s_abort = 1; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // the row's sum is the two halves' sums (both were scaled by the same maxima); every softmax thread reaches this
+    asm volatile("bar.sync 2, 256;" ::: "memory");          // the maxima in s_max have been read by everyone
+    s_max[half * BMQ + r] = l_sum;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    l_sum = s_max[r] + s_max[BMQ + r];
     if (ok && n_tiles > 0 && *s_abort == 0) {
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      __nv_bfloat16* orow = out + ((size_t)(row0 + r) * nh + h) * D;
+      __nv_bfloat16* orow = out + ((size_t)(row0 + r) * nh + h) * D + half * HC;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 16) {
+      for (int c = 0; c < HC; c += 16) {
         float o[16];
-        tmem_ld16(lane_addr + O_COL + c, o);               // every lane of the warp takes part in the load
+        tmem_ld16(lane_addr + O_COL + half * HC + c, o);   // every lane of the warp takes part in the load
         if (r < nrows) {
           uint32_t w[8];
 #pragma unroll
@@ -372,7 +412,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -428,7 +468,7 @@ template <int D>
 int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
            const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
            float scale, float softcap, int window, void* out, int* error_flag, cudaStream_t stream) {
-  const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256;
+  const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256 + 4 * BMQ * 4;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
