@@ -425,6 +425,61 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
+def _plant(pages, table, req, j, kvh, P, key=None, value=None):
+    """Overwrite key and/or value j of a request in its pages (host tensors)."""
+    pg = int(table[req, j // P])
+    if key is not None:
+        pages[pg, 0, kvh, j % P] = key.to(pages.dtype)
+    if value is not None:
+        pages[pg, 1, kvh, j % P] = value.to(pages.dtype)
+
+
+@pytest.mark.parametrize("path", ["decode_mma", "decode_simt", "prompt_rows", "generic_f32"])
+@pytest.mark.parametrize("nh,nkv,d", [(8, 4, 256), (4, 1, 128), (6, 2, 64)])
+def test_attention_finds_a_planted_key(ops, path, nh, nkv, d):
+    """Random keys hide a key that is wrongly skipped among thousands (its weight is 1/n).  Here one key is made to match
+    the query of head 0, so that it takes almost all the weight: the output must be that key's value when the key is
+    visible (the first key of a request, a page's last and first slot, the oldest key inside the window, the row's own
+    key) and must not be when it is just outside the window."""
+    P, n = 64, 3000
+    window = 1000
+    dtype = torch.float32 if path == "generic_f32" else torch.bfloat16
+    pos = n - 1
+    scale = 1.0 / math.sqrt(d)
+    cases = [(None, 0), (None, 63), (None, 64), (None, 1471), (None, pos), (window, pos - window + 1), (window, pos - window),
+             (window, pos - 1), (window, 0)]
+    for win, j in cases:
+        pages, table, ks, vs = _paged_setup(dtype, nh, nkv, d, P, [n, 10], seed=40 + j % 7, scramble=True)
+        g = torch.Generator().manual_seed(41)
+        rows = [(0, pos)] if path != "prompt_rows" else [(0, p) for p in range(pos - 69, pos + 1)]
+        q = torch.randn(len(rows), nh, d, generator=g)
+        qv = q[-1, 0]                                           # head 0 of the last row looks for key j
+        key = qv * (30.0 / (scale * float(qv @ qv)))            # score 30 before the cap, against scores of about +-1
+        marker_value = torch.full((d,), 5.0)
+        marker_value[::2] = -3.0
+        _plant(pages, table, 0, j, 0, P, key=key, value=marker_value)
+        ctx_rows = list(range(len(rows)))
+        dec, pre = (ctx_rows, []) if path.startswith("decode") else ([], ctx_rows)
+        if path == "generic_f32":
+            dec, pre = None, None
+        ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+                   torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
+        out = torch.full((len(rows), nh * d), float("nan"), dtype=dtype, device=DEV)
+        ops.decode_on_tensor_cores = path != "decode_simt"
+        try:
+            ops.paged_attention(q.view(len(rows), nh * d).to(dtype).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d,
+                                scale, 50.0, win)
+        finally:
+            ops.decode_on_tensor_cores = True
+        got = out.view(len(rows), nh, d)[-1, 0].float().cpu()
+        visible = j <= pos and (win is None or pos - j < win)
+        dist = float((got - marker_value).norm() / marker_value.norm())
+        if visible:
+            assert dist < 2e-2, (path, win, j, dist)
+        else:
+            assert dist > 0.5, (path, win, j, dist)
+
+
 @pytest.mark.parametrize("nh,nkv,d,P,window,rot", [(8, 4, 256, 64, 1000, 256), (4, 2, 16, 4, 8, 16), (6, 2, 32, 16, None, 16),
                                                    (16, 2, 128, 64, 4096, 128), (5, 5, 64, 32, None, 0), (8, 1, 128, 16, 33, 64)])
 @pytest.mark.parametrize("writes", [True, False])
