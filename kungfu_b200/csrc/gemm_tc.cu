@@ -631,12 +631,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = lane_addr + buf * PN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < PN; c0 += 16) {
-        float v[16], u[16];
-        tmem_ld16(acc + c0, v);
-        if (GATED) tmem_ld16(acc + PN + c0, u);
+      for (int c0 = 0; c0 < PN; c0 += 32) {                      // 32 tokens per wait on tensor memory
+        float v[32], u[32];
+        if (GATED) tmem_ld32x2(acc + c0, acc + PN + c0, v, u);
+        else tmem_ld32(acc + c0, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 32; ++j) {
           const int t = t0 + c0 + j;
           if (t < T && f < n_feat) {
             float r;

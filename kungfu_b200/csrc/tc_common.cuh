@@ -96,6 +96,39 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive columns of this thread's lane with one wait for both loads (the wait is most of a load's cost)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
+          "=r"(r[16 * q + 15])
+        : "r"(taddr + 16 * q));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Two 32-column ranges (gate and up accumulators) with one wait
+__device__ __forceinline__ void tmem_ld32x2(uint32_t ta, uint32_t tb, float* v, float* u) {
+  uint32_t r[64];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
+          "=r"(r[16 * q + 15])
+        : "r"((q < 2 ? ta : tb) + 16 * (q & 1)));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { v[i] = __uint_as_float(r[i]); u[i] = __uint_as_float(r[32 + i]); }
+}
+
 // Activations of the gated epilogue through the hardware exponential and reciprocal (relative error ~1e-6, far below
 // the bfloat16 rounding of the result).  The 32-bit path of the engine uses tanhf/expf in its own kernel.
 __device__ __forceinline__ float act_fast(float x, int act) {
