@@ -174,7 +174,7 @@ def run_ours(args) -> dict:
     from kungfu_b200 import api, ops
     from kungfu_b200.engine import StepEntry
     from kungfu_b200.engine.engine import Engine
-    from kungfu_b200.engine.scheduler import Request, RUNNING
+    from kungfu_b200.engine.scheduler import Request
     from kungfu_b200.sampling import Sampling
 
     pk, pk_src = peaks()
@@ -255,9 +255,8 @@ def run_ours(args) -> dict:
         req = Request(rid, prompt, Sampling(temperature=0.0), max_tokens=10 ** 9, eos=(), ignore_eos=True)
         fill_cache(runner, rid, start - 1, None)      # all but the last prompt token are "already run"
         req.n_cached = start - 1
-        req.status = RUNNING
         eng.requests[rid] = req
-        eng.scheduler.running.append(req)
+        eng.scheduler.adopt(req)
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()

@@ -69,6 +69,24 @@ def host_library():
                                        ctypes.c_int, ctypes.c_void_p]
         lib.kf_step_fill.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_void_p,
                                                                                                ctypes.c_void_p]
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        lib.kf_sched_create.restype = vp
+        lib.kf_sched_create.argtypes = [vp, ci, ci]
+        lib.kf_sched_destroy.argtypes = [vp]
+        lib.kf_sched_add.argtypes = [vp, i64, ci, ci, ci]
+        lib.kf_sched_adopt.argtypes = [vp, i64, ci, ci, ci, ci]
+        lib.kf_sched_forget.argtypes = [vp, i64]
+        lib.kf_sched_schedule.argtypes = [vp, vp, ci, vp, ci, vp]
+        lib.kf_sched_advance.argtypes = [vp, i64, ci]
+        lib.kf_sched_on_token.argtypes = [vp, i64, ci]
+        lib.kf_sched_finish.argtypes = [vp, i64]
+        lib.kf_sched_preempt_last.argtypes = [vp, i64]
+        lib.kf_sched_preempt_last.restype = i64
+        lib.kf_sched_n_preemptions.argtypes = [vp]
+        lib.kf_sched_n_preemptions.restype = ctypes.c_long
+        lib.kf_sched_counts.argtypes = [vp, vp, vp]
+        lib.kf_sched_lists.argtypes = [vp, vp, vp]
+        lib.kf_sched_state.argtypes = [vp, i64, vp]
         _host = lib
     return _host
 
@@ -241,6 +259,26 @@ class CacheManager:
             if isinstance(need, FixedState):
                 self.storage[s][slot].zero_()
         return slot
+
+    def new_key(self) -> int:
+        """A fresh 64-bit key for a request that the native scheduler will admit by itself later."""
+        key = self._next_key
+        self._next_key += 1
+        return key
+
+    def adopt(self, request, key: int, slot: int) -> None:
+        """The native side has admitted `request` under `key` into state slot `slot`: record it here (and zero its
+        fixed-size state)."""
+        if request in self._key:
+            raise CacheError(f"request {request!r} is already live")
+        self._key[request] = int(key)
+        for s, need in enumerate(self.needs):
+            if isinstance(need, FixedState):
+                self.storage[s][slot].zero_()
+
+    def forget(self, request) -> None:
+        """The native side has released `request` (finished or preempted): drop it here."""
+        self._key.pop(request, None)
 
     def pages_needed(self, request, n_new: int) -> list[int]:
         """Pages each group must still take so the request can hold `n_new` more tokens."""

@@ -149,11 +149,11 @@ HOST_LIB_NAME = "libkungfu_b200_host.so"
 
 
 def build_host() -> str:
-    """Compile the host-side runtime (host_runtime.cpp: page pools, block tables, the step's integer block) with the
+    """Compile the host-side runtime (host_runtime.cpp: page pools, block tables, the step's integer block, the scheduler) with the
     C++ compiler; it needs neither nvcc nor a GPU.  Returns the path of the shared library."""
     out = build_dir()
     src = os.path.join(HERE, "host_runtime.cpp")
-    tag = _file_hash(src, "host-v2")
+    tag = _file_hash(src, "host-v3")
     lib = os.path.join(out, HOST_LIB_NAME)
     stamp_path = os.path.join(out, "host_stamp")
 

@@ -1,6 +1,7 @@
-// Host-side runtime of the engine, in C++: the page pools and block tables of the cache manager, and the builder of
-// the integer block every step sends to the device.  The Python classes of kungfu_b200/cache and
-// kungfu_b200/engine/step.py are thin wrappers over the functions exported here (C ABI, called through ctypes).
+// Host-side runtime of the engine, in C++: the page pools and block tables of the cache manager, the builder of the
+// integer block every step sends to the device, and the scheduler that plans each step.  The Python classes of
+// kungfu_b200/cache, kungfu_b200/engine/step.py and kungfu_b200/engine/scheduler.py are thin wrappers over the functions
+// exported here (C ABI, called through ctypes).
 //
 // The reference keeps the corresponding state in Rust (per-slot ring caches sized at plan time,
 // crates/kf-core/src/plan.rs:59-64 and crates/kf-backend-cuda/src/exec.rs:1466-1498; per-pass integer inputs staged
@@ -10,6 +11,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <deque>
 #include <unordered_map>
 #include <vector>
 
@@ -355,5 +357,328 @@ KF_HOST_API int kf_step_fill(void* h, int n_entries, const int64_t* reqs, const 
     max_kv = c->max_context;                              // a captured graph's split plan must not depend on the step
   }
   info[5] = n_dec; info[6] = n_pre; info[7] = n_tiles; info[8] = n_wide; info[9] = max_kv; info[10] = max_rows;
+  return OK;
+}
+
+
+// ---- scheduler -------------------------------------------------------------------------------------------------------
+// Plans one mixed step at a time over the requests it knows by 64-bit key (the keys of the cache manager above):
+//   1. every decoding request gets its one token, oldest first; out of pages -> the request admitted last is preempted
+//      (everything given back, to be recomputed from its prompt and its own output) and the request tries again;
+//   2. the rest of the token budget goes to prompt portions of running requests, in order of admission;
+//   3. waiting requests are admitted first come first served while a state slot and the pages of their whole pending
+//      prompt are free; nothing is admitted in a step that had to preempt.
+// A request that cannot fit with the whole pool to itself finishes with "no_fit".  The reference plans per pass in
+// Rust too (crates/kf-serve/src/engine.rs:396-430 admit / prefill chunk / decode / retire); there prompt rows and decode
+// rows never share a pass and a context that cannot fit is refused at plan time (crates/kf-engine/src/plan.rs:213-215).
+// Token values stay with the caller: the scheduler needs counts only.
+namespace {
+
+enum { ST_WAITING = 0, ST_RUNNING = 1, ST_FINISHED = 2 };
+enum { EV_ADMITTED = 1, EV_PREEMPTED = 2, EV_NO_FIT = 3 };
+enum { FIN_NONE = 0, FIN_EOS = 1, FIN_LENGTH = 2, FIN_CONTEXT = 3 };
+
+struct SReq {
+  int64_t key = 0;
+  int prompt_len = 0, out_len = 0, n_cached = 0, max_tokens = 0, status = ST_WAITING, n_preempted = 0;
+};
+struct SPortion {
+  int64_t key;
+  int start, n, wants;
+};
+struct Sched {
+  Cache* cache = nullptr;
+  int max_batch_tokens = 0, max_requests = 0;
+  std::deque<int64_t> waiting;
+  std::vector<int64_t> running;                      // in order of admission
+  std::unordered_map<int64_t, SReq> reqs;
+  long n_preemptions = 0;
+  std::vector<SPortion> plan;
+  std::vector<int64_t> events;                       // (code, key, argument) triples of the last schedule()
+
+  int G() const { return (int)cache->groups.size(); }
+  static int n_pending(const SReq& r) { return r.prompt_len + r.out_len - r.n_cached; }
+  static bool decoding(const SReq& r) { return r.status == ST_RUNNING && n_pending(r) == 1 && r.out_len > 0; }
+  std::vector<int> free_pages() const {
+    std::vector<int> f(cache->groups.size());
+    for (size_t g = 0; g < f.size(); ++g) f[g] = cache->groups[g].pool.n_free();
+    return f;
+  }
+  std::vector<int> pages_needed(int64_t key, int n) const {
+    std::vector<int> out(cache->groups.size(), 0);
+    kf_cache_pages_needed(cache, key, n, out.data());
+    return out;
+  }
+  static bool covers(const std::vector<int>& need, const std::vector<int>& free) {
+    for (size_t g = 0; g < need.size(); ++g)
+      if (need[g] > free[g]) return false;
+    return true;
+  }
+  static bool take(const std::vector<int>& need, std::vector<int>& free) {
+    if (!covers(need, free)) return false;
+    for (size_t g = 0; g < need.size(); ++g) free[g] -= need[g];
+    return true;
+  }
+  void event(int code, int64_t key, int64_t arg) { events.push_back(code); events.push_back(key); events.push_back(arg); }
+
+  bool fits_at_all(const SReq& r) const {
+    int total = r.prompt_len + r.max_tokens;
+    if (total > cache->max_context) total = cache->max_context;
+    if (r.prompt_len >= cache->max_context) return false;
+    const int P = cache->page_size;
+    for (const Group& g : cache->groups) {
+      int need = total;
+      if (g.window >= 0) need = std::min(total, g.window + P + std::min(max_batch_tokens, r.prompt_len));
+      if (ceil_div(need, P) > g.pool.n) return false;
+    }
+    return true;
+  }
+  std::vector<int> admission_pages(const SReq& r) const {
+    const int P = cache->page_size;
+    std::vector<int> out;
+    for (const Group& g : cache->groups) {
+      int need = n_pending(r);
+      if (g.window >= 0) need = std::min(need, g.window + P + std::min(max_batch_tokens, n_pending(r)));
+      out.push_back(ceil_div(need, P));
+    }
+    return out;
+  }
+  // the most recently admitted running request other than `keep` goes back to the front of the waiting queue
+  int64_t preempt_last(int64_t keep) {
+    for (int i = (int)running.size() - 1; i >= 0; --i) {
+      const int64_t key = running[i];
+      if (key == keep) continue;
+      running.erase(running.begin() + i);
+      kf_cache_release(cache, key);
+      SReq& r = reqs[key];
+      r.status = ST_WAITING;
+      r.n_cached = 0;
+      r.n_preempted += 1;
+      n_preemptions += 1;
+      waiting.push_front(key);
+      event(EV_PREEMPTED, key, 0);
+      return key;
+    }
+    return 0;
+  }
+  void finish(int64_t key) {
+    SReq& r = reqs[key];
+    auto it = std::find(running.begin(), running.end(), key);
+    if (it != running.end()) {
+      running.erase(it);
+      kf_cache_release(cache, key);
+    } else {
+      auto iw = std::find(waiting.begin(), waiting.end(), key);
+      if (iw != waiting.end()) waiting.erase(iw);
+    }
+    r.status = ST_FINISHED;
+  }
+  // the most tokens (<= n_max) of a running request whose pages the free counts still cover
+  int largest_portion(int64_t key, int n_max, const std::vector<int>& free) const {
+    const int P = cache->page_size;
+    int n = n_max;
+    while (n > 0) {
+      if (covers(pages_needed(key, n), free)) return n;
+      const int have = kf_cache_length(cache, key);
+      n = std::min(n - 1, ((have + n - 1) / P) * P - have);     // the largest count that needs one page fewer
+    }
+    return 0;
+  }
+  bool planned(int64_t key) const {
+    for (const SPortion& p : plan)
+      if (p.key == key) return true;
+    return false;
+  }
+
+  void schedule() {
+    events.clear();
+    for (;;) {
+      plan.clear();
+      std::vector<int> free = free_pages();
+      int budget = max_batch_tokens;
+      bool preempted = false;
+      // 1. decoding requests
+      size_t i = 0;
+      while (i < running.size()) {
+        const int64_t key = running[i];
+        const SReq& r = reqs[key];
+        if (!decoding(r)) { ++i; continue; }
+        if (budget <= 0) break;
+        if (take(pages_needed(key, 1), free)) {
+          plan.push_back({key, r.n_cached, 1, 1});
+          --budget;
+          ++i;
+          continue;
+        }
+        const int64_t victim = preempt_last(key);
+        if (victim == 0) {                                       // alone and still no page
+          finish(key);
+          event(EV_NO_FIT, key, 0);
+          continue;
+        }
+        preempted = true;
+        for (size_t k = 0; k < plan.size();) {                   // it had been planned in this very call: undo
+          if (plan[k].key == victim) { budget += plan[k].n; plan.erase(plan.begin() + k); } else ++k;
+        }
+        free = free_pages();
+        for (const SPortion& p : plan) {                         // re-apply what is already planned
+          const std::vector<int> need = pages_needed(p.key, p.n);
+          for (size_t g = 0; g < need.size(); ++g) free[g] -= need[g];
+        }
+        i = (size_t)(std::find(running.begin(), running.end(), key) - running.begin());
+      }
+      // 2. prompt portions of running requests
+      for (const int64_t key : running) {
+        if (budget <= 0) break;
+        const SReq& r = reqs[key];
+        if (decoding(r) || n_pending(r) == 0 || planned(key)) continue;
+        const int n = largest_portion(key, std::min(budget, n_pending(r)), free);
+        if (n <= 0) continue;
+        take(pages_needed(key, n), free);
+        plan.push_back({key, r.n_cached, n, n == n_pending(r) ? 1 : 0});
+        budget -= n;
+      }
+      // 3. admission
+      while (!waiting.empty() && budget > 0 && (int)running.size() < max_requests) {
+        const int64_t key = waiting.front();
+        SReq& r = reqs[key];
+        if (!fits_at_all(r)) {
+          waiting.pop_front();
+          finish(key);
+          event(EV_NO_FIT, key, 0);
+          continue;
+        }
+        if (preempted || !covers(admission_pages(r), free)) break;
+        const int n = std::min(budget, n_pending(r));
+        waiting.pop_front();
+        const int slot = kf_cache_add_request(cache, key);
+        if (slot < 0) { waiting.push_front(key); break; }        // no state slot after all
+        r.status = ST_RUNNING;
+        running.push_back(key);
+        event(EV_ADMITTED, key, slot);
+        take(pages_needed(key, n), free);
+        plan.push_back({key, 0, n, n == n_pending(r) ? 1 : 0});
+        budget -= n;
+      }
+      if (plan.empty() && !running.empty()) {
+        bool any_decoding = false;
+        for (const int64_t key : running) any_decoding = any_decoding || decoding(reqs[key]);
+        if (!any_decoding) {
+          // every running request is mid-prompt and none can get a page: free the youngest so that the oldest moves
+          if (running.size() > 1) {
+            preempt_last(running[0]);
+            continue;
+          }
+          const int64_t key = running[0];
+          finish(key);
+          event(EV_NO_FIT, key, 0);
+        }
+      }
+      return;
+    }
+  }
+};
+
+}  // namespace
+
+KF_HOST_API void* kf_sched_create(void* cache, int max_batch_tokens, int max_requests) {
+  Sched* s = new Sched();
+  s->cache = (Cache*)cache;
+  s->max_batch_tokens = max_batch_tokens;
+  s->max_requests = max_requests;
+  return s;
+}
+KF_HOST_API void kf_sched_destroy(void* h) { delete (Sched*)h; }
+
+KF_HOST_API int kf_sched_add(void* h, int64_t key, int prompt_len, int out_len, int max_tokens) {
+  Sched* s = (Sched*)h;
+  if (s->reqs.count(key)) return E_ALREADY_LIVE;
+  SReq r;
+  r.key = key; r.prompt_len = prompt_len; r.out_len = out_len; r.max_tokens = max_tokens;
+  s->reqs.emplace(key, r);
+  s->waiting.push_back(key);
+  return OK;
+}
+// a request that already holds its cache (admitted and filled by the caller): joins the running list as it is
+KF_HOST_API int kf_sched_adopt(void* h, int64_t key, int prompt_len, int out_len, int n_cached, int max_tokens) {
+  Sched* s = (Sched*)h;
+  if (s->reqs.count(key) || !s->cache->reqs.count(key)) return E_NOT_LIVE;
+  SReq r;
+  r.key = key; r.prompt_len = prompt_len; r.out_len = out_len; r.n_cached = n_cached; r.max_tokens = max_tokens;
+  r.status = ST_RUNNING;
+  s->reqs.emplace(key, r);
+  s->running.push_back(key);
+  return OK;
+}
+KF_HOST_API void kf_sched_forget(void* h, int64_t key) { ((Sched*)h)->reqs.erase(key); }
+
+// Plans a step.  portions: up to cap_portions x 4 values (key, start, n, wants logits); events: up to cap_events x 3
+// values (code 1 admitted / 2 preempted / 3 finished with no_fit, key, state slot for admissions).  counts[0], [1].
+KF_HOST_API int kf_sched_schedule(void* h, int64_t* portions, int cap_portions, int64_t* events, int cap_events, int* counts) {
+  Sched* s = (Sched*)h;
+  s->schedule();
+  const int np = (int)s->plan.size(), ne = (int)s->events.size() / 3;
+  counts[0] = np;
+  counts[1] = ne;
+  if (np > cap_portions || ne > cap_events) return E_INCONSISTENT;
+  for (int i = 0; i < np; ++i) {
+    portions[4 * i] = s->plan[i].key; portions[4 * i + 1] = s->plan[i].start;
+    portions[4 * i + 2] = s->plan[i].n; portions[4 * i + 3] = s->plan[i].wants;
+  }
+  memcpy(events, s->events.data(), s->events.size() * sizeof(int64_t));
+  return OK;
+}
+KF_HOST_API int kf_sched_advance(void* h, int64_t key, int n) {
+  Sched* s = (Sched*)h;
+  auto it = s->reqs.find(key);
+  if (it == s->reqs.end()) return E_NOT_LIVE;
+  it->second.n_cached += n;
+  return OK;
+}
+// A sampled token: returns 0, or the finish reason (1 eos, 2 length, 3 context) after finishing and freeing the request.
+KF_HOST_API int kf_sched_on_token(void* h, int64_t key, int is_eos) {
+  Sched* s = (Sched*)h;
+  auto it = s->reqs.find(key);
+  if (it == s->reqs.end()) return -E_NOT_LIVE;
+  SReq& r = it->second;
+  r.out_len += 1;
+  int reason = FIN_NONE;
+  if (is_eos) reason = FIN_EOS;
+  else if (r.out_len >= r.max_tokens) reason = FIN_LENGTH;
+  else if (r.prompt_len + r.out_len >= s->cache->max_context) reason = FIN_CONTEXT;
+  if (reason != FIN_NONE) s->finish(key);
+  return reason;
+}
+KF_HOST_API int kf_sched_finish(void* h, int64_t key) {
+  Sched* s = (Sched*)h;
+  if (!s->reqs.count(key)) return E_NOT_LIVE;
+  s->finish(key);
+  return OK;
+}
+KF_HOST_API int64_t kf_sched_preempt_last(void* h, int64_t keep) {
+  Sched* s = (Sched*)h;
+  s->events.clear();
+  return s->preempt_last(keep);
+}
+KF_HOST_API long kf_sched_n_preemptions(void* h) { return ((Sched*)h)->n_preemptions; }
+KF_HOST_API int kf_sched_counts(void* h, int* n_waiting, int* n_running) {
+  Sched* s = (Sched*)h;
+  *n_waiting = (int)s->waiting.size();
+  *n_running = (int)s->running.size();
+  return OK;
+}
+// the queues in order: waiting first, then running (caps as given by kf_sched_counts)
+KF_HOST_API int kf_sched_lists(void* h, int64_t* waiting, int64_t* running) {
+  Sched* s = (Sched*)h;
+  std::copy(s->waiting.begin(), s->waiting.end(), waiting);
+  std::copy(s->running.begin(), s->running.end(), running);
+  return OK;
+}
+// (status, n_cached, n_preempted, out_len) of a request
+KF_HOST_API int kf_sched_state(void* h, int64_t key, int* out) {
+  Sched* s = (Sched*)h;
+  auto it = s->reqs.find(key);
+  if (it == s->reqs.end()) return E_NOT_LIVE;
+  out[0] = it->second.status; out[1] = it->second.n_cached; out[2] = it->second.n_preempted; out[3] = it->second.out_len;
   return OK;
 }

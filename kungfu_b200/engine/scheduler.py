@@ -18,10 +18,11 @@ not fit even with the whole pool to itself is failed with reason `no_fit` (the r
 context at plan time, crates/kf-engine/src/plan.rs:213-215).
 
 The scheduler only decides; it reads page accounting from the cache manager and changes nothing there except
-through `add_request`/`release`.
+by admitting and releasing requests.  The decisions themselves are native code (see `Scheduler`).
 """
 from __future__ import annotations
 
+import ctypes
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Hashable
@@ -84,6 +85,12 @@ class Portion:
 
 
 class Scheduler:
+    """The decisions are taken by the native scheduler (`kungfu_b200/csrc/host_runtime.cpp`, which also owns the page
+    accounting it reads); this class keeps the `Request` objects (token values, sampling state) in step with it and
+    offers the queues as lists of those objects."""
+
+    _FINISH = {1: "eos", 2: "length", 3: "context"}
+
     def __init__(self, cache, *, max_batch_tokens: int = 512, max_requests: int | None = None):
         self.cache = cache
         self.max_batch_tokens = int(max_batch_tokens)
@@ -91,193 +98,143 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []          # in order of admission
         self.finished: list[Request] = []
-        self.n_preemptions = 0
+        self._lib = cache._lib
+        self._h = ctypes.c_void_p(self._lib.kf_sched_create(cache._h, self.max_batch_tokens, self.max_requests))
+        self._by_key: dict[int, Request] = {}
+        self._key_of: dict[int, int] = {}         # id(request object) -> key
+        cap = 4 * (self.max_requests + 8)
+        self._portions = (ctypes.c_int64 * (4 * cap))()
+        self._events = (ctypes.c_int64 * (3 * 4 * cap))()
+        self._cap_portions, self._cap_events = cap, 4 * cap
+        self._counts = (ctypes.c_int * 2)()
+        self._state = (ctypes.c_int * 4)()
+
+    def __del__(self):
+        if getattr(self, "_h", None) and getattr(self.cache, "_h", None):
+            self._lib.kf_sched_destroy(self._h)
+        self._h = None
 
     # ---- queue ---------------------------------------------------------------------------------------
     def add(self, req: Request) -> None:
         if not req.prompt:
             raise ValueError(f"request {req.id!r} has an empty prompt")
+        key = self.cache.new_key()
+        if self._lib.kf_sched_add(self._h, key, len(req.prompt), len(req.output), int(req.max_tokens)) != 0:
+            raise ValueError(f"request {req.id!r} is already known to the scheduler")
         req.status = WAITING
+        self._by_key[key] = req
+        self._key_of[id(req)] = key
         self.waiting.append(req)
+
+    def adopt(self, req: Request) -> None:
+        """A request whose prompt (all but `n_pending` tokens) the caller has already put into the cache under
+        `req.id`: it joins the running requests as it is (measurement set-ups use this to start at a long context)."""
+        key = self.cache.key_of(req.id)
+        if self._lib.kf_sched_adopt(self._h, key, len(req.prompt), len(req.output), int(req.n_cached), int(req.max_tokens)) != 0:
+            raise ValueError(f"request {req.id!r} cannot be adopted: it must be live in the cache and new to the scheduler")
+        req.status = RUNNING
+        self._by_key[key] = req
+        self._key_of[id(req)] = key
+        self.running.append(req)
 
     @property
     def idle(self) -> bool:
         return not self.waiting and not self.running
 
-    # ---- page arithmetic --------------------------------------------------------------------------------
-    def _pages_for(self, req: Request, n_new: int, live: bool) -> list[int]:
-        if live:
-            return self.cache.pages_needed(req.id, n_new)
-        want = -(-n_new // self.cache.page_size)
-        return [want for _ in self.cache.groups]
+    @property
+    def n_preemptions(self) -> int:
+        return int(self._lib.kf_sched_n_preemptions(self._h))
 
-    def _fits_at_all(self, req: Request) -> bool:
-        """Could the request run with the whole pool to itself?  Worst case per group: its full length, or for a
-        windowed group the window plus one portion."""
-        total = len(req.prompt) + req.max_tokens
-        if total > self.cache.max_context:
-            total = self.cache.max_context
-        if len(req.prompt) >= self.cache.max_context:
-            return False
-        P = self.cache.page_size
-        for g in self.cache.groups:
-            need = total
-            if g.window is not None:
-                need = min(total, g.window + P + min(self.max_batch_tokens, len(req.prompt)))
-            if -(-need // P) > g.pool.n_pages:
-                return False
-        return True
+    def _key(self, req: Request) -> int:
+        try:
+            return self._key_of[id(req)]
+        except KeyError:
+            raise ValueError(f"request {req.id!r} is not known to the scheduler") from None
 
-    def _admission_pages(self, req: Request) -> list[int]:
-        """Pages per group that must be free to admit `req`: its whole pending prompt (a windowed group never
-        holds more than the window, a page of slack and one portion)."""
-        P = self.cache.page_size
-        out = []
-        for g in self.cache.groups:
-            need = req.n_pending
-            if g.window is not None:
-                need = min(need, g.window + P + min(self.max_batch_tokens, req.n_pending))
-            out.append(-(-need // P))
-        return out
+    def _sync(self) -> None:
+        """Bring the lists and the requests' counters in line with the native state."""
+        nw, nr = ctypes.c_int(0), ctypes.c_int(0)
+        self._lib.kf_sched_counts(self._h, ctypes.byref(nw), ctypes.byref(nr))
+        w = (ctypes.c_int64 * max(nw.value, 1))()
+        r = (ctypes.c_int64 * max(nr.value, 1))()
+        self._lib.kf_sched_lists(self._h, w, r)
+        self.waiting = deque(self._by_key[k] for k in w[:nw.value])
+        self.running = [self._by_key[k] for k in r[:nr.value]]
+
+    def _apply_events(self, n_events: int) -> None:
+        for i in range(n_events):
+            code, key, arg = self._events[3 * i], self._events[3 * i + 1], self._events[3 * i + 2]
+            req = self._by_key[key]
+            if code == 1:                                   # admitted: the native cache gave it a state slot
+                self.cache.adopt(req.id, key, int(arg))
+                req.status = RUNNING
+            elif code == 2:                                 # preempted: everything given back, to be recomputed
+                self.cache.forget(req.id)
+                req.status = WAITING
+                req.n_cached = 0
+                req.n_preempted += 1
+            elif code == 3:                                 # cannot fit even alone
+                self._retire(req, key, "no_fit")
+
+    def _retire(self, req: Request, key: int, reason: str) -> None:
+        req.finish_reason = reason
+        req.status = FINISHED
+        if req.id in self.cache and self.cache.key_of(req.id) == key:
+            self.cache.forget(req.id)
+        self.finished.append(req)
+        self._lib.kf_sched_forget(self._h, key)
+        del self._by_key[key]
+        del self._key_of[id(req)]
 
     # ---- decisions ---------------------------------------------------------------------------------------
     def preempt_last(self, keep: Request | None = None) -> Request | None:
         """Take the most recently admitted running request (other than `keep`) out, to be recomputed later."""
-        for req in reversed(self.running):
-            if req is keep:
-                continue
-            self.running.remove(req)
-            self.cache.release(req.id)
-            req.status = WAITING
-            req.n_cached = 0
-            req.n_preempted += 1
-            self.n_preemptions += 1
-            self.waiting.appendleft(req)
-            return req
-        return None
+        key = self._lib.kf_sched_preempt_last(self._h, self._key(keep) if keep is not None else 0)
+        if key == 0:
+            return None
+        req = self._by_key[key]
+        self.cache.forget(req.id)
+        req.status = WAITING
+        req.n_cached = 0
+        req.n_preempted += 1
+        self._sync()
+        return req
 
     def finish(self, req: Request, reason: str) -> None:
-        req.finish_reason = reason
-        req.status = FINISHED
-        if req in self.running:
-            self.running.remove(req)
-            self.cache.release(req.id)
-        elif req in self.waiting:
-            self.waiting.remove(req)
-        self.finished.append(req)
+        key = self._key(req)
+        self._lib.kf_sched_finish(self._h, key)
+        self._retire(req, key, reason)
+        self._sync()
 
     def schedule(self) -> list[Portion]:
         """Plan one step.  Returns the portions to run (possibly none if nothing can run right now)."""
-        free = list(self.cache.free_pages())
-        budget = self.max_batch_tokens
-        plan: list[Portion] = []
-        preempted = False
-
-        def take(need: list[int]) -> bool:
-            if any(n > f for n, f in zip(need, free)):
-                return False
-            for i, n in enumerate(need):
-                free[i] -= n
-            return True
-
-        # 1. decoding requests, oldest first; out of pages -> preempt the youngest and try again
-        i = 0
-        while i < len(self.running):
-            req = self.running[i]
-            if not req.decoding:
-                i += 1
-                continue
-            if budget <= 0:
-                break
-            need = self.cache.pages_needed(req.id, 1)
-            if take(need):
-                plan.append(Portion(req, req.n_cached, 1, True))
-                budget -= 1
-                i += 1
-                continue
-            victim = self.preempt_last(keep=req)
-            if victim is None:
-                # alone and still no page: the pool cannot hold this request
-                self.finish(req, "no_fit")
-                continue
-            preempted = True
-            planned = [p for p in plan if p.request is victim]
-            for p in planned:                       # it had been planned in this very call: undo
-                plan.remove(p)
-                budget += p.n
-            free = list(self.cache.free_pages())
-            for p in plan:                          # re-apply what is already planned
-                for gi, n in enumerate(self.cache.pages_needed(p.request.id, p.n)):
-                    free[gi] -= n
-            # `i` stays: retry the same request (the victim sat after it or before it in the list)
-            i = self.running.index(req)
-
-        # 2. prompt portions of running requests, in order of admission
-        for req in self.running:
-            if budget <= 0:
-                break
-            if req.decoding or req.n_pending == 0 or any(p.request is req for p in plan):
-                continue
-            n = self._largest_portion(req, min(budget, req.n_pending), free, live=True)
-            if n <= 0:
-                continue
-            take(self.cache.pages_needed(req.id, n))
-            plan.append(Portion(req, req.n_cached, n, n == req.n_pending))
-            budget -= n
-
-        # 3. admission, first come first served
-        while self.waiting and budget > 0 and len(self.running) < self.max_requests:
-            req = self.waiting[0]
-            if not self._fits_at_all(req):
-                self.waiting.popleft()
-                self.finish(req, "no_fit")
-                continue
-            if preempted or any(a > b for a, b in zip(self._admission_pages(req), free)):
-                break
-            n = min(budget, req.n_pending)
-            self.waiting.popleft()
-            self.cache.add_request(req.id)
-            req.status = RUNNING
-            self.running.append(req)
-            take(self._pages_for(req, n, live=True))
-            plan.append(Portion(req, 0, n, n == req.n_pending))
-            budget -= n
-
-        if not plan and self.running and not any(r.decoding for r in self.running):
-            # every running request is mid-prompt and none can get a page: free the youngest so the oldest moves
-            if len(self.running) > 1:
-                self.preempt_last(keep=self.running[0])
-                return self.schedule()
-            self.finish(self.running[0], "no_fit")
+        rc = self._lib.kf_sched_schedule(self._h, self._portions, self._cap_portions, self._events, self._cap_events, self._counts)
+        if rc != 0:
+            raise RuntimeError(f"the native scheduler returned more portions or events than fit ({self._counts[0]}, {self._counts[1]})")
+        n_portions, n_events = self._counts[0], self._counts[1]
+        if n_events:
+            self._apply_events(n_events)
+            self._sync()
+        plan = []
+        for i in range(n_portions):
+            key, start, n, wants = self._portions[4 * i:4 * i + 4]
+            plan.append(Portion(self._by_key[key], int(start), int(n), bool(wants)))
         return plan
-
-    def _largest_portion(self, req: Request, n_max: int, free: list[int], live: bool) -> int:
-        """The most tokens (<= n_max) whose pages the free counts still cover."""
-        P = self.cache.page_size
-        n = n_max
-        while n > 0:
-            need = self._pages_for(req, n, live)
-            if all(a <= b for a, b in zip(need, free)):
-                return n
-            # drop to the largest count that needs one page fewer in the tightest group
-            have = (self.cache.length(req.id) if live else 0)
-            n = min(n - 1, ((have + n - 1) // P) * P - have)
-        return 0
 
     # ---- after the step ------------------------------------------------------------------------------------
     def advance(self, portion: Portion) -> None:
         portion.request.n_cached += portion.n
+        self._lib.kf_sched_advance(self._h, self._key(portion.request), int(portion.n))
 
     def on_token(self, req: Request, token: int) -> str | None:
         """Record a sampled token; returns the finish reason if the request is done (and frees it)."""
         req.output.append(int(token))
-        reason = None
-        if not req.ignore_eos and int(token) in req.eos:
-            reason = "eos"
-        elif len(req.output) >= req.max_tokens:
-            reason = "length"
-        elif len(req.prompt) + len(req.output) >= self.cache.max_context:
-            reason = "context"
-        if reason is not None:
-            self.finish(req, reason)
+        key = self._key(req)
+        is_eos = (not req.ignore_eos) and int(token) in req.eos
+        code = self._lib.kf_sched_on_token(self._h, key, int(is_eos))
+        if code <= 0:
+            return None
+        reason = self._FINISH[code]
+        self._retire(req, key, reason)
+        self.running = [r for r in self.running if r is not req]
         return reason

@@ -234,3 +234,21 @@ def test_eos_and_context_finish():
     while not s.idle:
         reasons += [r for _, r in run_plan(s, s.schedule(), token=7) if r]
     assert reasons == ["context"] and len(s.finished[1].output) == 9
+
+
+def test_adopted_request_decodes_from_where_its_cache_ends():
+    """A request whose prompt the caller has put into the cache by hand joins the running requests as it is."""
+    c = make_cache(n_pages=32, page=4, window=None, max_context=64, state=False)
+    s = Scheduler(c, max_batch_tokens=64)
+    c.add_request("r")
+    c.reserve("r", 9)
+    c.commit("r", 9)
+    req = Request("r", list(range(10)), greedy(), max_tokens=3)
+    req.n_cached = 9
+    s.adopt(req)
+    plan = s.schedule()
+    assert [(p.request.id, p.start, p.n, p.wants_logits) for p in plan] == [("r", 9, 1, True)]
+    assert run_plan(s, plan) == [("r", None)]
+    while not s.idle:
+        run_plan(s, s.schedule())
+    assert req.finish_reason == "length" and len(req.output) == 3 and c.free_pages() == [32] and "r" not in c
