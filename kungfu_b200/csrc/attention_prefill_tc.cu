@@ -166,7 +166,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
                        float scale, float softcap, int window, __nv_bfloat16* __restrict__ out,
-                       int* __restrict__ error_flag) {
+                       int* __restrict__ error_flag, int n_parts, float* __restrict__ partial) {
   constexpr int NSUB = D / 64;                            // 64-element sub-tiles along the head dimension
   constexpr int Q_BYTES = BMQ * D * 2;
   constexpr int KV_BYTES = BKV * D * 2;                   // one K tile (or one V tile)
@@ -195,7 +195,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   float* s_max = (float*)(tmem_slot + 2);                 // [2 tile parities][2 halves][128 rows]; later [2][128] sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // tiles late in a request have the most keys: they start first.  With n_parts > 1 the keys of a tile are cut into
+  // that many runs, one block each (blockIdx.z); the blocks leave unnormalised partial rows that a second kernel merges.
+  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, part = blockIdx.z;
   const int row0 = tile_row0[tile], nrows = tile_nrows[tile];
   const int kvh = h / (nh / nkv);
 
@@ -225,8 +227,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int pos0 = positions[row0];
   const int pos_last = pos0 + nrows - 1;
   const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int kt_begin = (lo / BKV) * BKV;
-  const int n_tiles = req < 0 ? 0 : (pos_last - kt_begin) / BKV + 1;
+  const int kt_first = (lo / BKV) * BKV;
+  const int n_tiles_all = req < 0 ? 0 : (pos_last - kt_first) / BKV + 1;
+  const int per_part = (n_tiles_all + n_parts - 1) / n_parts;
+  const int kt_begin = kt_first + part * per_part * BKV;
+  const int n_tiles = max(0, min(per_part, n_tiles_all - part * per_part));
 
   if (warp == 8) {
     // ---- TMA producer --------------------------------------------------------------------------------------
@@ -390,7 +395,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     s_max[half * BMQ + r] = l_sum;
     asm volatile("bar.sync 2, 256;" ::: "memory");
     l_sum = s_max[r] + s_max[BMQ + r];
-    if (ok && n_tiles > 0 && *s_abort == 0) {
+    if (n_parts > 1) {
+      // ---- one of several runs of keys: leave O as it is (scaled by 2^-m), with m and the sum, for the merge ----------
+      const bool run_ok = __all_sync(0xffffffffu, ok && n_tiles > 0 && *s_abort == 0);
+      const bool have = run_ok && r < nrows && l_sum > 0.f;     // a row that saw no key in this run leaves m = -inf
+      float* rec = partial + (((size_t)(row0 + (r < nrows ? r : 0)) * nh + h) * n_parts + part) * (D + 4);
+      if (half == 0 && r < nrows) { rec[D] = have ? m_used : -INFINITY; rec[D + 1] = have ? l_sum : 0.f; }
+      if (run_ok) {
+#pragma unroll 1
+        for (int c = 0; c < HC; c += 16) {
+          float o[16];
+          tmem_ld16(lane_addr + O_COL + half * HC + c, o);       // every lane of the warp takes part in the load
+          if (have) {
+#pragma unroll
+            for (int e = 0; e < 16; e += 4)
+              *reinterpret_cast<float4*>(rec + half * HC + c + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+          }
+        }
+      }
+    } else if (ok && n_tiles > 0 && *s_abort == 0) {
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* orow = out + ((size_t)(row0 + r) * nh + h) * D + half * HC;
 #pragma unroll 1
@@ -415,6 +438,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (warp == 9) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// Merges the partial rows of the key runs: out = sum_p 2^(m_p - m) O_p / sum_p 2^(m_p - m) l_p, runs in index order.
+// One block per (tile, row of the tile); a thread owns groups of four output elements over all heads.
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ tile_row0,
+                          const int* __restrict__ tile_nrows, int nh, int n_parts, __nv_bfloat16* __restrict__ out) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int tile = blockIdx.x, r = blockIdx.y;
+  if (r >= tile_nrows[tile]) return;
+  const int row = tile_row0[tile] + r;
+  constexpr int REC = D + 4;
+  for (int e = threadIdx.x; e < nh * (D / 4); e += blockDim.x) {
+    const int h = e / (D / 4), c4 = e - h * (D / 4);
+    const float* rec0 = partial + ((size_t)row * nh + h) * n_parts * REC;
+    float m = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) m = fmaxf(m, rec0[(size_t)p * REC + D]);
+    float l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_parts; ++p) {
+      const float mp = rec0[(size_t)p * REC + D];
+      if (mp == -INFINITY) continue;                          // a run that saw no key: its O was never written
+      const float w = ex2_fast(mp - m);
+      l += rec0[(size_t)p * REC + D + 1] * w;
+      const float4 o = *reinterpret_cast<const float4*>(rec0 + (size_t)p * REC + c4 * 4);
+      acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)row * nh + h) * D + c4 * 4) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
   }
 }
 
@@ -467,7 +524,8 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 template <int D>
 int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
            const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
-           float scale, float softcap, int window, void* out, int* error_flag, cudaStream_t stream) {
+           float scale, float softcap, int window, void* out, int* error_flag, int n_parts, float* partial,
+           cudaStream_t stream) {
   const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256 + 4 * BMQ * 4;
   static bool configured = false;
   if (!configured) {
@@ -477,10 +535,15 @@ int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, 
     }
     configured = true;
   }
-  kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
+  kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles, nh, n_parts), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
             positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out,
-            error_flag);
+            error_flag, n_parts, partial);
   KF_CHECK_LAUNCH();
+  if (n_parts > 1) {
+    kf_launch(attn_prefill_merge_kernel<D>, dim3(n_tiles, BMQ), dim3(128), 0, stream, (const float*)partial, tile_row0,
+              tile_nrows, nh, n_parts, (__nv_bfloat16*)out);
+    KF_CHECK_LAUNCH();
+  }
   return KF_OK;
 }
 
@@ -492,18 +555,35 @@ KF_API int kf_attention_prefill_tc_supported(int d, int page_size, const void* q
 }
 KF_API int kf_attention_prefill_tc_tile_rows() { return BMQ; }
 
+// Into how many runs the keys of every tile are cut so that the blocks fill the GPU: 1 when tiles x heads fill half of it;
+// at most 8, and never so many that a run of the longest tile has fewer than two 64-key tiles.
+KF_API int kf_attention_prefill_tc_parts(int n_tiles, int nh, int max_keys) {
+  // The partial rows cost a write, a read and a second kernel (about 25 us at 2,048 rows x 8 heads), which only pays
+  // when the blocks would otherwise leave more than half of the SMs idle.
+  const long blocks = (long)n_tiles * nh;
+  if (blocks <= 0 || 2 * blocks > 148) return 1;
+  int parts = (int)(148 / blocks);
+  if (parts > 8) parts = 8;
+  const int key_tiles = (max_keys + BKV - 1) / BKV;
+  if (parts > key_tiles / 2) parts = key_tiles / 2;
+  return parts < 1 ? 1 : parts;
+}
+
 // q, out: [T, nh*d] bfloat16; pages: [n_pages, 2, nkv, page_size, d] bfloat16.  tile_row0/tile_nrows: tiles of up to 128
-// consecutive rows of one request (consecutive positions).
+// consecutive rows of one request (consecutive positions).  n_parts > 1 cuts every tile's keys into that many runs;
+// `partial` then holds T * nh * n_parts * (d + 4) floats.
 KF_API int kf_attention_prefill_tc(const void* q, void* out, const void* pages, long n_pages, int T, const int* tile_row0,
                                    const int* tile_nrows, int n_tiles, const int* positions, const int* row_req,
                                    const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
-                                   float softcap, int window, int* error_flag, cudaStream_t stream) {
+                                   float softcap, int window, int* error_flag, int n_parts, float* partial,
+                                   cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
   if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0) return KF_ERR_SIZE;
+  if (n_parts < 1 || n_parts > 8 || (n_parts > 1 && !partial)) return KF_ERR_SIZE;
   CUtensorMap tq, tkv;
   if (!tensor_map(q, T, (long)nh * d, BMQ, &tq)) return KF_ERR_SETUP;
   if (!tensor_map(pages, n_pages * 2 * nkv * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
-#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, stream
+#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, n_parts, partial, stream
   switch (d) {
     case 64: return launch<64>(KF_ARGS);
     case 128: return launch<128>(KF_ARGS);

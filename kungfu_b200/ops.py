@@ -205,6 +205,7 @@ _scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor,
 use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
 use_fast_attention = True    # likewise for the generic attention kernel
 prefill_on_tcgen05 = True       # False: the mma.sync prompt kernel for every head and page size
+split_prompt_keys = True        # False: one block per (tile of rows, head) however few blocks that makes
 decode_on_tensor_cores = True   # False: the SIMT split-KV decode kernel (kept for groups of more than 16 heads)
 
 
@@ -520,9 +521,15 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
     if (prompt_tiles and prefill_on_tcgen05 and getattr(ctx, "n_wide", 0) > 0
             and lib.kf_attention_prefill_tc_supported(head_dim, cache.page_size, _p(q), _p(pages))):
         sc = _dev_scratch(q.device)
+        max_keys = min(ctx.max_kv_len, window + 128) if window else ctx.max_kv_len
+        parts = lib.kf_attention_prefill_tc_parts(ctx.n_wide, n_heads, int(max_keys)) if split_prompt_keys else 1
+        partial = _partial(q.device, T * n_heads * parts * (head_dim + 4)) if parts > 1 else None
         _check(lib.kf_attention_prefill_tc(_p(q), _p(out), _p(pages), ctypes.c_long(pages.shape[0]), T, _p(ctx.wide_row0),
-                                           _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), _stream()),
+                                           _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), parts, _p(partial),
+                                           _stream()),
                "attention (prefill, tcgen05)")
+        if parts > 1:
+            add_launches(1)
         return
     if prompt_tiles and lib.kf_attention_prefill_supported(head_dim):
         _check(lib.kf_attention_prefill(_p(q), _p(out), _p(pages), _p(ctx.tile_row0), _p(ctx.tile_nrows), ctx.n_tiles,

@@ -425,6 +425,39 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("nh,nkv,d,window", [(8, 4, 256, None), (4, 1, 128, 300), (6, 2, 64, None)])
+@pytest.mark.parametrize("lens", [[700], [2048], [130, 513, 64]])
+def test_prompt_attention_with_keys_cut_into_runs(ops, nh, nkv, d, window, lens):
+    """Few blocks of prompt rows (a short portion at a long context, or one long prompt whose last tiles have most of
+    the keys) cut every tile's keys into runs with a block each, merged by a second kernel: the same result as one block
+    per tile, and as float64."""
+    P = 64
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=31)
+    # the last 200 rows of every request (a portion late in its prompt), all rows of short ones
+    rows = [(r, p) for r, n in enumerate(lens) for p in range(max(0, n - 200), n)]
+    g = torch.Generator().manual_seed(32)
+    q = torch.randn(len(rows), nh, d, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), [], list(range(len(rows))))
+    outs = []
+    for split in (True, False):
+        ops.split_prompt_keys = split
+        try:
+            out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+            before = ops.launch_count()
+            ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, 50.0, window)
+            outs.append((out, ops.launch_count() - before))
+        finally:
+            ops.split_prompt_keys = True
+    ops.raise_on_device_error()
+    assert outs[0][1] == 2 and outs[1][1] == 1, "cut into runs: the attention kernel and the merge"
+    ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, 50.0, window) for i, (r, p) in enumerate(rows)])
+    assert rel_err(outs[0][0].view(len(rows), nh, d), ref) < 1e-2
+    assert rel_err(outs[1][0].view(len(rows), nh, d), ref) < 1e-2
+    assert rel_err(outs[0][0], outs[1][0]) < 6e-3
+
+
 def _plant(pages, table, req, j, kvh, P, key=None, value=None):
     """Overwrite key and/or value j of a request in its pages (host tensors)."""
     pg = int(table[req, j // P])
