@@ -153,7 +153,7 @@ def build_host() -> str:
     C++ compiler; it needs neither nvcc nor a GPU.  Returns the path of the shared library."""
     out = build_dir()
     src = os.path.join(HERE, "host_runtime.cpp")
-    tag = _file_hash(src, "host-v3")
+    tag = _file_hash(src, "host-v4")
     lib = os.path.join(out, HOST_LIB_NAME)
     stamp_path = os.path.join(out, "host_stamp")
 

@@ -269,7 +269,9 @@ KF_HOST_API int kf_cache_check(void* h) {
 // `info` receives: [0] total ints, [1] T, [2] B, [3] n_out, [4] width, [5] n_dec, [6] n_pre, [7] n_tiles, [8] n_wide,
 // [9] max_kv, [10] max rows of a request, then the offset of every section in the order above (14 + n_groups).
 // With bucket > 0 the layout is that of `bucket` single-row requests with full-width tables; rows beyond the real
-// entries are padding (request -1).
+// entries are padding (request -1).  With bucket < 0 the entries are laid out as they are but with full-width tables
+// and the longest context as max_kv, so that the layout depends only on the entries' token and wanted counts (steps of
+// the same shape can then be replayed from one CUDA graph).
 enum { SEC_TOKENS, SEC_POSITIONS, SEC_ROW_REQ, SEC_LOGIT_ROWS, SEC_DEC_ROWS, SEC_PRE_ROWS, SEC_TILE_ROW0, SEC_TILE_NROWS,
        SEC_WIDE_ROW0, SEC_WIDE_NROWS, SEC_REQ_ROW_START, SEC_REQ_N_ROWS, SEC_REQ_KV_LEN, SEC_REQ_STATE_SLOT, SEC_TABLE0 };
 constexpr int INFO_FIXED = 11;
@@ -289,6 +291,7 @@ KF_HOST_API int kf_step_layout(void* h, int n_entries, const int64_t* reqs, cons
   }
   int B = n_entries;
   if (bucket > 0) { T = B = n_out = bucket; width = c->max_pages; }
+  if (bucket < 0) width = c->max_pages;
   width = align4(width);
   const int sizes[SEC_TABLE0] = {T, T, T, std::max(n_out, 1), T, T, T / 64 + B + 1, T / 64 + B + 1, T / 128 + B + 1,
                                  T / 128 + B + 1, B, B, B, B};
@@ -356,6 +359,7 @@ KF_HOST_API int kf_step_fill(void* h, int n_entries, const int64_t* reqs, const 
     }
     max_kv = c->max_context;                              // a captured graph's split plan must not depend on the step
   }
+  if (bucket < 0) max_kv = c->max_context;
   info[5] = n_dec; info[6] = n_pre; info[7] = n_tiles; info[8] = n_wide; info[9] = max_kv; info[10] = max_rows;
   return OK;
 }

@@ -148,7 +148,7 @@ class Runner:
         reqs = np.fromiter((cache.key_of(e.request) for e in entries), dtype=np.int64, count=n)
         n_tokens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=n)
         n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n)
-        if bucket is not None or int(n_tokens.max(initial=0)) == 1:
+        if (bucket is not None and bucket > 0) or int(n_tokens.max(initial=0)) == 1:
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
         else:
             tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]) if n else np.zeros(0, np.int32)
@@ -259,12 +259,23 @@ class Runner:
         return logits
 
     # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
-    def _graph_bucket(self, entries) -> int | None:
-        """The padded batch size whose graph runs this step, or None if the step is not a pure decode step."""
+    MAX_PORTION_GRAPHS = 8
+
+    def _graph_bucket(self, entries):
+        """The key of the CUDA graph that runs this step, or None if the step runs eagerly.  A pure decode step: the
+        padded batch size (an int).  A step that is one short portion (64 to 256 rows) of one prompt: ("portion", rows,
+        wanted rows): such steps repeat with the same shape while a long prompt is fed under a small token budget, and
+        at that size launching their two hundred kernels one by one takes the host longer than the GPU needs to run
+        them (longer portions keep the GPU busy for longer than the host needs, so a graph would gain nothing)."""
         if not self.cuda_graphs or self.device.type != "cuda" or not self._graph_safe:
             return None
         from .. import ops
         if ops.tracing():                                  # per-kernel timing needs eager launches
+            return None
+        if len(entries) == 1 and 64 <= len(entries[0].tokens) <= 256:
+            key = ("portion", len(entries[0].tokens), len(entries[0].want))
+            if key in self._graphs or sum(1 for k in self._graphs if isinstance(k, tuple)) < self.MAX_PORTION_GRAPHS:
+                return key
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None
@@ -282,31 +293,41 @@ class Runner:
         if chain:
             ops.chain_begin()
         try:
+            if self.device.type == "cuda":
+                with ops.pinned_stream():
+                    return self.model.forward(ctx)
             return self.model.forward(ctx)
         finally:
             if chain:
                 ops.chain_end()
 
-    def _step_graphed(self, entries, bucket: int):
-        """First time a bucket is seen the step runs eagerly (that also sizes every buffer); the second time the
+    def _step_graphed(self, entries, key):
+        """First time a key is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
-        n = len(entries)
-        state = self._graphs.get(bucket)
+        if isinstance(key, tuple):                         # one portion of one prompt: the entries as they are, fixed layout
+            n, bucket = key[2], -1
+        else:
+            n, bucket = len(entries), key
+        state = self._graphs.get(key)
         if state is not None and state["generation"] != self.buffers.generation:
             state = None                                   # a buffer moved: the old graph points at freed memory
-            self._graphs.pop(bucket)
+            self._graphs.pop(key)
+
+        def result(logits):
+            return None if (logits is None or n == 0) else logits[:n]
+
         if state is not None and state["graph"] is not None:
             self._build_block(entries, bucket)            # same layout as at capture; a replay needs no context object
             state["graph"].replay()
             ops.add_launches(state["kernels"])
-            return state["logits"][:n]
+            return result(state["logits"])
         ctx = self._fill(entries, bucket)
         if state is None:
-            self._graphs[bucket] = {"generation": None, "graph": None, "seen": 1}
+            self._graphs[key] = {"generation": None, "graph": None, "seen": 1}
             logits = self._forward(ctx)
-            self._graphs[bucket]["generation"] = self.buffers.generation
-            return logits[:n]
+            self._graphs[key]["generation"] = self.buffers.generation
+            return result(logits)
         if state["graph"] is None:
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
@@ -314,10 +335,10 @@ class Runner:
             with torch.cuda.graph(graph):
                 logits = self._forward(ctx)
             if self.buffers.generation != state["generation"]:
-                self._graphs.pop(bucket)                   # capture itself grew a buffer: run this step eagerly
-                return self._forward(ctx)[:n]
+                self._graphs.pop(key)                      # capture itself grew a buffer: run this step eagerly
+                return result(self._forward(ctx))
             state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
             ops.add_launches(-state["kernels"])            # capture launched nothing
         state["graph"].replay()
         ops.add_launches(state["kernels"])
-        return state["logits"][:n]
+        return result(state["logits"])

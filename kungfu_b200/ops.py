@@ -101,8 +101,29 @@ def _p(t: torch.Tensor | None):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_pinned_stream = None
+
+
 def _stream():
+    if _pinned_stream is not None:
+        return _pinned_stream
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class pinned_stream:
+    """Within this context every launch goes to the stream that is current on entry, looked up once (asking torch for the
+    current stream costs as much as a launch).  The step function wraps the model's pass in it."""
+
+    def __enter__(self):
+        global _pinned_stream
+        self._was = _pinned_stream
+        _pinned_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _pinned_stream
+        _pinned_stream = self._was
+        return False
 
 
 def _f(x: float):
@@ -244,6 +265,9 @@ def raise_on_device_error(device=None) -> None:
                           f"3 = accumulator never completed)")
 
 
+_linear_plans: dict = {}          # (rows, features, K, mode) -> (token tile, K splits) as the library plans them
+
+
 def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> bool:
     """Launch the tcgen05 product if it takes these operands; False if the generic kernel must run."""
     T, K = x.shape
@@ -251,16 +275,19 @@ def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> b
     if not (use_tensor_cores and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and lib.kf_linear_tc_supported(_p(x), _p(weight), K)):
         return False
-    bn, splits = ctypes.c_int(0), ctypes.c_int(0)
-    lib.kf_linear_tc_plan(T, N, K, int(mode == 2), ctypes.byref(bn), ctypes.byref(splits))
+    plan = _linear_plans.get((T, N, K, mode))
+    if plan is None:
+        bn, splits = ctypes.c_int(0), ctypes.c_int(0)
+        lib.kf_linear_tc_plan(T, N, K, int(mode == 2), ctypes.byref(bn), ctypes.byref(splits))
+        plan = _linear_plans[(T, N, K, mode)] = (bn.value, splits.value)
+    bn, splits = plan
     sc = _dev_scratch(x.device)
-    tiles = -(-N // 128) * -(-T // bn.value)
     partial = None
-    if splits.value > 1:
-        if tiles > sc["counters"].numel():
+    if splits > 1:
+        if -(-N // 128) * -(-T // bn) > sc["counters"].numel():
             return False
-        partial = _partial(x.device, splits.value * T * (2 * N if mode == 2 else N))
-    _check(lib.kf_linear_tc(_p(x), _p(weight), _p(out), mode, T, N, K, _f(softcap), act, bn.value, splits.value,
+        partial = _partial(x.device, splits * T * (2 * N if mode == 2 else N))
+    _check(lib.kf_linear_tc(_p(x), _p(weight), _p(out), mode, T, N, K, _f(softcap), act, bn, splits,
                             _p(partial), _p(sc["counters"]), _p(sc["error"]), _stream()), "linear (tensor cores)")
     return True
 
