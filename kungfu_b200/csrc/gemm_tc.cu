@@ -229,25 +229,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #pragma unroll
       for (int z = 0; z < 8; ++z)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[z]) : "r"(red_addr), "r"(z < splits ? z : 0));
-      for (int tl = rank; tl < t_hi; tl += splits) {
-        // all peers' values are requested before any is added, so the remote latencies overlap; the sum itself
-        // runs in split order
-        float pv[8], pu[8];
-        const uint32_t off = (uint32_t)(((size_t)tl * BM + fl) * 4);
-        const uint32_t off_u = (uint32_t)(((size_t)(BN + tl) * BM + fl) * 4);
+      // All peers' values of several tokens are requested before any is added, so the remote latencies overlap (a token
+      // tile of 256 would otherwise pay one round trip per token); the sum itself runs in split order.
+      constexpr int TB = BN >= 64 ? 4 : 1;                                      // tokens per batch of remote loads
+      for (int tl0 = rank; tl0 < t_hi; tl0 += splits * TB) {
+        float pv[TB][8], pu[TB][8];
 #pragma unroll
-        for (int z = 0; z < 8; ++z) {
-          pv[z] = 0.f;
-          pu[z] = 0.f;
-          if (z < splits) {
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[z]) : "r"(remote[z] + off) : "memory");
-            if (GATED) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pu[z]) : "r"(remote[z] + off_u) : "memory");
+        for (int b = 0; b < TB; ++b) {
+          const int tl = tl0 + b * splits;
+          const uint32_t off = (uint32_t)(((size_t)tl * BM + fl) * 4);
+          const uint32_t off_u = (uint32_t)(((size_t)(BN + tl) * BM + fl) * 4);
+#pragma unroll
+          for (int z = 0; z < 8; ++z) {
+            pv[b][z] = 0.f;
+            pu[b][z] = 0.f;
+            if (z < splits && tl < t_hi) {
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[b][z]) : "r"(remote[z] + off) : "memory");
+              if (GATED) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pu[b][z]) : "r"(remote[z] + off_u) : "memory");
+            }
           }
         }
-        float v = 0.f, u = 0.f;
 #pragma unroll
-        for (int z = 0; z < 8; ++z) { v += pv[z]; u += pu[z]; }
-        if (f < n_out) store(t0 + tl, finish(v, u));
+        for (int b = 0; b < TB; ++b) {
+          const int tl = tl0 + b * splits;
+          float v = 0.f, u = 0.f;
+#pragma unroll
+          for (int z = 0; z < 8; ++z) { v += pv[b][z]; u += pu[b][z]; }
+          if (tl < t_hi && f < n_out) store(t0 + tl, finish(v, u));
+        }
       }
       asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // nobody leaves while peers still read
       asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -716,17 +725,39 @@ namespace {
 int g_cluster_reduce = 1;
 int g_stage_cap_kb = 108;
 // Choice of token tile and split-K for a launch.
+int g_plan_bn = 0, g_plan_splits = 0;               // measurement hook: a fixed plan for products over more than 64 rows
+
 int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
   int bn = 16;
   while (bn < T && bn < 256) bn *= 2;
   if (gated && bn > 256) bn = 256;
   const int nkb = (K + BK - 1) / BK;
-  const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
+  if (T > 64 && g_plan_bn > 0) {
+    *bn_out = g_plan_bn;
+    *splits_out = g_plan_splits > nkb ? nkb : (g_plan_splits < 1 ? 1 : g_plan_splits);
+    return KF_OK;
+  }
   int splits = 1;
-  if (tiles <= 74) {                                   // fewer tiles than half the SMs: cut K so that every SM streams
-    splits = (int)(148 / tiles);                       // weights, in ONE wave (one CTA per SM fits)
-    if (splits > 8) splits = 8;                        // a portable thread-block cluster holds 8 CTAs
-    if (splits > nkb) splits = nkb;
+  if (T > 64 && gated) {
+    // Prompt portions through the gated epilogue never split K (their partial tiles would have to go through global
+    // memory); up to 256 rows a 128-token tile gives twice the tiles (measured at 256 rows, 9216 x 2304: 29 us against
+    // 42 us with one 256-token tile and 220 us split in two).
+    bn = T <= 256 ? 128 : 256;
+  } else if (T > 64 && (T <= 512 || (T <= 1024 && K <= 4096 && (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, 64) <= 296))) {
+    // Short portions: 64-token tiles on the weight-streaming kernel, two CTAs per SM, K cut so that about 2 x 148 CTAs
+    // run (measured at 2304-wide layers, 128 to 512 rows: 1.3x to 2x faster than one 256-token tile split four ways).
+    bn = 64;
+    const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
+    while (splits < 8 && tiles * splits * 2 <= 296 && nkb / (splits * 2) >= 8) splits *= 2;
+  } else {
+    const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
+    if (tiles <= 74) {                                 // fewer tiles than half the SMs: cut K so that every SM streams
+      splits = (int)(148 / tiles);                     // weights, in ONE wave (one CTA per SM fits)
+      if (splits > 8) splits = 8;                      // a portable thread-block cluster holds 8 CTAs
+      if (splits > nkb) splits = nkb;
+    }
+  }
+  if (splits > 1) {
     const int kb_per = (nkb + splits - 1) / splits;
     splits = (nkb + kb_per - 1) / kb_per;              // no empty split
   }
@@ -957,6 +988,8 @@ KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; 
 KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
+// Measurement hook: token tile and K splits for every product over more than 64 rows (0, 0: the planner decides).
+KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.

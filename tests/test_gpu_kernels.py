@@ -83,10 +83,15 @@ def test_linear(ops, T, N, K, xd, wd):
     capped = torch.empty(T, N, device=DEV)
     ops.linear(x, w, capped, softcap=0.7)
     assert rel_err(capped, 0.7 * torch.tanh(ref / 0.7)) < 1e-5
-    # a row's result does not depend on the other rows of the launch
+    # a row's result does not depend on the other rows of the launch: to the bit on the generic kernel (the order of
+    # the sum over K is fixed per output), to the rounding of a 32-bit sum on the tensor cores (how K is cut across
+    # CTAs depends on the number of rows)
     one = torch.empty(1, N, device=DEV)
     ops.linear(x[T - 1:T].contiguous(), w, one)
-    assert torch.equal(one[0], out[T - 1])
+    if xd == torch.bfloat16 and wd == torch.bfloat16 and K % 8 == 0:
+        assert rel_err(one[0], out[T - 1]) < 2e-6 * math.sqrt(K)
+    else:
+        assert torch.equal(one[0], out[T - 1])
 
 
 TC_SHAPES = [(1, 256, 64), (8, 2304, 2048), (5, 130, 200), (16, 128, 96), (17, 1000, 120), (40, 4096, 2304), (64, 777, 320),
