@@ -774,8 +774,10 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   const int nkb = (K + BK - 1) / BK;
   const int kb_per = (nkb + splits - 1) / splits;
   int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
-  if (BN <= 64 && g_stage_cap_kb > 0) {                 // weight streaming: optionally leave room for a second resident
-    const int cap = (g_stage_cap_kb * 1024) / STAGE_BYTES;   // CTA so that the next product can prefetch meanwhile
+  if (BN <= 64 && g_stage_cap_kb > 0) {                 // weight streaming: leave room for a second resident CTA so
+    // that the next product can request its first tiles meanwhile.  The gated product gets 20 KB more (a third stage
+    // at 64 tokens): its neighbours in a layer are plain products, and 128 + 96 KB still share an SM.
+    const int cap = ((g_stage_cap_kb + (EPI == EPI_GATED ? 20 : 0)) * 1024) / STAGE_BYTES;
     if (stages > cap) stages = cap;
   }
   if (stages > kb_per) stages = kb_per;
