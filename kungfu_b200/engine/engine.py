@@ -113,12 +113,16 @@ class Engine:
         for p in plan:
             toks = p.request.slice(p.start, p.n)
             entries.append(StepEntry(p.request.id, toks, [p.n - 1] if p.wants_logits else []))
-        logits = self.runner.step(entries)
+        wanting = [p for p in plan if p.wants_logits]
+        greedy = bool(wanting) and all(p.request.sampling.greedy for p in wanting)
+        if greedy:                                       # the largest logit is found in the step's own pass
+            logits, picked = self.runner.step(entries, greedy=True)
+        else:
+            logits, picked = self.runner.step(entries), None
         for p in plan:
             self.scheduler.advance(p)
-        wanting = [p for p in plan if p.wants_logits]
         if wanting:
-            tokens = self._pick(logits, [p.request for p in wanting])
+            tokens = picked.cpu().tolist() if picked is not None else self._pick(logits, [p.request for p in wanting])
             for p, tok in zip(wanting, tokens):
                 reason = self.scheduler.on_token(p.request, tok)
                 events.append((p.request.id, tok, reason))

@@ -229,14 +229,16 @@ class Runner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False):
         """Run the tokens of `entries` as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
         in the order of the entries and of each entry's `want`, or None when nothing is wanted.  The result
         lives in a buffer the next step overwrites.  Raises OutOfPages before touching anything when the
-        pages for the new tokens cannot all be had."""
+        pages for the new tokens cannot all be had.
+        With `greedy` the index of the largest logit of every wanted row is computed in the same pass (inside the
+        replayed graph for decode steps) and the result is (logits, int32 token ids [wanted])."""
         entries = list(entries)
         if not entries:
-            return None
+            return (None, None) if greedy else None
         self.validate(entries)
         reserved = []
         try:
@@ -248,15 +250,28 @@ class Runner:
                 self.cache.cancel_reservation(e.request)
             raise
         bucket = self._graph_bucket(entries)
+        picked = None
         if bucket is None:
             ctx = self._fill(entries)
             logits = self._forward(ctx)
+            if greedy and logits is not None:
+                picked = self._argmax(logits)
+        elif greedy and isinstance(bucket, int):
+            logits, picked = self._step_graphed(entries, ("greedy", bucket))
         else:
             logits = self._step_graphed(entries, bucket)
+            if greedy and logits is not None:
+                picked = self._argmax(logits)
         for e in entries:
             self.cache.commit(e.request, len(e.tokens))
         self.steps_run += 1
-        return logits
+        return (logits, picked) if greedy else logits
+
+    def _argmax(self, logits):
+        from .. import ops
+        out = self.buffers.get("greedy_ids", (logits.shape[0],), torch.int32)
+        ops.argmax(logits, out)
+        return out
 
     # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
     MAX_PORTION_GRAPHS = 8
@@ -274,7 +289,7 @@ class Runner:
             return None
         if len(entries) == 1 and 64 <= len(entries[0].tokens) <= 256:
             key = ("portion", len(entries[0].tokens), len(entries[0].want))
-            if key in self._graphs or sum(1 for k in self._graphs if isinstance(k, tuple)) < self.MAX_PORTION_GRAPHS:
+            if key in self._graphs or sum(1 for k in self._graphs if isinstance(k, tuple) and k[0] == "portion") < self.MAX_PORTION_GRAPHS:
                 return key
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
@@ -305,7 +320,10 @@ class Runner:
         """First time a key is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
-        if isinstance(key, tuple):                         # one portion of one prompt: the entries as they are, fixed layout
+        pick = isinstance(key, tuple) and key[0] == "greedy"   # a decode bucket whose graph also holds the argmax
+        if pick:
+            n, bucket = len(entries), key[1]
+        elif isinstance(key, tuple):                       # one portion of one prompt: the entries as they are, fixed layout
             n, bucket = key[2], -1
         else:
             n, bucket = len(entries), key
@@ -314,31 +332,36 @@ class Runner:
             state = None                                   # a buffer moved: the old graph points at freed memory
             self._graphs.pop(key)
 
-        def result(logits):
-            return None if (logits is None or n == 0) else logits[:n]
+        def result(logits, picked=None):
+            out = None if (logits is None or n == 0) else logits[:n]
+            return (out, picked[:n]) if pick else out
+
+        def run(ctx):
+            logits = self._forward(ctx)
+            return (logits, self._argmax(logits)) if pick else (logits, None)
 
         if state is not None and state["graph"] is not None:
             self._build_block(entries, bucket)            # same layout as at capture; a replay needs no context object
             state["graph"].replay()
             ops.add_launches(state["kernels"])
-            return result(state["logits"])
+            return result(state["logits"], state["picked"])
         ctx = self._fill(entries, bucket)
         if state is None:
             self._graphs[key] = {"generation": None, "graph": None, "seen": 1}
-            logits = self._forward(ctx)
+            logits, picked = run(ctx)
             self._graphs[key]["generation"] = self.buffers.generation
-            return result(logits)
+            return result(logits, picked)
         if state["graph"] is None:
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
             with torch.cuda.graph(graph):
-                logits = self._forward(ctx)
+                logits, picked = run(ctx)
             if self.buffers.generation != state["generation"]:
                 self._graphs.pop(key)                      # capture itself grew a buffer: run this step eagerly
-                return result(self._forward(ctx))
-            state.update(graph=graph, logits=logits, kernels=ops.launch_count() - before)
+                return result(*run(ctx))
+            state.update(graph=graph, logits=logits, picked=picked, kernels=ops.launch_count() - before)
             ops.add_launches(-state["kernels"])            # capture launched nothing
         state["graph"].replay()
         ops.add_launches(state["kernels"])
-        return result(state["logits"])
+        return result(state["logits"], state["picked"])
