@@ -513,8 +513,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Two warps per quarter of the lanes drain an accumulator (each takes half of its columns): the epilogue of the gated
+// product cannot overlap the next tile (its two accumulators fill tensor memory), and the last epilogue of every
+// launch is exposed too.
+constexpr int PAIR_THREADS = 320;
+
 template <int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
                     int stages, int* __restrict__ error_flag) {
@@ -546,7 +551,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * (PAIR_THREADS - 64)); }
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -627,6 +632,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // ---- epilogue (both CTAs): each drains its own 128 lanes ------------------------------------------------------------
     kf_pdl_wait();
     const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;                          // warps 2-5: tokens 0..127 of the tile, warps 6-9: the rest
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     int ti = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++ti) {
@@ -640,7 +646,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = lane_addr + buf * PN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < PN; c0 += 32) {                      // 32 tokens per wait on tensor memory
+      for (int c0 = col_half * (PN / 2); c0 < (col_half + 1) * (PN / 2); c0 += 32) {   // 32 tokens per wait on tensor memory
         float v[32], u[32];
         if (GATED) tmem_ld32x2(acc + c0, acc + PN + c0, v, u);
         else tmem_ld32(acc + c0, v);
@@ -946,7 +952,7 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, 
   if (pairs > n_tiles) pairs = n_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(PAIR_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
