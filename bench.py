@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--context C] [--size 2b|9b|27b]
-    python bench.py --micro attention|gemm      (one kernel alone, JSON lines; used for the summaries in profiles/)
+    python bench.py --micro attention|gemm|products   (one kernel alone, JSON lines; used for the summaries in profiles/)
 
 A "step" is one decode step: every live request gets one token.  Default: the layer sizes of Gemma 2 2B,
 random bfloat16 weights, 8 requests at a context of 8192 tokens.  `value` is decoded tokens per second timed
@@ -372,6 +372,56 @@ def micro_gemm() -> int:
     return 0
 
 
+def micro_products() -> int:
+    """The four products of a Gemma 2 2B layer over 8 to 2,048 rows, each replayed from a CUDA graph of six launches over
+    distinct weights; one JSON line per (rows, product) with microseconds per launch."""
+    import torch
+    from kungfu_b200 import api, ops
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    H, Q, inner, n_w = 2304, 2048, 9216, 6
+    gen = torch.Generator(device=device)
+    gen.manual_seed(0)
+    shapes = {"q,k,v": (4096, H, False), "o": (H, Q, False), "gate+up": (inner, H, True), "down": (H, inner, False)}
+    for rows in (8, 64, 128, 256, 512, 1024, 2048):
+        for name, (n_out, k, gated) in shapes.items():
+            ws = [(torch.randn(2 * n_out if gated else n_out, k, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+                  for _ in range(n_w)]
+            x = torch.randn(rows, k, device=device).to(torch.bfloat16)
+            out = torch.empty(rows, n_out, device=device, dtype=torch.bfloat16 if gated else torch.float32)
+
+            def run():
+                for w in ws:
+                    if gated:
+                        ops.linear_gated(x, w, out, "gelu_tanh", None)
+                    else:
+                        ops.linear(x, w, out)
+            run()
+            torch.cuda.synchronize()
+            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                run()
+                with torch.cuda.graph(graph, stream=side):
+                    run()
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 10 / n_w * 1e3
+            flops = 2.0 * rows * n_out * k * (2 if gated else 1)
+            print(json.dumps({"micro": "product", "rows": rows, "product": name, "us": round(us, 1),
+                              "tflops": round(flops / us / 1e6, 1)}))
+            del ws
+    ops.raise_on_device_error()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,12 +434,14 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
-    ap.add_argument("--micro", choices=["attention", "gemm"], help="time one kernel alone instead of the model step")
+    ap.add_argument("--micro", choices=["attention", "gemm", "products"], help="time one kernel alone instead of the model step")
     args = ap.parse_args()
     if args.micro == "attention":
         return micro_attention()
     if args.micro == "gemm":
         return micro_gemm()
+    if args.micro == "products":
+        return micro_products()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built"}))
