@@ -220,11 +220,85 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ a, const TW1* __res
   }
 }
 
+// Many rows, two warps per row: every lane requests all of its part of both rows at once (the branch row and the
+// residual row, up to 2 x NV 16-byte loads in flight), so a row costs about three trips to memory instead of one per
+// 128 elements; the two warps meet through shared memory for the two sums.  Needs H % 4 == 0 and H <= 256 * NV.
+template <typename TW1, typename TW2, typename TO, int NV>
+__global__ void __launch_bounds__(256, 2)
+add_rmsnorm_split_kernel(const float* __restrict__ a, const TW1* __restrict__ w1, float eps1, int plus1,
+                         float* __restrict__ x, const TW2* __restrict__ w2, float eps2, int plus2,
+                         TO* __restrict__ out2, int T, int H) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ float red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (warp >> 1), half = warp & 1;
+  const bool valid = r < T;
+  const float* ar = a + (size_t)(valid ? r : 0) * H;
+  float* xr = x + (size_t)(valid ? r : 0) * H;
+  float4 v[NV], xo[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (lane + 32 * (half + 2 * k)) * 4;
+    const bool in = valid && i < H;
+    v[k] = in ? *reinterpret_cast<const float4*>(ar + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    xo[k] = in ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  ss = kf_warp_sum(ss);
+  if (lane == 0) red[0][warp] = ss;
+  __syncthreads();
+  ss = red[0][warp & ~1] + red[0][warp | 1];
+  const float inv = 1.f / sqrtf(ss / (float)H + eps1);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (lane + 32 * (half + 2 * k)) * 4;
+    if (valid && i < H) {
+      const float4 g = kf_gain4(w1, i, plus1);
+      v[k] = make_float4(xo[k].x + v[k].x * inv * g.x, xo[k].y + v[k].y * inv * g.y, xo[k].z + v[k].z * inv * g.z,
+                         xo[k].w + v[k].w * inv * g.w);
+      *reinterpret_cast<float4*>(xr + i) = v[k];
+      ss2 += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  if (out2 == nullptr) return;                                    // uniform over the block
+  ss2 = kf_warp_sum(ss2);
+  if (lane == 0) red[1][warp] = ss2;
+  __syncthreads();
+  ss2 = red[1][warp & ~1] + red[1][warp | 1];
+  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  TO* o = out2 + (size_t)(valid ? r : 0) * H;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (lane + 32 * (half + 2 * k)) * 4;
+    if (valid && i < H) {
+      const float4 g = kf_gain4(w2, i, plus2);
+      kf_store4(o, i, make_float4(v[k].x * inv2 * g.x, v[k].y * inv2 * g.y, v[k].z * inv2 * g.z, v[k].w * inv2 * g.w));
+    }
+  }
+}
+
 template <typename TW1, typename TW2>
 static int launch_add_rmsnorm(const float* a, const TW1* w1, float eps1, int plus1, float* x, const TW2* w2, float eps2,
                               int plus2, void* out2, int out2_dtype, int T, int H, cudaStream_t stream) {
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const bool aligned = H % 4 == 0 && (((uintptr_t)a | (uintptr_t)x | (uintptr_t)out2) & 15) == 0;
+  if (T >= 256 && aligned && H <= 256 * 20 && H >= 256) {         // many rows: two warps per row, all loads at once
+    const int nv = kf_ceil_div(H, 256);
+#define KF_GO(TO, NV) kf_launch(add_rmsnorm_split_kernel<TW1, TW2, TO, NV>, dim3(kf_ceil_div(T, 4)), dim3(256), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (TO*)out2, T, H)
+#define KF_PICK(TO)                                                                         \
+    if (nv <= 4) KF_GO(TO, 4); else if (nv <= 9) KF_GO(TO, 9); else if (nv <= 14) KF_GO(TO, 14); else KF_GO(TO, 20)
+    if (out2 == nullptr || out2_dtype == KF_F32) { KF_PICK(float); }
+    else if (out2_dtype == KF_BF16) { KF_PICK(__nv_bfloat16); }
+    else return KF_ERR_DTYPE;
+#undef KF_PICK
+#undef KF_GO
+    KF_CHECK_LAUNCH();
+    return KF_OK;
+  }
   if (T >= 256 && aligned && H <= 128 * 40 && H >= 128) {        // many rows: a warp per row
     const int nv4 = kf_ceil_div(H, 128);
 #define KF_GO(TO, NV4) kf_launch(add_rmsnorm_warp_kernel<TW1, TW2, TO, NV4>, dim3(kf_ceil_div(T, 8)), dim3(256), 0, stream, a, w1, eps1, plus1, x, w2, eps2, plus2, (TO*)out2, T, H)
