@@ -414,6 +414,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
     if (tile < n_tiles && tile != own_tile) load_tile(tile, s);
   }
   kf_pdl_wait();
+  q = kf_produced(q), qkv = kf_produced(qkv), cos_t = kf_produced(cos_t), sin_t = kf_produced(sin_t);
 
   if (qkv != nullptr) {
     // ---- Q: rotated here; rows 0..G-1 are the heads of this kv head, the rest of the 16 rows are zero ---------------------

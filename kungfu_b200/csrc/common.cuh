@@ -36,6 +36,17 @@ extern "C" void kf_record_message(const char* msg);
 __device__ __forceinline__ void kf_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void kf_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// A kernel that reads global memory before kf_pdl_wait() passes every pointer to what earlier kernels of the stream
+// wrote through this, after the wait.  Loads through a const __restrict__ parameter count as invariant for the whole
+// kernel, and the compiler may then schedule them together with the loads that stand before the wait (it did, in a
+// norm kernel, and read rows that the product before it had not finished).  The empty statement makes the pointer's
+// value depend on something that is ordered after the wait, so no load through it can move above it.
+template <typename T>
+__device__ __forceinline__ T* kf_produced(T* p) {
+  asm volatile("" : "+l"(p)::"memory");
+  return p;
+}
+
 extern "C" int kf_pdl_enabled();
 
 // Launch with the programmatic-dependent-launch attribute when it is switched on (kf_set_pdl).

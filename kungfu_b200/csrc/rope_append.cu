@@ -90,6 +90,7 @@ __global__ void rope_kv_append_vec_kernel(const float* __restrict__ qkv, const f
   const int pos = positions[t];
   const int page = (write_kv && req >= 0) ? block_table[(size_t)req * table_stride + pos / page_size] : -1;
   kf_pdl_wait();
+  qkv = kf_produced(qkv), cos_t = kf_produced(cos_t), sin_t = kf_produced(sin_t);
   const int half = rot >> 1;
   const int row_w = (nh + 2 * nkv) * d;
   const float* in = qkv + (size_t)t * row_w;
