@@ -106,6 +106,20 @@ __device__ __forceinline__ float rcp_fast(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// cap * tanh(s / cap) in base-2 units for two scores with |s * ct| <= 1 (ct = scale / cap, c4 = cap * log2(e) * ct):
+// tanh(t) = t * P(t^2), P of degree 6 fitted on Chebyshev nodes of [0, 1] (relative error 1.8e-7 in 32-bit Horner form,
+// below that of the exp2 / reciprocal form), evaluated on the packed 32-bit pipe: no special-function unit.
+__device__ __forceinline__ float2 capped2(float2 s, float ct, float c4) {
+  const float2 t = __fmul2_rn(s, make_float2(ct, ct));
+  const float2 u = __fmul2_rn(t, t);
+  float2 p = __ffma2_rn(u, make_float2(1.045553596e-03f, 1.045553596e-03f), make_float2(-6.217069924e-03f, -6.217069924e-03f));
+  p = __ffma2_rn(p, u, make_float2(2.030551992e-02f, 2.030551992e-02f));
+  p = __ffma2_rn(p, u, make_float2(-5.346517637e-02f, -5.346517637e-02f));
+  p = __ffma2_rn(p, u, make_float2(1.332539767e-01f, 1.332539767e-01f));
+  p = __ffma2_rn(p, u, make_float2(-3.333285749e-01f, -3.333285749e-01f));
+  p = __ffma2_rn(p, u, make_float2(9.999999404e-01f, 9.999999404e-01f));
+  return __fmul2_rn(__fmul2_rn(s, make_float2(c4, c4)), p);
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -307,6 +321,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const float c0 = scale * LOG2E;                                        // no cap: s2 = s * c0
     const float c1 = softcap > 0.f ? scale * 2.f * LOG2E / softcap : 0.f;   // exp(2 x / cap) = exp2(s * c1)
     const float c3 = softcap * LOG2E;
+    const float ct = softcap > 0.f ? scale / softcap : 0.f;
+    const float c4 = c3 * ct;
     constexpr int HC = D / 2;                              // O columns of this thread
     float m_used = -INFINITY, l_sum = 0.f;                 // the maximum is the row's; the sum is this half's
     bool ok = true;
@@ -324,8 +340,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const bool whole = (kt + 31 <= pos0 + wq * 32) && (window <= 0 || pos0 + wq * 32 + 31 - kt < window);
       float m_tile = -INFINITY;
       if (softcap > 0.f) {
+        // A cap is chosen beyond what scores usually reach: while every score of this warp's half tile is within it
+        // (|scale * s / cap| <= 1), tanh is a polynomial on the packed 32-bit pipe; otherwise it goes through exp2 and
+        // 1 / x on the special-function unit, which bounds the tile with three of its operations per score.
+        float amax = 0.f;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
+        for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fabsf(sv[c]));
+        if (__all_sync(0xffffffffu, amax * ct <= 1.f)) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float2 y = capped2(make_float2(sv[c], sv[c + 1]), ct, c4);
+            sv[c] = y.x, sv[c + 1] = y.y;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
+        }
       } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) sv[c] *= c0;
