@@ -173,6 +173,23 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
         "r"(__float_as_uint(v[15])) : "memory");
 }
 
+// The 64-key tiles a tile of query rows reads (and its first key), and into how many runs they are cut: `n_parts` runs for
+// every tile when `run_tiles` is 0; otherwise as many runs of at most `run_tiles` key tiles as the tile needs, at most
+// n_parts (short tiles then stay whole and write their rows themselves, long ones are shared between blocks).
+__device__ __forceinline__ int tile_key_tiles(int row0, int nrows, const int* positions, const int* row_req, int window,
+                                              int* kt_first) {
+  const int pos0 = positions[row0];
+  const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  *kt_first = (lo / BKV) * BKV;
+  return row_req[row0] < 0 ? 0 : (pos0 + nrows - 1 - *kt_first) / BKV + 1;
+}
+__device__ __forceinline__ int tile_runs(int n_key_tiles, int n_parts, int run_tiles) {
+  if (n_parts <= 1) return 1;
+  if (run_tiles <= 0) return n_parts;
+  const int p = (n_key_tiles + run_tiles - 1) / run_tiles;
+  return p < 1 ? 1 : (p > n_parts ? n_parts : p);
+}
+
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
@@ -180,7 +197,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
                        float scale, float softcap, int window, __nv_bfloat16* __restrict__ out,
-                       int* __restrict__ error_flag, int n_parts, float* __restrict__ partial) {
+                       int* __restrict__ error_flag, int n_parts, int run_tiles, float* __restrict__ partial) {
   constexpr int NSUB = D / 64;                            // 64-element sub-tiles along the head dimension
   constexpr int Q_BYTES = BMQ * D * 2;
   constexpr int KV_BYTES = BKV * D * 2;                   // one K tile (or one V tile)
@@ -209,9 +226,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   float* s_max = (float*)(tmem_slot + 2);                 // [2 tile parities][2 halves][128 rows]; later [2][128] sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // tiles late in a request have the most keys: they start first.  With n_parts > 1 the keys of a tile are cut into
-  // that many runs, one block each (blockIdx.z); the blocks leave unnormalised partial rows that a second kernel merges.
-  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, part = blockIdx.z;
+  // Blocks are numbered (tile, run, head) with the head fastest and the last tile first: tiles late in a request have
+  // the most keys, and blocks start in the order of their numbers.  With n_parts > 1 the keys of a tile are cut into
+  // runs, one block each; the blocks of a tile with several runs leave unnormalised partial rows that a second kernel
+  // merges, and a block whose run its tile does not have leaves at once.
+  const int h = blockIdx.x % nh, slot = blockIdx.x / nh;
+  const int tile = (int)(gridDim.x / (nh * n_parts)) - 1 - slot / n_parts, part = slot % n_parts;
   const int row0 = tile_row0[tile], nrows = tile_nrows[tile];
   const int kvh = h / (nh / nkv);
 
@@ -239,13 +259,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
   const int req = row_req[row0];
   const int pos0 = positions[row0];
-  const int pos_last = pos0 + nrows - 1;
-  const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int kt_first = (lo / BKV) * BKV;
-  const int n_tiles_all = req < 0 ? 0 : (pos_last - kt_first) / BKV + 1;
-  const int per_part = (n_tiles_all + n_parts - 1) / n_parts;
+  int kt_first;
+  const int n_tiles_all = tile_key_tiles(row0, nrows, positions, row_req, window, &kt_first);
+  const int my_parts = tile_runs(n_tiles_all, n_parts, run_tiles);
+  const bool idle = part >= my_parts;                     // this tile has fewer runs than the launch has blocks per tile
+  const int per_part = (n_tiles_all + my_parts - 1) / my_parts;
   const int kt_begin = kt_first + part * per_part * BKV;
-  const int n_tiles = max(0, min(per_part, n_tiles_all - part * per_part));
+  const int n_tiles = idle ? 0 : max(0, min(per_part, n_tiles_all - part * per_part));
 
   if (warp == 8) {
     // ---- TMA producer --------------------------------------------------------------------------------------
@@ -425,7 +445,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     s_max[half * BMQ + r] = l_sum;
     asm volatile("bar.sync 2, 256;" ::: "memory");
     l_sum = s_max[r] + s_max[BMQ + r];
-    if (n_parts > 1) {
+    if (idle) {
+      // nothing to do and nothing to write
+    } else if (my_parts > 1) {
       // ---- one of several runs of keys: leave O as it is (scaled by 2^-m), with m and the sum, for the merge ----------
       const bool run_ok = __all_sync(0xffffffffu, ok && n_tiles > 0 && *s_abort == 0);
       const bool have = run_ok && r < nrows && l_sum > 0.f;     // a row that saw no key in this run leaves m = -inf
@@ -476,16 +498,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ tile_row0,
-                          const int* __restrict__ tile_nrows, int nh, int n_parts, __nv_bfloat16* __restrict__ out) {
+                          const int* __restrict__ tile_nrows, const int* __restrict__ positions,
+                          const int* __restrict__ row_req, int window, int nh, int n_parts_max, int run_tiles,
+                          __nv_bfloat16* __restrict__ out) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int tile = blockIdx.x, r = blockIdx.y;
   if (r >= tile_nrows[tile]) return;
+  int kt_first;
+  const int n_parts = tile_runs(tile_key_tiles(tile_row0[tile], tile_nrows[tile], positions, row_req, window, &kt_first),
+                                n_parts_max, run_tiles);
+  if (n_parts == 1) return;                                   // a tile with one run wrote its rows itself
   const int row = tile_row0[tile] + r;
   constexpr int REC = D + 4;
   for (int e = threadIdx.x; e < nh * (D / 4); e += blockDim.x) {
     const int h = e / (D / 4), c4 = e - h * (D / 4);
-    const float* rec0 = partial + ((size_t)row * nh + h) * n_parts * REC;
+    const float* rec0 = partial + ((size_t)row * nh + h) * n_parts_max * REC;
     float m = -INFINITY;
     for (int p = 0; p < n_parts; ++p) m = fmaxf(m, rec0[(size_t)p * REC + D]);
     float l = 0.f;
@@ -554,8 +582,8 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 template <int D>
 int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
            const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
-           float scale, float softcap, int window, void* out, int* error_flag, int n_parts, float* partial,
-           cudaStream_t stream) {
+           float scale, float softcap, int window, void* out, int* error_flag, int n_parts, int run_tiles,
+           float* partial, cudaStream_t stream) {
   const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256 + 4 * BMQ * 4;
   static bool configured = false;
   if (!configured) {
@@ -565,13 +593,13 @@ int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, 
     }
     configured = true;
   }
-  kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles, nh, n_parts), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
+  kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles * n_parts * nh), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
             positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out,
-            error_flag, n_parts, partial);
+            error_flag, n_parts, run_tiles, partial);
   KF_CHECK_LAUNCH();
   if (n_parts > 1) {
     kf_launch(attn_prefill_merge_kernel<D>, dim3(n_tiles, BMQ), dim3(128), 0, stream, (const float*)partial, tile_row0,
-              tile_nrows, nh, n_parts, (__nv_bfloat16*)out);
+              tile_nrows, positions, row_req, window, nh, n_parts, run_tiles, (__nv_bfloat16*)out);
     KF_CHECK_LAUNCH();
   }
   return KF_OK;
@@ -585,11 +613,20 @@ KF_API int kf_attention_prefill_tc_supported(int d, int page_size, const void* q
 }
 KF_API int kf_attention_prefill_tc_tile_rows() { return BMQ; }
 
-// Into how many runs the keys of every tile are cut so that the blocks fill the GPU: 1 when tiles x heads fill half of it;
-// at most 8, and never so many that a run of the longest tile has fewer than two 64-key tiles.
-KF_API int kf_attention_prefill_tc_parts(int n_tiles, int nh, int max_keys) {
-  // The partial rows cost a write, a read and a second kernel (about 25 us at 2,048 rows x 8 heads), which only pays
-  // when the blocks would otherwise leave more than half of the SMs idle.
+static int g_forced_parts = 0, g_forced_run_tiles = 0;
+// A fixed plan instead of the planner's (0, 0 gives its choice back): runs per tile and key tiles per run.
+KF_API void kf_set_attention_prefill_plan(int parts, int run_tiles) { g_forced_parts = parts, g_forced_run_tiles = run_tiles; }
+
+// Into how many runs the keys of a tile are cut, and how long a run may be (0: every tile gets `parts` runs).
+// Few blocks (tiles x heads fill less than half of the GPU): every tile is cut so that the blocks fill it; at most 8
+// runs, and never so many that a run of the longest tile has fewer than two 64-key tiles.
+// About one block per SM and long tiles (a whole prompt of 2,048 tokens x 8 heads: the launch lasts as long as the tile
+// with the most keys, twice the average): cutting only the tiles longer than 1/2 or 5/8 of the longest in two
+// (kf_set_attention_prefill_plan(2, 16 or 20)) measured within +-0.5 % of uncut over the 26-layer step, three or four
+// runs slower: the partial rows cost a write, a read and a second kernel.  So such launches stay uncut.
+KF_API int kf_attention_prefill_tc_plan(int n_tiles, int nh, int max_keys, int* run_tiles) {
+  *run_tiles = 0;
+  if (g_forced_parts > 0) { *run_tiles = g_forced_run_tiles; return g_forced_parts; }
   const long blocks = (long)n_tiles * nh;
   if (blocks <= 0 || 2 * blocks > 148) return 1;
   int parts = (int)(148 / blocks);
@@ -600,20 +637,21 @@ KF_API int kf_attention_prefill_tc_parts(int n_tiles, int nh, int max_keys) {
 }
 
 // q, out: [T, nh*d] bfloat16; pages: [n_pages, 2, nkv, page_size, d] bfloat16.  tile_row0/tile_nrows: tiles of up to 128
-// consecutive rows of one request (consecutive positions).  n_parts > 1 cuts every tile's keys into that many runs;
+// consecutive rows of one request (consecutive positions).  n_parts > 1 cuts a tile's keys into up to that many runs
+// (every tile's when run_tiles is 0, else those of tiles with more than run_tiles key tiles);
 // `partial` then holds T * nh * n_parts * (d + 4) floats.
 KF_API int kf_attention_prefill_tc(const void* q, void* out, const void* pages, long n_pages, int T, const int* tile_row0,
                                    const int* tile_nrows, int n_tiles, const int* positions, const int* row_req,
                                    const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
-                                   float softcap, int window, int* error_flag, int n_parts, float* partial,
+                                   float softcap, int window, int* error_flag, int n_parts, int run_tiles, float* partial,
                                    cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
   if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0) return KF_ERR_SIZE;
-  if (n_parts < 1 || n_parts > 8 || (n_parts > 1 && !partial)) return KF_ERR_SIZE;
+  if (n_parts < 1 || n_parts > 8 || (n_parts > 1 && !partial) || run_tiles < 0) return KF_ERR_SIZE;
   CUtensorMap tq, tkv;
   if (!tensor_map(q, T, (long)nh * d, BMQ, &tq)) return KF_ERR_SETUP;
   if (!tensor_map(pages, n_pages * 2 * nkv * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
-#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, n_parts, partial, stream
+#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, n_parts, run_tiles, partial, stream
   switch (d) {
     case 64: return launch<64>(KF_ARGS);
     case 128: return launch<128>(KF_ARGS);

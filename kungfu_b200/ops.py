@@ -549,11 +549,12 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
             and lib.kf_attention_prefill_tc_supported(head_dim, cache.page_size, _p(q), _p(pages))):
         sc = _dev_scratch(q.device)
         max_keys = min(ctx.max_kv_len, window + 128) if window else ctx.max_kv_len
-        parts = lib.kf_attention_prefill_tc_parts(ctx.n_wide, n_heads, int(max_keys)) if split_prompt_keys else 1
+        run_tiles = ctypes.c_int(0)
+        parts = lib.kf_attention_prefill_tc_plan(ctx.n_wide, n_heads, int(max_keys), ctypes.byref(run_tiles)) if split_prompt_keys else 1
         partial = _partial(q.device, T * n_heads * parts * (head_dim + 4)) if parts > 1 else None
         _check(lib.kf_attention_prefill_tc(_p(q), _p(out), _p(pages), ctypes.c_long(pages.shape[0]), T, _p(ctx.wide_row0),
-                                           _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), parts, _p(partial),
-                                           _stream()),
+                                           _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), parts, run_tiles.value,
+                                           _p(partial), _stream()),
                "attention (prefill, tcgen05)")
         if parts > 1:
             add_launches(1)

@@ -463,6 +463,42 @@ def test_prompt_attention_with_keys_cut_into_runs(ops, nh, nkv, d, window, lens)
     assert rel_err(outs[0][0], outs[1][0]) < 6e-3
 
 
+@pytest.mark.parametrize("nh,nkv,d,window,lens", [(8, 4, 256, None, [2048]), (16, 4, 64, None, [1500]),
+                                                  (8, 2, 128, 1500, [2048]), (8, 4, 256, None, [1100, 300])])
+def test_prompt_attention_with_only_the_long_tiles_cut(ops, nh, nkv, d, window, lens):
+    """A launch may cut only its long tiles (here: those with more than half of the longest tile's keys, into two runs
+    that a second kernel merges) while the others stay whole and write their rows themselves.  Rows of both kinds of
+    tile against float64 and against the launch that cuts nothing."""
+    P = 64
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=35)
+    rows = [(r, p) for r, n in enumerate(lens) for p in range(n)]
+    g = torch.Generator().manual_seed(36)
+    q = torch.randn(len(rows), nh, d, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), [], list(range(len(rows))))
+    outs = []
+    key_tiles = (min(max(lens), window + 128 if window else max(lens)) + 63) // 64
+    for split in (True, False):
+        ops.library().kf_set_attention_prefill_plan(2 if split else 1, (key_tiles + 1) // 2 if split else 0)
+        try:
+            out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+            before = ops.launch_count()
+            ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, 50.0, window)
+            outs.append((out, ops.launch_count() - before))
+        finally:
+            ops.library().kf_set_attention_prefill_plan(0, 0)
+    ops.raise_on_device_error()
+    assert outs[0][1] == 2 and outs[1][1] == 1, "long tiles cut into runs: the attention kernel and the merge"
+    assert not torch.isnan(outs[0][0].float()).any()
+    step = 7                                                        # every 7th row and the last rows of every request
+    pick = sorted(set(range(0, len(rows), step)) | {i for i, (r, p) in enumerate(rows) if p >= lens[r] - 3})
+    ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, 50.0, window) for i, (r, p) in ((i, rows[i]) for i in pick)])
+    assert rel_err(outs[0][0].view(len(rows), nh, d)[pick], ref) < 1e-2
+    assert rel_err(outs[1][0].view(len(rows), nh, d)[pick], ref) < 1e-2
+    assert rel_err(outs[0][0], outs[1][0]) < 6e-3
+
+
 def _plant(pages, table, req, j, kvh, P, key=None, value=None):
     """Overwrite key and/or value j of a request in its pages (host tensors)."""
     pg = int(table[req, j // P])
