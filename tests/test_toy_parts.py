@@ -3,7 +3,9 @@
 * `RunningMean`: a mixer with a state of its own (a fixed-size per-request state: the sum of its inputs and their
   count); token i gets W . mean(x_0..x_i).
 * `RoutedFfn`: a feed-forward with routing (two experts, the router's top choice, 32-bit router logits).
-* a toy architecture that mixes both with the framework's paged attention layer by layer, names one layer twice in
+* `ClockHands`: another position encoding (only the first half of a head is rotated, hand i turns by position / (i + 2):
+  no power law, no base), handed to the framework's attention in place of its rotary embedding.
+* a toy architecture that mixes these with the framework's paged attention layer by layer, names one layer twice in
   its schedule and lets one call read the cache another call wrote.
 The toy model is compared with a whole-sequence computation written here, for whole prompts, portions and
 single tokens, several requests per step.
@@ -22,8 +24,8 @@ def _define():
     from kungfu_b200 import registry
     from kungfu_b200.config.base import KeyReader
     from kungfu_b200.parts import (DecoderModel, Embedding, FeedForward, FixedState, LayerCall, LmHead, Mixer,
-                                   PagedAttention, RmsNorm, Rope, SandwichBlock, known, register_feed_forward,
-                                   register_mixer)
+                                   PagedAttention, PositionEncoding, RmsNorm, SandwichBlock, known,
+                                   register_feed_forward, register_mixer, register_position)
     from kungfu_b200.weights.store import TensorSpec
 
     class RunningMean(Mixer):
@@ -64,9 +66,20 @@ def _define():
                 y[sel] = torch.relu(xf[sel] @ self.w_in[e].float().T) @ self.w_out[e].float().T
             return y
 
+    class ClockHands(PositionEncoding):
+        graph_safe = False
+
+        def __init__(self, head_dim, device):
+            self.turn = (1.0 / torch.arange(2, 2 + head_dim // 4, dtype=torch.float32)).to(device)   # rotates head_dim / 2
+
+        def rotation(self, ctx):
+            angle = ctx.positions[:ctx.n_rows].to(torch.float32)[:, None] * self.turn[None, :]
+            return torch.cos(angle).contiguous(), torch.sin(angle).contiguous()
+
     if "running_mean" not in known("mixer"):
         register_mixer("running_mean", RunningMean)
         register_feed_forward("routed", RoutedFfn)
+        register_position("clock_hands", ClockHands)
 
     @dataclass(frozen=True)
     class ToyConfig:
@@ -106,7 +119,7 @@ def _define():
         from kungfu_b200.parts import make
         H, I, nh, d = c.hidden_size, c.intermediate_size, c.num_attention_heads, c.head_dim
         emb = Embedding(w.take("emb", (c.vocab_size, H)))
-        rope = Rope(d, 10000.0, w.device)
+        rope = make("position", "clock_hands", d, w.device)
         mixers = [make("mixer", "running_mean", w.take("l0.mean_w", (H, H))),
                   PagedAttention(w.take("l1.wqkv", (3 * nh * d, H)), w.take("l1.wo", (H, nh * d)), n_heads=nh,
                                  n_kv_heads=nh, head_dim=d, scale=d ** -0.5, position=rope)]
@@ -146,8 +159,13 @@ def _plain(cfg, t, tokens):
         import plain_gemma2 as pg
         qkv = x @ t["l1.wqkv"].to(dt).T
         q, k, v = [qkv[:, i * nh * d:(i + 1) * nh * d].view(T, nh, d) for i in range(3)]
-        cos, sin = pg.rope_angles(torch.arange(T), d, 10000.0, dt)
-        q, k = pg.apply_rope(q, cos, sin), pg.apply_rope(k, cos, sin)
+        angle = torch.arange(T, dtype=dt)[:, None] / torch.arange(2, 2 + d // 4, dtype=dt)[None, :]
+
+        def turn(x):                             # the first d / 2 elements of a head, element i paired with i + d / 4
+            a, b = x[..., :d // 4], x[..., d // 4:d // 2]
+            c, s_ = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            return torch.cat([a * c - b * s_, a * s_ + b * c, x[..., d // 2:]], -1)
+        q, k = turn(q), turn(k)
         if "kv" in kept:                         # the second call reads what the first call cached
             k, v = kept["kv"]
         else:
