@@ -318,8 +318,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // warp-private shared memory by cp.async (double-buffered, so the next tile is in flight while this one is used),
 // S = Q K^T (16 heads x 16 keys) and O += P V run on mma.sync with 32-bit accumulators, the online softmax is the
 // one of the prompt kernel.  Warps are merged through shared memory in warp order, splits by the last block.
-constexpr int DM_WARPS = 4;
-constexpr int DM_STAGES = 3;                     // tiles of a warp in shared memory (one in use, the others in flight)
+constexpr int DM_WARPS = 8;                       // two per scheduler: a warp's tile is one chain of dependent instructions
+constexpr int DM_BUFS = 3;                        // buffers of one key tile or one value tile per warp: one in use, two in flight
 constexpr int DM_KEYS = 16;                       // keys per warp tile
 
 // With `qkv` given (the 32-bit q|k|v rows of the step, a row = [nh*D | nkv*D | nkv*D]) the kernel also does what the
@@ -344,7 +344,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   constexpr int TILE = DM_KEYS * D;                               // elements of one key (or value) tile
   extern __shared__ __align__(128) uint8_t dm_smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dm_smem);  // [16][D]
-  __nv_bfloat16* sKV = sQ + 16 * D;                               // [warp][stage][K|V][16][D]
+  __nv_bfloat16* sKV = sQ + 16 * D;                               // [warp][buffer][16][D]
   __shared__ float sm_ml[DM_WARPS][16][2];
   __shared__ int s_last;
 
@@ -378,41 +378,43 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
   const size_t v_off = (size_t)nkv * head_stride;
-  __nv_bfloat16* my = sKV + (size_t)warp * DM_STAGES * 2 * TILE;  // [stage][K|V]
+  __nv_bfloat16* my = sKV + (size_t)warp * DM_BUFS * TILE;        // [buffer]
 
-  auto load_tile = [&](int tile, int stage) {
+  // A warp walks its tiles (warp, warp + DM_WARPS, ...) as the sequence K0 V0 K1 V1 ...: item n is the keys (n even) or
+  // the values (n odd) of its tile n / 2 and lands in buffer n % DM_BUFS.
+  const int n_mine = n_tiles > warp ? (n_tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
+  const int n_loads = 2 * n_mine;
+  long row_base = -1;                                             // lanes 0..15: where key j0 + lane of the item's tile lies
+  auto load_item = [&](int n, int buf) {
+    const int tile = warp + (n >> 1) * DM_WARPS;
     const int j0 = k_begin + tile * DM_KEYS;
     // lanes 0..15 look up the row of key j0 + lane; everyone fetches a row's base by shuffle
-    long base = -1;
+    row_base = -1;
     if (lane < DM_KEYS) {
       const int j = j0 + lane;
       if (j < k_end) {
         const int page = tab[j / page_size];
-        if (page >= 0) base = ((long)page * 2 * nkv + kvh) * (long)head_stride + (long)(j % page_size) * D;
+        if (page >= 0) row_base = ((long)page * 2 * nkv + kvh) * (long)head_stride + (long)(j % page_size) * D;
       }
     }
-    __nv_bfloat16* dk = my + (size_t)stage * 2 * TILE;
-    __nv_bfloat16* dv = dk + TILE;
+    __nv_bfloat16* dst = my + (size_t)buf * TILE;
+    const size_t off = (n & 1) ? v_off : 0;
 #pragma unroll
     for (int i = 0; i < (DM_KEYS * CH + 31) / 32; ++i) {
       const int idx = lane + 32 * i;
       const int r = idx / CH, c = idx - r * CH;
-      const long b = __shfl_sync(0xffffffffu, base, r & 15);
+      const long b = __shfl_sync(0xffffffffu, row_base, r & 15);
       if (idx < DM_KEYS * CH) {
         const bool ok = b >= 0;
-        const __nv_bfloat16* src = pages + (ok ? b : 0) + c * 8;
-        cp_async16(tile_ptr<D>(dk, r, c), src, ok);
-        cp_async16(tile_ptr<D>(dv, r, c), src + v_off, ok);
+        cp_async16(tile_ptr<D>(dst, r, c), pages + (ok ? b : 0) + off + c * 8, ok);
       }
     }
   };
 
-  // first tiles of this warp, except the one with the row's own key: keys of earlier steps
+  // the first items of this warp, except those of the tile with the row's own key: keys of earlier steps
 #pragma unroll
-  for (int s = 0; s < DM_STAGES - 1; ++s) {
-    const int tile = warp + s * DM_WARPS;
-    if (tile < n_tiles && tile != own_tile) load_tile(tile, s);
-  }
+  for (int n = 0; n < DM_BUFS; ++n)
+    if (n < n_loads && warp + (n >> 1) * DM_WARPS != own_tile) load_item(n, n);
   kf_pdl_wait();
   q = kf_produced(q), qkv = kf_produced(qkv), cos_t = kf_produced(cos_t), sin_t = kf_produced(sin_t);
 
@@ -466,15 +468,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   }
   __syncthreads();                                                // Q in place; the new key and value are in the page
   {
-    // the own-key tile, if it is one of this warp's first tiles; then all of them are one group, and empty groups keep
-    // the count of groups per stage that the loop below relies on
+    // the own-key tile, if it is one of this warp's first tiles; then all first items are one group, and empty groups
+    // keep the count of one group per item that the loop below relies on
 #pragma unroll
-    for (int s = 0; s < DM_STAGES - 1; ++s) {
-      const int tile = warp + s * DM_WARPS;
-      if (tile < n_tiles && tile == own_tile) load_tile(tile, s);
-    }
+    for (int n = 0; n < DM_BUFS; ++n)
+      if (n < n_loads && warp + (n >> 1) * DM_WARPS == own_tile) load_item(n, n);
 #pragma unroll
-    for (int s = 0; s < DM_STAGES - 1; ++s) cp_async_commit();
+    for (int n = 0; n < DM_BUFS; ++n) cp_async_commit();
   }
 
   float o_acc[NT_O][4];
@@ -483,29 +483,44 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
 
-  int it = 0;
-  for (int tile = warp; tile < n_tiles; tile += DM_WARPS, ++it) {
-    const int stage = it % DM_STAGES;
-    const int ahead = tile + (DM_STAGES - 1) * DM_WARPS;
-    if (ahead < n_tiles) load_tile(ahead, (it + DM_STAGES - 1) % DM_STAGES);
-    cp_async_commit();
-    cp_async_wait<DM_STAGES - 1>();
+  int buf = 0;                                                     // buffer of the item in use: item n is in n % DM_BUFS
+  for (int it = 0; it < n_mine; ++it) {
+    const int tile = warp + it * DM_WARPS;
+    // ---- the keys of the tile: item 2 it, its group and at most two younger ones are outstanding -----------------------
+    cp_async_wait<DM_BUFS - 1>();
     __syncwarp();
-    const __nv_bfloat16* k_s = my + (size_t)stage * 2 * TILE;
-    const __nv_bfloat16* v_s = k_s + TILE;
+    const __nv_bfloat16* k_s = my + (size_t)buf * TILE;
     const int j0 = k_begin + tile * DM_KEYS;
 
-    float s_acc[2][4];
+    // two accumulators per 8 keys (even and odd steps along the head), so that the chain of dependent MMAs is half as long
+    float s_acc[2][4], s_odd[2][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
+    for (int n = 0; n < 2; ++n) {
+      s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f;
+      s_odd[n][0] = s_odd[n][1] = s_odd[n][2] = s_odd[n][3] = 0.f;
+    }
 #pragma unroll
     for (int ks = 0; ks < KS_QK; ++ks) {
       uint32_t a[4], b[4];
       ldmatrix_x4(a, tile_ptr<D>(sQ, lane & 15, ks * 2 + (lane >> 4)));
       ldmatrix_x4(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(k_s), (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
-      mma_bf16(s_acc[0], a, b[0], b[1]);
-      mma_bf16(s_acc[1], a, b[2], b[3]);
+      if (ks & 1) {
+        mma_bf16(s_odd[0], a, b[0], b[1]);
+        mma_bf16(s_odd[1], a, b[2], b[3]);
+      } else {
+        mma_bf16(s_acc[0], a, b[0], b[1]);
+        mma_bf16(s_acc[1], a, b[2], b[3]);
+      }
     }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_acc[n][e] += s_odd[n][e];
+    }
+    __syncwarp();                                                  // every lane has read the keys: their buffer takes item 2 it + 3
+    if (2 * it + DM_BUFS < n_loads) load_item(2 * it + DM_BUFS, buf);
+    cp_async_commit();
+    buf = buf + 1 == DM_BUFS ? 0 : buf + 1;
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -554,6 +569,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
     a[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
     a[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
     a[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
+    // ---- the values of the tile: item 2 it + 1 ----------------------------------------------------------------------
+    cp_async_wait<DM_BUFS - 1>();
+    __syncwarp();
+    const __nv_bfloat16* v_s = my + (size_t)buf * TILE;
 #pragma unroll
     for (int np = 0; np < NT_O / 2; ++np) {
       uint32_t b[4];
@@ -561,7 +580,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
       mma_bf16(o_acc[2 * np], a, b[0], b[1]);
       mma_bf16(o_acc[2 * np + 1], a, b[2], b[3]);
     }
-    __syncwarp();                                                  // this stage is refilled on the next turn
+    __syncwarp();                                                  // the values' buffer takes item 2 it + 4
+    if (2 * it + 1 + DM_BUFS < n_loads) load_item(2 * it + 1 + DM_BUFS, buf);
+    cp_async_commit();
+    buf = buf + 1 == DM_BUFS ? 0 : buf + 1;
   }
   cp_async_wait<0>();
   // ---- merge the warps through shared memory (the tile buffers are free now) ---------------------------------------
@@ -618,20 +640,30 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   if (tid == 0) counters[cidx] = 0;
 }
 
+// Blocks of the tensor-core decode kernel that one SM holds at a time (shared memory or registers, whichever binds), as
+// the runtime reports it; also sets the kernel's shared-memory limit.  0 if that fails.
+template <int D>
+int decode_mma_blocks_per_sm() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  const size_t smem = (size_t)(16 * D + DM_WARPS * DM_BUFS * DM_KEYS * D) * 2;
+  int n = 0;
+  if (cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_mma_kernel<D>, DM_WARPS * 32, smem) != cudaSuccess) {
+    kf_record_cuda_error(cudaGetLastError());
+    return 0;
+  }
+  cached = n;
+  return n;
+}
+
 template <int D>
 int launch_decode_mma(const float* qkv, const float* cos_t, const float* sin_t, int rot, int write_kv,
                       const void* q, const void* pages, const int* items, int n_items, const int* positions,
                       const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
                       float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
-  const size_t smem = (size_t)(16 * D + DM_WARPS * DM_STAGES * 2 * DM_KEYS * D) * 2;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      kf_record_cuda_error(cudaGetLastError());
-      return KF_ERR_SETUP;
-    }
-    configured = true;
-  }
+  const size_t smem = (size_t)(16 * D + DM_WARPS * DM_BUFS * DM_KEYS * D) * 2;
+  if (decode_mma_blocks_per_sm<D>() < 1) return KF_ERR_SETUP;
   kf_launch(attn_decode_mma_kernel<D>, dim3(n_items * nkv, n_splits), dim3(DM_WARPS * 32), smem, stream,
             (const __nv_bfloat16*)q, qkv, cos_t, sin_t, rot, write_kv, (__nv_bfloat16*)const_cast<void*>(pages), items, n_items,
             positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters,
@@ -674,9 +706,10 @@ KF_API void kf_set_attention_decode_splits(int splits) { g_forced_splits = split
 KF_API int kf_attention_decode_mma_plan(int n_items, int nh, int nkv, int d, int max_keys, int* splits_out) {
   if (g_forced_splits > 0) { *splits_out = g_forced_splits; return KF_OK; }
   const long blocks = (long)n_items * nkv;
-  // shared memory allows 227 KB / (smem per block) blocks per SM; fill one wave
-  const long smem = (long)(16 * d + DM_WARPS * DM_STAGES * 2 * DM_KEYS * d) * 2 + 1024;
-  long per_sm = (227 * 1024) / smem;
+  // fill one wave: as many splits as resident blocks allow
+  long per_sm = d == 256 ? decode_mma_blocks_per_sm<256>() : d == 128 ? decode_mma_blocks_per_sm<128>()
+              : d == 64 ? decode_mma_blocks_per_sm<64>() : d == 32 ? decode_mma_blocks_per_sm<32>()
+              : d == 16 ? decode_mma_blocks_per_sm<16>() : 0;
   if (per_sm > 8) per_sm = 8;
   if (per_sm < 1) per_sm = 1;
   int splits = (int)((148 * per_sm) / blocks);
