@@ -275,7 +275,8 @@ def run_ours(args) -> dict:
               "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
               "sliding_window": cfg.sliding_window, "global_batch": B, "seq_len": ctx_len, "page_size": page,
               "parallelism": "single", "weights": "random bf16", "cache": "bf16 random fill", "l2": "inputs larger than L2",
-              "cuda_graphs": bool(getattr(runner, "cuda_graphs", False))}
+              "cuda_graphs": bool(getattr(runner, "cuda_graphs", False)),
+              "e2e_reads": "ids of step n read on the host while step n+1 runs" if eng.pipeline else "every step before the next"}
     return {"metric": "decode tokens/s (batch 8, context 8192, Gemma 2 2B sizes, 1 B200)" if (args.size, B, ctx_len) == ("2b", 8, 8192)
             else f"decode tokens/s (batch {B}, context {ctx_len}, Gemma 2 {args.size} sizes, 1 B200)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,

@@ -30,11 +30,14 @@ class Engine:
     def __init__(self, model_dir: str | None = None, *, config=None, seed: int = 0, dtype="bfloat16", device="cuda:0",
                  ctx: int | str = 4096, batch: int = 512, parallel: int = 8, page_size: int | None = None,
                  max_tokens_in_cache: int | None = None, events: bool = False, runner: Runner | None = None,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, pipeline: bool = True):
         """`model_dir`: folder with config.json and model.safetensors; or `config` (typed configuration, dictionary
         or config.json path) with `seed` for random weights.  `ctx`: context length per request ('auto' = the
         model's trained length); `batch`: most tokens one step runs; `parallel`: most live requests.
-        `max_tokens_in_cache`: size of each cache group's pool in tokens (default: parallel * ctx)."""
+        `max_tokens_in_cache`: size of each cache group's pool in tokens (default: parallel * ctx).
+        `pipeline`: greedy decode steps are launched before the tokens of the step before them have been read (they
+        stay on the device as the next step's input), so `step()` returns a step's tokens one call later and the GPU
+        does not wait for the host between steps."""
         from .. import api
         self.events = events
         if runner is not None:
@@ -68,6 +71,8 @@ class Engine:
         dev = self.runner.device
         self._ids_dev = None
         self._cand_k = CANDIDATES
+        self.pipeline = bool(pipeline)
+        self._inflight = None                  # (requests and their output places, picked ids on the device, fetch)
 
     # ---- requests ---------------------------------------------------------------------------------------
     def add_request(self, ids: Sequence[int], sampling: Sampling | None = None, *, max_tokens: int = 64,
@@ -92,35 +97,101 @@ class Engine:
         return request_id
 
     def cancel(self, request_id: Hashable) -> None:
+        self.flush()
         req = self.requests[request_id]
         if req.status != "finished":
             self.scheduler.finish(req, "cancelled")
 
     @property
     def idle(self) -> bool:
-        return self.scheduler.idle
+        return self.scheduler.idle and self._inflight is None
+
+    # ---- tokens that a launched step has not delivered yet ---------------------------------------------------
+    def flush(self) -> list[tuple]:
+        """Wait for the step in flight, if any, and return its events."""
+        return self._collect() if self._inflight is not None else []
+
+    def _collect(self, flight=None) -> list[tuple]:
+        """Read the tokens of a launched step, put them where their placeholders stand and see which of them end a
+        request by their value."""
+        if flight is None:
+            flight, self._inflight = self._inflight, None
+        items, _picked, fetch = flight
+        events = []
+        for (r, at), tok in zip(items, fetch()):
+            if at >= len(r.output):                      # produced after the token that ended the request: dropped
+                continue
+            r.output[at] = int(tok)
+            reason = None
+            if not r.ignore_eos and int(tok) in r.eos:
+                del r.output[at + 1:]                    # the placeholder of a step launched since
+                if r.status != "finished":
+                    self.scheduler.finish(r, "eos")
+                else:
+                    r.finish_reason = "eos"
+                reason = "eos"
+            elif r.status == "finished" and at == len(r.output) - 1:
+                reason = r.finish_reason
+            events.append((r.id, int(tok), reason))
+            if reason is not None and self.events:
+                self._request_event(r)
+        return events
+
+    def _tokens_needed_first(self) -> bool:
+        """True if the coming plan must not be made on counts alone: a request may be admitted or preempted (its
+        tokens are then read back as a prompt), which needs every token's value."""
+        sched = self.scheduler
+        if sched.waiting:
+            return True
+        running = len(sched.running)
+        return any(g.pool.n_free < running for g in self.runner.cache.groups)
 
     # ---- one step -----------------------------------------------------------------------------------------
     def step(self) -> list[tuple]:
         """Plan and run one step.  Returns (request id, token, finish reason or None) for every token produced,
-        and (request id, None, reason) for requests that ended without one (no_fit)."""
+        and (request id, None, reason) for requests that ended without one (no_fit).  With `pipeline`, the tokens of
+        a greedy decode step are returned by the next call (or by `flush()`); a request that one of them ends by its
+        value (an end-of-sequence id) has then already run one more step, whose token is dropped."""
+        events = []
+        if self._inflight is not None and self._tokens_needed_first():
+            events += self._collect()
         n_fin = len(self.scheduler.finished)
         plan = self.scheduler.schedule()
-        events = [(r.id, None, r.finish_reason) for r in self.scheduler.finished[n_fin:]]
+        events += [(r.id, None, r.finish_reason) for r in self.scheduler.finished[n_fin:]]
+        wanting = [p for p in plan if p.wants_logits]
+        greedy = bool(wanting) and all(p.request.sampling.greedy for p in wanting)
+        # a step of one token per request, all greedy: its tokens can stay on the device for the step after it
+        decode_only = self.pipeline and greedy and len(wanting) == len(plan) and all(p.n == 1 for p in plan)
+        feedback = None
+        if self._inflight is not None:
+            if decode_only and [id(p.request) for p in plan] == [id(r) for r, _ in self._inflight[0]]:
+                feedback = self._inflight[1]
+            else:                                        # another step than the one in flight was counted on
+                events += self._collect()
+                plan = [p for p in plan if p.request.status != "finished"]    # ended by a token that was in flight
+                wanting = [p for p in plan if p.wants_logits]
         if not plan:
             return events
         entries = []
         for p in plan:
             toks = p.request.slice(p.start, p.n)
             entries.append(StepEntry(p.request.id, toks, [p.n - 1] if p.wants_logits else []))
-        wanting = [p for p in plan if p.wants_logits]
-        greedy = bool(wanting) and all(p.request.sampling.greedy for p in wanting)
         if greedy:                                       # the largest logit is found in the step's own pass
-            logits, picked = self.runner.step(entries, greedy=True)
+            logits, picked = self.runner.step(entries, greedy=True, feedback=feedback)
         else:
             logits, picked = self.runner.step(entries), None
         for p in plan:
             self.scheduler.advance(p)
+        if decode_only and picked is not None:
+            fetch = self.runner.fetch_async(picked, len(wanting))
+            items = []
+            for p in wanting:
+                self.scheduler.on_token_pending(p.request)
+                items.append((p.request, len(p.request.output) - 1))
+            before, self._inflight = self._inflight, (items, picked, fetch)
+            if before is not None:                       # the step before this one: its tokens are read while this one runs
+                events += self._collect(before)
+            return events
         if wanting:
             tokens = picked.cpu().tolist() if picked is not None else self._pick(logits, [p.request for p in wanting])
             for p, tok in zip(wanting, tokens):
@@ -164,10 +235,10 @@ class Engine:
         """Token ids in, generated token ids out, one list per prompt (host lists both ways)."""
         ids = [self.add_request(p, sampling, max_tokens=max_tokens, eos=eos, ignore_eos=ignore_eos, seed=seed + i)
                for i, p in enumerate(prompts)]
-        while any(self.requests[i].status != "finished" for i in ids):
+        while any(self.requests[i].status != "finished" for i in ids) or self._inflight is not None:
             before = sum(len(self.requests[i].output) for i in ids)
             ev = self.step()
-            if not ev and before == sum(len(self.requests[i].output) for i in ids) and self.scheduler.idle:
+            if not ev and before == sum(len(self.requests[i].output) for i in ids) and self.idle:
                 break
         if self.runner.device.type == "cuda":
             ops.raise_on_device_error(self.runner.device)

@@ -238,3 +238,17 @@ class Scheduler:
         self._retire(req, key, reason)
         self.running = [r for r in self.running if r is not req]
         return reason
+
+    def on_token_pending(self, req: Request) -> str | None:
+        """Count a token that a step has produced but the host has not read yet: a placeholder takes its place in
+        `req.output` (the caller puts the value there later), and the request is retired if the count alone ends it
+        (length, context).  Whether the token ends the request by its value is for the caller to see when it arrives."""
+        req.output.append(0)
+        key = self._key(req)
+        code = self._lib.kf_sched_on_token(self._h, key, 0)
+        if code <= 0:
+            return None
+        reason = self._FINISH[code]
+        self._retire(req, key, reason)
+        self.running = [r for r in self.running if r is not req]
+        return reason

@@ -136,9 +136,11 @@ class Runner:
     _SECTIONS = ("tokens", "positions", "row_req", "logit_rows", "dec_rows", "pre_rows", "tile_row0", "tile_nrows",
                  "wide_row0", "wide_nrows", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot")
 
-    def _build_block(self, entries: Sequence[StepEntry], bucket: int | None):
+    def _build_block(self, entries: Sequence[StepEntry], bucket: int | None, feedback: torch.Tensor | None = None):
         """The step's integer block, built by the native host runtime (`kf_step_layout` / `kf_step_fill` in
         csrc/host_runtime.cpp) straight into a pinned staging block, and its copy to the device.
+        `feedback` (a device tensor of token ids, one per entry, for steps of single tokens) then overwrites the
+        block's tokens on the device: the host need not know them yet.
         Returns (info, device block): info[0] total ints, [1] rows, [2] requests, [3] wanted rows, [4] table width,
         [5] decode rows, [6] prompt rows, [7] tiles of 64, [8] tiles of 128, [9] longest kv length, [10] most rows of
         one request, then the offset of every section."""
@@ -170,14 +172,17 @@ class Runner:
             if slot[1] is None:
                 slot[1] = torch.cuda.Event()
             slot[1].record()
+        if feedback is not None:
+            at = int(info[11])                            # the tokens' section; row i is entry i in a step of single tokens
+            dev[at:at + n].copy_(feedback[:n])
         return info, dev, host
 
-    def _fill(self, entries: Sequence[StepEntry], bucket: int | None = None) -> StepContext:
+    def _fill(self, entries: Sequence[StepEntry], bucket: int | None = None, feedback=None) -> StepContext:
         """Build the step's integer block and the context that names its sections.  With `bucket` (decode-only
         steps replayed from a CUDA graph) the layout is the one of `bucket` single-row requests with full-width
         block tables, whatever the step holds: rows beyond the real ones are padding (request index -1) that every
         kernel skips."""
-        info, dev, host = self._build_block(entries, bucket)
+        info, dev, host = self._build_block(entries, bucket, feedback)
         ctx = StepContext(self)
         total, T, B, n_out, width, n_dec, n_pre, n_tiles, n_wide, max_kv, max_rows = (int(v) for v in info[:11])
         off = info[11:]
@@ -229,13 +234,16 @@ class Runner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry], greedy: bool = False):
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False, feedback: torch.Tensor | None = None):
         """Run the tokens of `entries` as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
         in the order of the entries and of each entry's `want`, or None when nothing is wanted.  The result
         lives in a buffer the next step overwrites.  Raises OutOfPages before touching anything when the
         pages for the new tokens cannot all be had.
         With `greedy` the index of the largest logit of every wanted row is computed in the same pass (inside the
-        replayed graph for decode steps) and the result is (logits, int32 token ids [wanted])."""
+        replayed graph for decode steps) and the result is (logits, int32 token ids [wanted]).
+        `feedback`: for a step in which every entry brings one token, a device tensor with those tokens in the order
+        of the entries (the ids an earlier greedy step picked, which the host has not read yet); the entries' own
+        token values are then ignored."""
         entries = list(entries)
         if not entries:
             return (None, None) if greedy else None
@@ -249,23 +257,47 @@ class Runner:
             for e in reserved:
                 self.cache.cancel_reservation(e.request)
             raise
+        if feedback is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("tokens can only be fed back on the device to a step of single tokens")
         bucket = self._graph_bucket(entries)
         picked = None
         if bucket is None:
-            ctx = self._fill(entries)
+            ctx = self._fill(entries, None, feedback)
             logits = self._forward(ctx)
             if greedy and logits is not None:
                 picked = self._argmax(logits)
         elif greedy and isinstance(bucket, int):
-            logits, picked = self._step_graphed(entries, ("greedy", bucket))
+            logits, picked = self._step_graphed(entries, ("greedy", bucket), feedback)
         else:
-            logits = self._step_graphed(entries, bucket)
+            logits = self._step_graphed(entries, bucket, feedback)
             if greedy and logits is not None:
                 picked = self._argmax(logits)
         for e in entries:
             self.cache.commit(e.request, len(e.tokens))
         self.steps_run += 1
         return (logits, picked) if greedy else logits
+
+    def fetch_async(self, ids: torch.Tensor, n: int):
+        """Start the copy of `ids[:n]` (token ids on the device) to pinned host memory, in stream order after the step
+        that wrote them and before anything that overwrites them; returns a function that waits for the copy and gives
+        the ids as a list."""
+        if self.device.type != "cuda":
+            vals = ids[:n].tolist()
+            return lambda: vals
+        ring = getattr(self, "_fetch_ring", None)
+        if ring is None or ring[0][0].numel() < n:
+            cap = max(64, 1 << (max(n, 1) - 1).bit_length())
+            ring = self._fetch_ring = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), torch.cuda.Event()] for _ in range(4)]
+            self._fetch_next = 0
+        buf, ev = ring[self._fetch_next]
+        self._fetch_next = (self._fetch_next + 1) % len(ring)
+        buf[:n].copy_(ids[:n], non_blocking=True)
+        ev.record()
+
+        def wait():
+            ev.synchronize()
+            return buf[:n].tolist()
+        return wait
 
     def _argmax(self, logits):
         from .. import ops
@@ -316,7 +348,7 @@ class Runner:
             if chain:
                 ops.chain_end()
 
-    def _step_graphed(self, entries, key):
+    def _step_graphed(self, entries, key, feedback=None):
         """First time a key is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
@@ -341,11 +373,11 @@ class Runner:
             return (logits, self._argmax(logits)) if pick else (logits, None)
 
         if state is not None and state["graph"] is not None:
-            self._build_block(entries, bucket)            # same layout as at capture; a replay needs no context object
+            self._build_block(entries, bucket, feedback)  # same layout as at capture; a replay needs no context object
             state["graph"].replay()
             ops.add_launches(state["kernels"])
             return result(state["logits"], state["picked"])
-        ctx = self._fill(entries, bucket)
+        ctx = self._fill(entries, bucket, feedback)
         if state is None:
             self._graphs[key] = {"generation": None, "graph": None, "seen": 1}
             logits, picked = run(ctx)

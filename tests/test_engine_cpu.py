@@ -49,12 +49,12 @@ def test_cpu_modes_match_plain(tmp_path, cpu_ops, cfg_dict, lengths, page, mode)
     assert all(f == g.pool.n_pages for f, g in zip(runner.cache.free_pages(), runner.cache.groups))
 
 
-def _engine(folder, cfg_dict, *, page, pool_tokens, batch, parallel):
+def _engine(folder, cfg_dict, *, page, pool_tokens, batch, parallel, pipeline=True):
     from kungfu_b200.engine.engine import Engine
     cfg, model = api.load_model(folder, dtype="float32", device="cpu")
     runner = api.make_runner(cfg, model, dtype="float32", device="cpu", page_size=page, max_tokens=pool_tokens,
                              max_requests=parallel, max_context=cfg_dict["max_position_embeddings"])
-    return Engine(runner=runner, batch=batch, parallel=parallel)
+    return Engine(runner=runner, batch=batch, parallel=parallel, pipeline=pipeline)
 
 
 def test_generate_matches_plain_greedy_and_survives_preemption(tmp_path, cpu_ops):
@@ -76,6 +76,53 @@ def test_generate_matches_plain_greedy_and_survives_preemption(tmp_path, cpu_ops
     assert tight.generate(short, Sampling(temperature=0.0), max_tokens=8) == want_short
     assert tight.scheduler.n_preemptions > 0
     assert tight.runner.cache.n_live == 0 and tight.runner.cache.free_pages() == [9, 9]
+
+
+def test_tokens_read_one_step_late_end_requests_where_they_should(tmp_path, cpu_ops):
+    """Greedy decode steps are launched before the step before them has been read.  A request that an end-of-sequence id
+    ends has then run one step too many: its output must still end with that id, with reason eos, the others go on to
+    their length, everything is given back, and the result equals the engine that reads every step at once."""
+    from kungfu_b200.sampling import Sampling
+    cfg_dict = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=4, dtype=torch.float32)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg_dict["vocab_size"], 50 + n) for n in (5, 17, 23)]
+    full = [plain_gemma2.greedy(cfg_dict, tensors, p, 12) for p in prompts]
+    eos = full[1][5]                                       # ends the second request at its sixth token at the latest
+    want, why = [], []
+    for seq in full:
+        cut = seq.index(eos) + 1 if eos in seq else len(seq)
+        want.append(seq[:cut])
+        why.append("eos" if eos in seq else "length")
+    assert "eos" in why and len(want[1]) <= 6
+    for pipeline in (True, False):
+        e = _engine(folder, cfg_dict, page=4, pool_tokens=256, batch=16, parallel=4, pipeline=pipeline)
+        ids = [e.add_request(p, Sampling(temperature=0.0), max_tokens=12, eos=[eos]) for p in prompts]
+        seen = {i: [] for i in ids}
+        ended = {}
+        late = 0
+        while not e.idle:
+            n_running = len(e.scheduler.running)
+            ev = e.step()
+            late += int(e._inflight is not None)
+            for rid, tok, reason in ev:
+                assert rid not in ended, "a token after the request's end"
+                seen[rid].append(tok)
+                if reason is not None:
+                    ended[rid] = reason
+        assert [seen[i] for i in ids] == want and [ended[i] for i in ids] == why
+        assert [e.requests[i].output for i in ids] == want and [e.finish_reason(i) for i in ids] == why
+        assert (late > 0) == pipeline
+        assert e.runner.cache.n_live == 0 and e.runner.cache.free_pages() == [64, 64]
+    # the last token of a request that ends by its length arrives with flush() at the latest
+    e = _engine(folder, cfg_dict, page=4, pool_tokens=256, batch=16, parallel=4)
+    rid = e.add_request(prompts[0], Sampling(temperature=0.0), max_tokens=3)
+    got = []
+    for _ in range(3):
+        got += [tok for _rid, tok, _r in e.step()]
+    assert e.scheduler.idle and not e.idle and len(got) == 2      # counted out, but its last token is still on its way
+    got += [tok for _rid, tok, _r in e.flush()]
+    assert got == full[0][:3] and e.idle and e.finish_reason(rid) == "length"
 
 
 def test_temperature_sampling_is_reproducible(tmp_path, cpu_ops):

@@ -164,6 +164,17 @@ def test_generate_through_the_entry_point(tmp_path, name):
         for i, tok in enumerate(out):
             row = logits[len(p) + i - 1]
             assert float(row.max() - row[tok]) <= 2 * 2e-2 * scale
+    # decode steps launched before the step before them was read (the ids stay on the device) against steps read at once,
+    # with an end-of-sequence id that ends one request early and enough steps for the replayed graphs to be in use
+    long = [pg.greedy(cfg, tensors, p, 20) for p in prompts]
+    eos = long[1][9]
+    cut = [seq[:seq.index(eos) + 1] if eos in seq else seq for seq in long]
+    for pipeline in (True, False):
+        e = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], batch=16, parallel=4, page_size=8,
+                   pipeline=pipeline)
+        assert e.generate(prompts, Sampling(temperature=0.0), max_tokens=20, eos=[eos]) == cut
+        assert [e.finish_reason(i) for i in range(len(prompts))] == ["eos" if eos in seq else "length" for seq in long]
+        assert e.runner.cache.n_live == 0 and e.idle
     # temperature sampling with a fixed seed is reproducible and differs between seeds
     s = Sampling(temperature=0.8, top_k=0, top_p=1.0)
     a = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], parallel=4, page_size=8).generate(prompts, s, max_tokens=12, seed=5)
