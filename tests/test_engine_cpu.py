@@ -125,6 +125,33 @@ def test_tokens_read_one_step_late_end_requests_where_they_should(tmp_path, cpu_
     assert got == full[0][:3] and e.idle and e.finish_reason(rid) == "length"
 
 
+def test_requests_that_arrive_or_are_cancelled_while_a_step_is_in_flight(tmp_path, cpu_ops):
+    """A request added while decode steps are in flight joins with a prompt portion beside the others' tokens (the
+    engine reads what is in flight first); one that is cancelled keeps the tokens it had; the others are not disturbed."""
+    from kungfu_b200.sampling import Sampling
+    cfg_dict = helpers.TINY_B
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=8, dtype=torch.float32)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg_dict["vocab_size"], 20 + n) for n in (9, 30, 14)]
+    want = [plain_gemma2.greedy(cfg_dict, tensors, p, 10) for p in prompts]
+    e = _engine(folder, cfg_dict, page=8, pool_tokens=512, batch=16, parallel=4)
+    a = e.add_request(prompts[0], Sampling(temperature=0.0), max_tokens=10)
+    b = e.add_request(prompts[1], Sampling(temperature=0.0), max_tokens=10)
+    for _ in range(6):
+        e.step()
+    assert e._inflight is not None
+    c = e.add_request(prompts[2], Sampling(temperature=0.0), max_tokens=10)      # joins while a step is in flight
+    e.step()
+    e.step()
+    e.cancel(b)
+    kept = list(e.requests[b].output)
+    assert e.finish_reason(b) == "cancelled" and 0 < len(kept) < 10 and kept == want[1][:len(kept)]
+    while not e.idle:
+        e.step()
+    assert e.requests[a].output == want[0] and e.requests[c].output == want[2] and e.requests[b].output == kept
+    assert e.runner.cache.n_live == 0
+
+
 def test_temperature_sampling_is_reproducible(tmp_path, cpu_ops):
     from kungfu_b200.sampling import Sampling
     cfg_dict = helpers.TINY_B
