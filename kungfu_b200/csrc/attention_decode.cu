@@ -700,8 +700,10 @@ int launch_decode_d(int ht, const void* q, const void* pages, const int* items, 
 
 // The tensor-core variant: ht = 0 selects it in kf_attention_decode.  It takes groups of up to 16 query heads.
 static int g_forced_splits = 0;
-// Measurement hook: a fixed number of splits for the tensor-core decode kernel (0 gives the planner's choice back).
+#ifdef KF_TUNING
+// Measurement hook of a tuning build: a fixed number of splits for the tensor-core decode kernel (0: the planner's choice).
 KF_API void kf_set_attention_decode_splits(int splits) { g_forced_splits = splits; }
+#endif
 
 KF_API int kf_attention_decode_mma_plan(int n_items, int nh, int nkv, int d, int max_keys, int* splits_out) {
   if (g_forced_splits > 0) { *splits_out = g_forced_splits; return KF_OK; }

@@ -614,8 +614,10 @@ KF_API int kf_attention_prefill_tc_supported(int d, int page_size, const void* q
 KF_API int kf_attention_prefill_tc_tile_rows() { return BMQ; }
 
 static int g_forced_parts = 0, g_forced_run_tiles = 0;
-// A fixed plan instead of the planner's (0, 0 gives its choice back): runs per tile and key tiles per run.
+#ifdef KF_TUNING
+// Measurement hook of a tuning build: a fixed plan instead of the planner's (0, 0 gives its choice back).
 KF_API void kf_set_attention_prefill_plan(int parts, int run_tiles) { g_forced_parts = parts, g_forced_run_tiles = run_tiles; }
+#endif
 
 // Into how many runs the keys of a tile are cut, and how long a run may be (0: every tile gets `parts` runs).
 // Few blocks (tiles x heads fill less than half of the GPU): every tile is cut so that the blocks fill it; at most 8

@@ -22,6 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libkungfu_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+if os.environ.get("KUNGFU_TUNING") == "1":          # a tuning build also exports the planners' measurement hooks
+    NVCC_FLAGS.append("-DKF_TUNING")
 
 
 class BuildError(RuntimeError):

@@ -35,19 +35,17 @@ struct Tile {
   static constexpr int B_BYTES = BN * BK * 2;
 };
 
-// XN: the activation rows come from a pending norm (NormIn) instead of the tm_x map; they are written once into a
-// shared-memory region of their own ([k block][BN][128 bytes], before the stage ring), so a stage holds weights only.
-template <int BN, int EPI, bool XN = false>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
                int stages, int cluster_reduce, float* __restrict__ partial, int* __restrict__ counters,
-               int* __restrict__ error_flag, const NormIn norm_in) {
+               int* __restrict__ error_flag) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int NACC = GATED ? 2 : 1;
   constexpr int COLS = Tile<BN>::COLS;
   constexpr int TMEM_COLS = COLS * NACC;
-  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + (XN ? 0 : Tile<BN>::B_BYTES);
+  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC + Tile<BN>::B_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
@@ -59,19 +57,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int nkb = kb_end - kb_begin;                              // >= 1 by the host's choice of splits
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem_x = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* smem = smem_x + (XN ? (size_t)kb_per * (BN * 128) : 0);    // the stage ring
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);    // the stage ring
   uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
   uint64_t* empty = full + stages;
   uint64_t* acc_full = empty + stages;
-  uint64_t* x_ready = acc_full + 1;
-  uint32_t* tmem_slot = (uint32_t*)(x_ready + 1);
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   int* s_flags = (int*)(tmem_slot + 1);                           // [0] abort, [1] arrival order of this CTA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
-    mbar_init(x_ready, 128);
     s_flags[0] = 0;
     s_flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -101,11 +96,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tma_load_2d(st, &tm_w, &full[i], k, f0);
         if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[i], k, up_offset + f0);
       }
-      if (!XN) {
-        kf_pdl_wait();                                             // activations come from the previous kernel
-        for (int i = 0; i < pre; ++i)
-          tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
-      }
+      kf_pdl_wait();                                               // activations come from the previous kernel
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
       for (int i = pre; i < nkb; ++i) {
         const int s = i % stages;
         if (!mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
@@ -118,7 +111,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int k = (kb_begin + i) * BK;
         tma_load_2d(st, &tm_w, &full[s], k, f0);
         if (GATED) tma_load_2d(st + Tile<BN>::A_BYTES, &tm_w, &full[s], k, up_offset + f0);
-        if (!XN) tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
+        tma_load_2d(st + Tile<BN>::A_BYTES * NACC, &tm_x, &full[s], k, t0);
       }
     }
   } else if (warp == 1) {
@@ -126,18 +119,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN);
       bool ok = true;
-      const uint64_t da0 = umma_desc(smem), db0 = XN ? umma_desc(smem_x) : umma_desc(smem + Tile<BN>::A_BYTES * NACC);
+      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + Tile<BN>::A_BYTES * NACC);
       const uint64_t du0 = umma_desc(smem + Tile<BN>::A_BYTES);
       int s = 0;
       uint32_t ph = 0;
-      if (XN) {
-        if (!mbar_wait(x_ready, 0)) {
-          atomicExch(error_flag, ERR_WAIT_FULL);
-          s_flags[0] = 1;
-          ok = false;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      }
       for (int i = 0; i < nkb && ok; ++i) {
         if (!mbar_wait(&full[s], ph)) {
           atomicExch(error_flag, ERR_WAIT_FULL);
@@ -146,8 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           break;
         }
         const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));   // descriptors hold address >> 4
-        const uint64_t da = da0 + so, du = du0 + so;
-        const uint64_t db = XN ? db0 + (uint64_t)((uint32_t)i * (uint32_t)((BN * 128) >> 4)) : db0 + so;
+        const uint64_t da = da0 + so, du = du0 + so, db = db0 + so;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {                                // 32 bytes per K = 16 step
           const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
@@ -163,12 +147,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ---- epilogue: warps 2..5, each owns the lane quarter (warp % 4) ---------------------------------------------
     kf_pdl_wait();                                                             // before any global write
     const int quarter = warp & 3;
-    if (XN) {
-      normed_rows_to_smem<BN>(norm_in, T, K, kb_begin, nkb, smem_x, blockIdx.x == 0 && blockIdx.y == 0, quarter, lane,
-                              reinterpret_cast<float*>(s_flags + 2));
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");             // generic writes -> the tensor core's reads
-      mbar_arrive(x_ready);
-    }
     const int f = f0 + quarter * 32 + lane;                                    // this thread's output feature
     const bool acc_ok = mbar_wait(acc_full, 0);
     if (!acc_ok && lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
@@ -205,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // Each CTA of the cluster (one per K split) parks its accumulator in its own shared memory (the pipeline
       // stages are free by now); after a cluster barrier CTA r sums, in split order, the tokens t with t % splits == r
       // straight out of its peers' shared memory and stores them.
-      float* red = reinterpret_cast<float*>(smem_x);                           // [NACC][BN][128]
+      float* red = reinterpret_cast<float*>(smem);                           // [NACC][BN][128]
       const int fl = quarter * 32 + lane;
       if (good) {
 #pragma unroll 1
@@ -515,7 +493,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 // Four warps per quarter of the lanes drain an accumulator (each takes a quarter of its columns): the epilogue of the
 // gated product cannot overlap the next tile (its two accumulators fill tensor memory), and the last epilogue of every
-// launch is exposed too.  With 4 epilogue warps a 2,048-token prompt took 11.3 ms, with 8 10.0 ms, with 16 9.5 ms.
+// launch is exposed too.
 constexpr int PAIR_THREADS = 576;
 
 template <int EPI>
@@ -731,7 +709,7 @@ namespace {
 int g_cluster_reduce = 1;
 int g_stage_cap_kb = 108;
 // Choice of token tile and split-K for a launch.
-int g_plan_bn = 0, g_plan_splits = 0;               // measurement hook: a fixed plan for products over more than 64 rows
+int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix the plan of products over more than 64 rows
 
 int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
   int bn = 16;
@@ -825,70 +803,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   cfg.attrs = attr;
   cfg.numAttrs = na;
   cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages,
-                     cluster ? 1 : 0, partial, counters, error_flag, NormIn{});
-  KF_CHECK_LAUNCH();
-  return KF_OK;
-}
-
-// The decode tile (16 tokens) with the activation rows taken from a pending norm.  K % 64 == 0, T <= 16.
-constexpr int NORMED_BN = 16;
-constexpr int NORMED_X_LIMIT = 64 * 1024;             // shared memory for the rows of one CTA's K range
-
-template <int EPI>
-int launch_normed(const CUtensorMap& tw, const NormIn& ni, void* out, int T, int N, int K, int ld_out, float softcap,
-                  int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
-  constexpr int BN = NORMED_BN;
-  constexpr int NACC = EPI == EPI_GATED ? 2 : 1;
-  constexpr int STAGE_BYTES = Tile<BN>::A_BYTES * NACC;
-  const int nkb = K / BK;
-  const int kb_per = (nkb + splits - 1) / splits;
-  const int x_bytes = kb_per * BN * 128;
-  if (x_bytes > NORMED_X_LIMIT) return KF_ERR_SIZE;
-  int stages = (SMEM_LIMIT - 2560 - x_bytes) / STAGE_BYTES;
-  if (g_stage_cap_kb > 0) {
-    const int cap = (g_stage_cap_kb * 1024) / STAGE_BYTES;
-    if (stages > cap) stages = cap;
-  }
-  if (stages > kb_per) stages = kb_per;
-  if (stages > 12) stages = 12;
-  if (stages < 1) return KF_ERR_SIZE;
-  const size_t smem = (size_t)stages * STAGE_BYTES + x_bytes + 1024 + 1024;
-  static bool configured = false;                      // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
-      kf_record_cuda_error(cudaGetLastError());
-      return KF_ERR_SETUP;
-    }
-    configured = true;
-  }
-  const int n_feat = EPI == EPI_GATED ? up_offset : N;
-  dim3 grid(kf_ceil_div(n_feat, BM), 1, splits);
-  const bool cluster = splits > 1 && splits <= 8 && g_cluster_reduce &&
-                       (size_t)NACC * BN * BM * 4 <= (size_t)stages * STAGE_BYTES + x_bytes;
-  if (splits > 1 && !cluster && (!partial || !counters)) return KF_ERR_SIZE;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  int na = 0;
-  if (kf_pdl_enabled()) {
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  if (cluster) {
-    attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = 1;
-    attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = splits;
-    ++na;
-  }
-  cfg.attrs = attr;
-  cfg.numAttrs = na;
-  cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, true>, tw, tw, out, T, N, K, ld_out, softcap, act, up_offset, stages,
-                     cluster ? 1 : 0, partial, counters, error_flag, ni);
+                     cluster ? 1 : 0, partial, counters, error_flag);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -989,16 +904,15 @@ int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
 
 }  // namespace
 
-// 1: split-K partial tiles are reduced through the cluster's shared memory; 0: through global memory and counters.
-KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; }
-
-// 1: products over many tokens run the persistent kernel; 0: one tile per CTA for every shape.
+#ifdef KF_TUNING
+// Measurement hooks, compiled only into a tuning build (-DKF_TUNING): they override the planner's choices.
+KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; }   // 0: split sums through global memory
 KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
-// Measurement hook: token tile and K splits for every product over more than 64 rows (0, 0: the planner decides).
-KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }
+KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
+#endif
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
 KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
@@ -1008,44 +922,6 @@ KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {
 // Choice of token tile and split-K for a launch; also used by the caller to size the partial buffer.
 KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
   return plan_linear(T, N_features, K, gated, bn_out, splits_out);
-}
-
-// Whether kf_linear_tc_normed takes this shape (with the split count kf_linear_tc_plan gives for it).
-KF_API int kf_linear_tc_normed_supported(int T, int N_features, int K, int gated) {
-  if (T < 1 || T > NORMED_BN || K < BK || K % BK != 0 || encode_fn() == nullptr) return 0;
-  int bn = 0, splits = 1;
-  kf_linear_tc_plan(T, N_features, K, gated, &bn, &splits);
-  const int nkb = K / BK;
-  const int kb_per = (nkb + splits - 1) / splits;
-  return kb_per * NORMED_BN * 128 <= NORMED_X_LIMIT ? 1 : 0;
-}
-
-// The product of kf_linear_tc over rows that a pending norm defines (see NormIn):
-//   y = res_in + rmsnorm(branch; w_post);  res_out = y;  x = rmsnorm(y; w_next) in bfloat16;  out = x . w^T (mode as below).
-// branch, res_in, res_out: [T, K] 32-bit, res_out distinct from res_in; w_post, w_next: [K] bfloat16.
-KF_API int kf_linear_tc_normed(const float* branch, const float* res_in, float* res_out, const void* w_post, float eps_post,
-                               int plus_post, const void* w_next, float eps_next, int plus_next, const void* w, void* out,
-                               int mode, int T, int N, int K, float softcap, int act, int splits, float* partial,
-                               int* counters, int* error_flag, cudaStream_t stream) {
-  if (T <= 0 || N <= 0) return KF_OK;
-  if (!kf_linear_tc_normed_supported(T, N, K, mode == EPI_GATED)) return KF_ERR_SIZE;
-  if (!branch || !res_in || !res_out || res_in == res_out || !w_post || !w_next) return KF_ERR_SIZE;
-  if (((uintptr_t)w & 15) || ((uintptr_t)branch & 15) || ((uintptr_t)res_in & 15) || ((uintptr_t)res_out & 15) ||
-      ((uintptr_t)w_post & 15) || ((uintptr_t)w_next & 15)) return KF_ERR_ALIGN;
-  const int w_rows = mode == EPI_GATED ? 2 * N : N;
-  CUtensorMap tw;
-  if (!tensor_map(w, w_rows, K, BM, &tw)) return KF_ERR_SETUP;
-  NormIn ni;
-  ni.branch = branch; ni.res_in = res_in; ni.res_out = res_out;
-  ni.w_post = (const __nv_bfloat16*)w_post; ni.w_next = (const __nv_bfloat16*)w_next;
-  ni.eps_post = eps_post; ni.eps_next = eps_next; ni.plus_post = plus_post; ni.plus_next = plus_next;
-  const int up_offset = mode == EPI_GATED ? N : 0;
-  switch (mode) {
-    case EPI_F32: return launch_normed<EPI_F32>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
-    case EPI_BF16: return launch_normed<EPI_BF16>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
-    case EPI_GATED: return launch_normed<EPI_GATED>(tw, ni, out, T, N, K, N, softcap, act, up_offset, splits, partial, counters, error_flag, stream);
-  }
-  return KF_ERR_SIZE;
 }
 
 // mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out, 2 = gated: w = [gate; up] stacked

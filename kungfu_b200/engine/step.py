@@ -332,21 +332,12 @@ class Runner:
         return b if b <= max(self.cache.max_requests, 1) * 2 else None
 
     def _forward(self, ctx):
-        """The model's pass over the step.  Steps of few rows queue their products, so that products that follow one
-        another run as one kernel (ops.chain_begin); the queue is emptied before this returns."""
-        from .. import ops
-        chain = (self.device.type == "cuda" and 0 < ctx.n_rows <= 16 and ctx.act_dtype == torch.bfloat16
-                 and not ops.tracing())
-        if chain:
-            ops.chain_begin()
-        try:
-            if self.device.type == "cuda":
-                with ops.pinned_stream():
-                    return self.model.forward(ctx)
-            return self.model.forward(ctx)
-        finally:
-            if chain:
-                ops.chain_end()
+        """The model's pass over the step, every launch on the stream that is current now."""
+        if self.device.type == "cuda":
+            from .. import ops
+            with ops.pinned_stream():
+                return self.model.forward(ctx)
+        return self.model.forward(ctx)
 
     def _step_graphed(self, entries, key, feedback=None):
         """First time a key is seen the step runs eagerly (that also sizes every buffer); the second time the

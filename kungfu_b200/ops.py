@@ -49,8 +49,6 @@ def library():
                 # kernels may start before their predecessor in the stream has finished (each waits for it before
                 # touching dependent memory); KUNGFU_PDL=0 switches that off
                 lib.kf_set_pdl(0 if os.environ.get("KUNGFU_PDL", "1") == "0" else 1)
-                if os.environ.get("KUNGFU_GEMM_STAGE_KB"):           # tuning knob: shared memory per weight-streaming CTA
-                    lib.kf_set_gemm_stage_cap_kb(int(os.environ["KUNGFU_GEMM_STAGE_KB"]))
                 _lib = lib
     return _lib
 
@@ -158,8 +156,6 @@ def _dispatch(name):
         def wrapper(*a, **k):
             if _override is not None:
                 return getattr(_override, name)(*a, **k)
-            if _chain and name not in _CHAINABLE:
-                flush()                                    # queued products run before anything that may read them
             if _trace is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -228,6 +224,7 @@ use_fast_attention = True    # likewise for the generic attention kernel
 prefill_on_tcgen05 = True       # False: the mma.sync prompt kernel for every head and page size
 split_prompt_keys = True        # False: one block per (tile of rows, head) however few blocks that makes
 decode_on_tensor_cores = True   # False: the SIMT split-KV decode kernel (kept for groups of more than 16 heads)
+prefill_plan_override = None    # (runs per tile, key tiles above which a tile is cut): tests reach every launch shape with it
 
 
 def _dev_scratch(device) -> dict:
@@ -236,8 +233,7 @@ def _dev_scratch(device) -> dict:
     if sc is None:
         sc = {"partial": torch.empty(1 << 20, dtype=torch.float32, device=device),
               "counters": torch.zeros(8192, dtype=torch.int32, device=device),
-              "error": torch.zeros(1, dtype=torch.int32, device=device),
-              "grid_barrier": torch.zeros(2, dtype=torch.int32, device=device), "retired": []}
+              "error": torch.zeros(1, dtype=torch.int32, device=device), "retired": []}
         _scratch[key] = sc
     return sc
 
@@ -292,156 +288,6 @@ def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> b
     return True
 
 
-# ---- chains of products over few rows --------------------------------------------------------------------------------
-# Between chain_begin() and chain_end(), `linear` and `linear_gated` over at most 16 bfloat16 rows are queued instead of
-# launched; any other operation of this module, flush() or chain_end() launches what is queued: one product as usual,
-# several as ONE persistent kernel that runs them as phases and keeps the weight stream going across them.
-_CHAINABLE = ("linear", "linear_gated")
-_chain: list | None = None
-_chain_on = False
-# Off by default (KUNGFU_CHAIN=1 switches it on): at Gemma 2 2B sizes only 16 clusters of 8 CTAs are resident at once
-# with the kernel's shared memory, so phases of 18 feature tiles x 8 splits need a second round, and the rows' sums of a
-# pending norm take about 20 us per phase; measured 5.8 ms per decode step against 2.75 ms with one kernel per product.
-chain_products = os.environ.get("KUNGFU_CHAIN", "0") == "1"
-
-
-class KfChainOp(ctypes.Structure):
-    _fields_ = [("w", ctypes.c_void_p), ("x", ctypes.c_void_p), ("out", ctypes.c_void_p), ("n_out", ctypes.c_int),
-                ("K", ctypes.c_int), ("mode", ctypes.c_int), ("act", ctypes.c_int), ("softcap", ctypes.c_float),
-                ("branch", ctypes.c_void_p), ("res_in", ctypes.c_void_p), ("res_out", ctypes.c_void_p),
-                ("w_post", ctypes.c_void_p), ("w_next", ctypes.c_void_p), ("eps_post", ctypes.c_float),
-                ("eps_next", ctypes.c_float), ("plus_post", ctypes.c_int), ("plus_next", ctypes.c_int)]
-
-
-def chain_begin() -> None:
-    """Start queueing products of few rows (the step function does this for steps of at most 16 rows)."""
-    global _chain, _chain_on
-    if _override is None and chain_products and use_tensor_cores:
-        _chain, _chain_on = [], True
-
-
-def chain_end() -> None:
-    global _chain, _chain_on
-    flush()
-    _chain, _chain_on = None, False
-
-
-def chaining() -> bool:
-    return _chain_on
-
-
-def _addr(t) -> int | None:
-    return None if t is None else t.data_ptr()
-
-
-def _chain_take(x, weight, out, mode: int, N: int, softcap: float, act: int) -> bool:
-    """Queue the product if a chain is open and the kernel takes its shape."""
-    if not _chain_on:
-        return False
-    pending = isinstance(x, PendingNorm)
-    rows = x.residual if pending else x
-    T, K = rows.shape
-    if (T > 16 or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.shape[1] != K
-            or (not pending and x.dtype != torch.bfloat16)):
-        return False
-    if not library().kf_linear_chain_supported(int(T), int(N), int(K)):
-        return False
-    if _chain and _chain[0][0] != T:
-        flush()
-    if len(_chain) >= library().kf_linear_chain_max_phases():
-        flush()
-    # the queue keeps the tensors alive until the launch
-    _chain.append((T, x, weight, out, mode, N, float(softcap), act))
-    return True
-
-
-def flush() -> None:
-    """Launch the queued products."""
-    global _chain
-    if not _chain:
-        return
-    queued, _chain = _chain, ([] if _chain_on else None)
-    lib = library()
-    if len(queued) == 1:
-        T, x, weight, out, mode, N, softcap, act = queued[0]
-        if isinstance(x, PendingNorm):
-            _linear_normed(x, weight, out, mode, N, softcap, act)
-        elif not _linear_tc(x, weight, out, mode, N, softcap, act):
-            raise KernelError("a queued product was refused by the tensor-core kernel")
-        return
-    ops_c = (KfChainOp * len(queued))()
-    T = queued[0][0]
-    for o, (_, x, weight, out, mode, N, softcap, act) in zip(ops_c, queued):
-        o.w, o.out, o.n_out, o.K, o.mode, o.act, o.softcap = weight.data_ptr(), out.data_ptr(), N, weight.shape[1], mode, act, softcap
-        if isinstance(x, PendingNorm):
-            if (x.branch.dtype != torch.float32 or x.residual.dtype != torch.float32 or x.post_weight.dtype != torch.bfloat16
-                    or x.next_weight.dtype != torch.bfloat16):
-                raise KernelError("product over a pending norm: 32-bit branch and residual and bfloat16 norm weights are required")
-            o.x = None
-            o.branch, o.res_in, o.res_out = x.branch.data_ptr(), x.residual.data_ptr(), x.residual_out.data_ptr()
-            o.w_post, o.w_next = x.post_weight.data_ptr(), x.next_weight.data_ptr()
-            o.eps_post, o.eps_next, o.plus_post, o.plus_next = x.post_eps, x.next_eps, int(x.post_plus_one), int(x.next_plus_one)
-        else:
-            o.x = x.data_ptr()
-    sc = _dev_scratch(queued[0][2].device)
-    _check(lib.kf_linear_chain(ops_c, len(queued), T, _p(sc["grid_barrier"]), _p(sc["error"]), _stream()), "chain of products")
-
-
-# True: a norm between two products of few rows is computed inside the second product's kernel (one launch fewer).  Off by
-# default: in the one-kernel-per-product path the rows' sums stall the weight stream longer than the norm's own kernel
-# takes (measured at Gemma 2 2B sizes, batch 8: 3.76 ms per step against 2.76 ms).  KUNGFU_FUSE_NORMS=1 switches it on.
-fuse_pending_norms = os.environ.get("KUNGFU_FUSE_NORMS", "0") == "1"
-
-
-class PendingNorm:
-    """Rows that are not computed yet: y = residual + rmsnorm(branch; post), rows = rmsnorm(y; then).
-    `linear` and `linear_gated` take one in place of their activation rows and compute the norm inside the product's
-    kernel; that kernel also writes y to `residual_out` (a buffer other than `residual`).  Only made for shapes that
-    `linear_fuses_norm` accepts."""
-    __slots__ = ("branch", "residual", "residual_out", "post_weight", "post_eps", "post_plus_one", "next_weight",
-                 "next_eps", "next_plus_one")
-
-    def __init__(self, branch, residual, residual_out, post_weight, post_eps, post_plus_one, next_weight, next_eps,
-                 next_plus_one):
-        self.branch, self.residual, self.residual_out = branch, residual, residual_out
-        self.post_weight, self.post_eps, self.post_plus_one = post_weight, float(post_eps), bool(post_plus_one)
-        self.next_weight, self.next_eps, self.next_plus_one = next_weight, float(next_eps), bool(next_plus_one)
-
-    @property
-    def shape(self):
-        return self.residual.shape
-
-
-def linear_fuses_norm(T: int, weight, gated: bool, act_dtype) -> bool:
-    """Whether a product of T rows with `weight` can take a PendingNorm (few rows, bfloat16, on the tensor cores)."""
-    if _override is not None or not use_tensor_cores or not (fuse_pending_norms or _chain_on):
-        return False
-    if weight.dtype != torch.bfloat16 or act_dtype != torch.bfloat16 or not weight.is_cuda:
-        return False
-    N = weight.shape[0] // 2 if gated else weight.shape[0]
-    return bool(library().kf_linear_tc_normed_supported(int(T), int(N), int(weight.shape[1]), int(gated)))
-
-
-def _linear_normed(p: PendingNorm, weight, out, mode: int, N: int, softcap: float, act: int) -> None:
-    T, K = p.residual.shape
-    lib = library()
-    if (p.branch.dtype != torch.float32 or p.residual.dtype != torch.float32 or p.post_weight.dtype != torch.bfloat16
-            or p.next_weight.dtype != torch.bfloat16 or weight.shape[1] != K):
-        raise KernelError("linear over a pending norm: 32-bit branch and residual and bfloat16 norm weights are required")
-    bn, splits = ctypes.c_int(0), ctypes.c_int(0)
-    lib.kf_linear_tc_plan(T, N, K, int(mode == 2), ctypes.byref(bn), ctypes.byref(splits))
-    sc = _dev_scratch(weight.device)
-    partial = None
-    if splits.value > 1:
-        if -(-N // 128) > sc["counters"].numel():
-            raise KernelError("linear over a pending norm: too many output tiles for the split counters")
-        partial = _partial(weight.device, splits.value * T * (2 * N if mode == 2 else N))
-    _check(lib.kf_linear_tc_normed(_p(p.branch), _p(p.residual), _p(p.residual_out), _p(p.post_weight), _f(p.post_eps),
-                                   int(p.post_plus_one), _p(p.next_weight), _f(p.next_eps), int(p.next_plus_one),
-                                   _p(weight), _p(out), mode, T, N, K, _f(softcap), act, splits.value, _p(partial),
-                                   _p(sc["counters"]), _p(sc["error"]), _stream()), "linear over a pending norm")
-
-
 @_dispatch("linear")
 def linear(x, weight, out, softcap: float = 0.0) -> None:
     """out[T, N] = x[T, K] . weight[N, K]^T, 32-bit accumulation; softcap > 0 applies cap*tanh(v/cap).
@@ -451,15 +297,6 @@ def linear(x, weight, out, softcap: float = 0.0) -> None:
     N = weight.shape[0]
     if weight.shape[1] != K or tuple(out.shape) != (T, N):
         raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
-    if out.dtype in (torch.float32, torch.bfloat16) and (out.dtype == torch.float32 or softcap == 0.0):
-        if _chain_take(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0):
-            return
-    flush()
-    if isinstance(x, PendingNorm):
-        if out.dtype != torch.float32 and softcap != 0.0:
-            raise KernelError("linear over a pending norm: a softcap needs a 32-bit output")
-        _linear_normed(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0)
-        return
     if out.dtype == torch.float32 or softcap == 0.0:
         if _linear_tc(x, weight, out, 0 if out.dtype == torch.float32 else 1, N, softcap, 0):
             return
@@ -472,14 +309,6 @@ def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
     """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows."""
     T = x.shape[0]
     I = out.shape[1]
-    if out.dtype == torch.bfloat16 and w_gate_up.shape[0] == 2 * I and _chain_take(x, w_gate_up, out, 2, I, 0.0, _ACT[activation]):
-        return
-    flush()
-    if isinstance(x, PendingNorm):
-        if out.dtype != torch.bfloat16:
-            raise KernelError("gated product over a pending norm: the output must be bfloat16")
-        _linear_normed(x, w_gate_up, out, 2, I, 0.0, _ACT[activation])
-        return
     if out.dtype == torch.bfloat16 and _linear_tc(x, w_gate_up, out, 2, I, 0.0, _ACT[activation]):
         return
     gu = ctx.buf("ffn_gate_up", (T, 2 * I), torch.float32)
@@ -550,7 +379,10 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         sc = _dev_scratch(q.device)
         max_keys = min(ctx.max_kv_len, window + 128) if window else ctx.max_kv_len
         run_tiles = ctypes.c_int(0)
-        parts = lib.kf_attention_prefill_tc_plan(ctx.n_wide, n_heads, int(max_keys), ctypes.byref(run_tiles)) if split_prompt_keys else 1
+        if prefill_plan_override is not None:
+            parts, run_tiles = int(prefill_plan_override[0]), ctypes.c_int(int(prefill_plan_override[1]))
+        else:
+            parts = lib.kf_attention_prefill_tc_plan(ctx.n_wide, n_heads, int(max_keys), ctypes.byref(run_tiles)) if split_prompt_keys else 1
         partial = _partial(q.device, T * n_heads * parts * (head_dim + 4)) if parts > 1 else None
         _check(lib.kf_attention_prefill_tc(_p(q), _p(out), _p(pages), ctypes.c_long(pages.shape[0]), T, _p(ctx.wide_row0),
                                            _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), parts, run_tiles.value,

@@ -36,9 +36,6 @@ class PagedAttention(Mixer):
     def state_need(self):
         return PagedKV(self.n_kv_heads, self.head_dim, self.window)
 
-    def takes_pending_norm(self, n_rows, ctx):
-        return ops.linear_fuses_norm(n_rows, self.wqkv, False, ctx.act_dtype)
-
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         nh, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim

@@ -97,11 +97,6 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
-    def takes_pending_norm(self, n_rows: int, ctx) -> bool:
-        """True if forward() may be given an ops.PendingNorm in place of x for this many rows: the part then hands
-        it to its first ops.linear, whose kernel computes the norm itself."""
-        return False
-
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """x: normalised input [rows, width] in the step's activation dtype; returns 32-bit [rows, width].
         `cache` is the view of this call's cache slot (`PagedKVView` or `FixedStateView`) or None."""
@@ -109,10 +104,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    def takes_pending_norm(self, n_rows: int, ctx) -> bool:
-        """As Mixer.takes_pending_norm, for the feed-forward's first product."""
-        return False
-
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         """x: normalised input [rows, width] in the activation dtype; returns 32-bit [rows, width]."""
         raise NotImplementedError
@@ -122,9 +113,8 @@ class Block(Part):
     """An arrangement of norms, one mixer and one feed-forward around the residual stream."""
 
     mixer: Mixer
-    # A block that sets this takes forward(x, ctx, cache, normed=None, then=None, then_consumer=None) and returns
-    # (x, normed_for_next): `normed` is its own first norm computed by the block before it (rows, or an
-    # ops.PendingNorm if its mixer takes one), `then` the next block's first norm and `then_consumer` that block's mixer.
+    # A block that sets this takes forward(x, ctx, cache, normed=None, then=None) and returns (x, normed_for_next):
+    # `normed` is its own first norm computed by the block before it, `then` the next block's first norm.
     fuses_next_norm = False
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:

@@ -23,31 +23,19 @@ class SandwichBlock(Block):
         self.pre_mixer, self.mixer, self.post_mixer = pre_mixer, mixer, post_mixer
         self.pre_ffn, self.ffn, self.post_ffn = pre_ffn, ffn, post_ffn
 
-    @staticmethod
-    def _add_into(post: Norm, branch, x, ctx, then, out_dtype, consumer):
-        """(rows for the consumer, residual).  A norm that can defer its work may hand the consumer a pending norm; the
-        residual is then the buffer that the consumer's kernel writes."""
-        if consumer is not None and getattr(post, "can_defer", False):
-            n = post.add_into(branch, x, ctx, then=then, out_dtype=out_dtype, consumer=consumer)
-            if isinstance(n, ops.PendingNorm):
-                return n, n.residual_out
-            return n, x
-        return post.add_into(branch, x, ctx, then=then, out_dtype=out_dtype), x
-
-    def forward(self, x, ctx, cache, normed=None, then=None, then_consumer=None):
+    def forward(self, x, ctx, cache, normed=None, then=None):
         act = ctx.act_dtype
         n = normed if normed is not None else self.pre_mixer.forward(x, ctx, act)
         a = self.mixer.forward(n, ctx, cache)
         if self.post_mixer is not None:
-            n, x = self._add_into(self.post_mixer, a, x, ctx, self.pre_ffn, act, self.ffn)
+            n = self.post_mixer.add_into(a, x, ctx, then=self.pre_ffn, out_dtype=act)
         else:
             ops.add(a, x)
             n = self.pre_ffn.forward(x, ctx, act)
         f = self.ffn.forward(n, ctx)
         nxt = None
         if self.post_ffn is not None:
-            nxt, x = self._add_into(self.post_ffn, f, x, ctx, then, act if then is not None else None,
-                                    then_consumer if then is not None else None)
+            nxt = self.post_ffn.add_into(f, x, ctx, then=then, out_dtype=act if then is not None else None)
         else:
             ops.add(f, x)
             if then is not None:

@@ -28,9 +28,6 @@ class GatedFfn(FeedForward):
         self.inner = w_down.shape[1]
         self.width = w_down.shape[0]
 
-    def takes_pending_norm(self, n_rows, ctx):
-        return ops.linear_fuses_norm(n_rows, self.w_gate_up, True, ctx.act_dtype)
-
     def forward(self, x, ctx):
         T = x.shape[0]
         h = ctx.buf("ffn_h", (T, self.inner), ctx.act_dtype)

@@ -66,8 +66,7 @@ class DecoderModel(Part):
                 # the last kernel of this block also computes the next block's first norm, when both can
                 nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
                 then = nxt.pre_mixer if nxt is not None and getattr(nxt, "fuses_next_norm", False) else None
-                x, normed = block.forward(x, ctx, view, normed=normed, then=then,
-                                          then_consumer=nxt.mixer if then is not None else None)
+                x, normed = block.forward(x, ctx, view, normed=normed, then=then)
             else:
                 x, normed = block.forward(x, ctx, view), None
         if ctx.n_logits == 0:

@@ -26,20 +26,8 @@ class RmsNorm(Norm):
         ops.rmsnorm(x, self.weight, self.eps, self.plus_one, out, rows)
         return out
 
-    can_defer = True          # add_into(..., consumer=part) may return an ops.PendingNorm instead of computed rows
-
-    def add_into(self, branch, residual, ctx, then=None, out_dtype=None, consumer=None):
-        """residual += norm(branch); returns then(residual) if `then` is given.  With a `consumer` (the part that reads
-        the returned rows first, through ops.linear or ops.linear_gated) that takes pending norms for this many rows, nothing
-        runs here: the returned PendingNorm is computed inside the consumer's first product, and the new residual lives
-        in its `residual_out`."""
-        if (consumer is not None and isinstance(then, RmsNorm) and branch.dtype == torch.float32
-                and consumer.takes_pending_norm(residual.shape[0], ctx)):
-            out = ctx.buf("residual_even", tuple(residual.shape), torch.float32)
-            if out.data_ptr() == residual.data_ptr():
-                out = ctx.buf("residual_odd", tuple(residual.shape), torch.float32)
-            return ops.PendingNorm(branch, residual, out, self.weight, self.eps, self.plus_one,
-                                   then.weight, then.eps, then.plus_one)
+    def add_into(self, branch, residual, ctx, then=None, out_dtype=None):
+        """residual += norm(branch); returns then(residual) if `then` is given (one kernel when `then` is an RmsNorm)."""
         if then is None:
             ops.add_rmsnorm(branch, self.weight, self.eps, self.plus_one, residual)
             return None

@@ -96,21 +96,6 @@ def test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, dtype):
     ops.raise_on_device_error()
 
 
-@pytest.mark.parametrize("mode", ["tail", "mixed"])
-@pytest.mark.parametrize("chain", [False, True])
-def test_norms_computed_inside_the_next_product_match_plain(tmp_path_factory, mode, chain):
-    """The same configuration with the switch on that lets a product of few rows compute the norm before it in its own
-    kernel (decode steps then run two kernels fewer per layer, and the residual alternates between two buffers); and
-    with the switch that runs the products of such a step as phases of one persistent kernel."""
-    from kungfu_b200 import ops
-    was = ops.fuse_pending_norms, ops.chain_products
-    ops.fuse_pending_norms, ops.chain_products = True, chain
-    try:
-        test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, "bfloat16")
-    finally:
-        ops.fuse_pending_norms, ops.chain_products = was
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_stored_in_32_bit_stay_so(tmp_path, dtype):
     """A file whose tensors are 32-bit floats: the bfloat16 engine keeps them 32-bit (and multiplies them with the

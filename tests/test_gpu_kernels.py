@@ -146,137 +146,6 @@ def test_linear_gated_tensor_cores(ops, T, I, K, act):
     assert rel_err(out, ref) < 6e-3
 
 
-@pytest.mark.parametrize("T,N,K,gated", [(1, 256, 64, False), (8, 4096, 2304, False), (5, 130, 192, False), (16, 1000, 512, False),
-                                         (8, 9216, 2304, True), (3, 200, 128, True), (16, 320, 1024, True), (7, 136, 4608, False)])
-@pytest.mark.parametrize("plus_one", [True, False])
-def test_linear_over_pending_norm(ops, T, N, K, gated, plus_one):
-    """The product whose activation rows are a norm not yet run: y = x + rmsnorm(a; w1), rows = rmsnorm(y; w2), computed
-    inside the tcgen05 kernel; the kernel also leaves y in a second buffer.  Against float64, with and without split-K."""
-    from cpu_ops import _act
-    g = torch.Generator().manual_seed(T * 13 + N + K)
-    a = (torch.randn(T, K, generator=g) * 3.0).to(DEV)
-    x = torch.randn(T, K, generator=g).to(DEV)
-    x[:, 5] *= 40.0                                            # one large residual element: the sums must be 32-bit
-    w1 = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
-    w2 = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
-    eps1, eps2 = 1e-6, 3e-5
-    rows_w = 2 * N if gated else N
-    w = (torch.randn(rows_w, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    was, ops.fuse_pending_norms = ops.fuse_pending_norms, True
-    try:
-        assert ops.linear_fuses_norm(T, w, gated, torch.bfloat16)
-    finally:
-        ops.fuse_pending_norms = was
-    p1 = 1.0 if plus_one else 0.0
-
-    def rms(v, wt, eps):
-        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * (wt.double() + p1)
-
-    y = x.double() + rms(a.double(), w1, eps1)
-    rows = rms(y, w2, eps2).to(torch.bfloat16).double()          # the kernel rounds the rows to bfloat16 too
-    full = rows @ w.double().T
-    ref = _act("gelu_tanh", full[:, :N]) * full[:, N:] if gated else full
-    y_out = torch.full((T, K), float("nan"), device=DEV)
-    pend = ops.PendingNorm(a, x, y_out, w1, eps1, plus_one, w2, eps2, plus_one)
-    out = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
-    x_before = x.clone()
-    if gated:
-        ops.linear_gated(pend, w, out, "gelu_tanh", None)
-    else:
-        ops.linear(pend, w, out)
-    ops.raise_on_device_error()
-    assert torch.equal(x, x_before), "the old residual is left as it was"
-    assert rel_err(y_out, y) < 1e-6
-    # a row element that sits near a bfloat16 rounding boundary may round the other way than in the reference
-    assert rel_err(out, ref) < (6e-3 if gated else 2e-3)
-    again = torch.empty_like(out)
-    y2 = torch.empty_like(y_out)
-    pend2 = ops.PendingNorm(a, x, y2, w1, eps1, plus_one, w2, eps2, plus_one)
-    (ops.linear_gated(pend2, w, again, "gelu_tanh", None) if gated else ops.linear(pend2, w, again))
-    assert torch.equal(out, again) and torch.equal(y_out, y2)
-    # and it agrees with the unfused kernels run one after the other
-    xs = x.clone()
-    rows_dev = torch.empty(T, K, dtype=torch.bfloat16, device=DEV)
-    ops.add_rmsnorm(a, w1, eps1, plus_one, xs, next_weight=w2, next_eps=eps2, next_plus_one=plus_one, next_out=rows_dev)
-    sep = torch.empty_like(out)
-    (ops.linear_gated(rows_dev, w, sep, "gelu_tanh", None) if gated else ops.linear(rows_dev, w, sep))
-    assert rel_err(y_out, xs) < 1e-6
-    assert rel_err(out, sep) < (6e-3 if gated else 2e-3)
-
-
-@pytest.mark.parametrize("T,H,Q,I", [(8, 2304, 2048, 9216), (1, 128, 64, 320), (5, 512, 768, 1536), (16, 192, 320, 200), (3, 1024, 64, 4608)])
-def test_chain_of_products(ops, T, H, Q, I):
-    """Products queued between chain_begin and chain_end run as ONE persistent kernel: output projection, gated pair over
-    a pending norm, down projection, and the next projection over a second pending norm, as a decode layer strings them.
-    Against float64 and against the same products launched one by one; twice for the same bits."""
-    from cpu_ops import _act
-    g = torch.Generator().manual_seed(T + H + I)
-    bf = torch.bfloat16
-    attn = torch.randn(T, Q, generator=g).to(bf).to(DEV)
-    resid = torch.randn(T, H, generator=g).to(DEV)
-    wo = (torch.randn(H, Q, generator=g) * 0.05).to(bf).to(DEV)
-    wgu = (torch.randn(2 * I, H, generator=g) * 0.05).to(bf).to(DEV)
-    wd = (torch.randn(H, I, generator=g) * 0.05).to(bf).to(DEV)
-    wq = (torch.randn(Q + 128, H, generator=g) * 0.05).to(bf).to(DEV)
-    norms = [(torch.randn(H, generator=g) * 0.3).to(bf).to(DEV) for _ in range(4)]
-    eps = 1e-6
-
-    def run(chained):
-        a = torch.full((T, H), float("nan"), device=DEV)
-        h = torch.full((T, I), float("nan"), device=DEV, dtype=bf)
-        f = torch.full((T, H), float("nan"), device=DEV)
-        q = torch.full((T, Q + 128), float("nan"), device=DEV)
-        r1 = torch.full((T, H), float("nan"), device=DEV)
-        r2 = torch.full((T, H), float("nan"), device=DEV)
-        was, was_chain = ops.fuse_pending_norms, ops.chain_products
-        ops.fuse_pending_norms = True
-        if chained:
-            ops.chain_products = True
-            ops.chain_begin()
-            assert ops.chaining()
-        try:
-            ops.linear(attn, wo, a)
-            ops.linear_gated(ops.PendingNorm(a, resid, r1, norms[0], eps, True, norms[1], eps, True), wgu, h, "gelu_tanh", None)
-            ops.linear(h, wd, f)
-            ops.linear(ops.PendingNorm(f, r1, r2, norms[2], eps, True, norms[3], eps, True), wq, q)
-        finally:
-            if chained:
-                ops.chain_end()
-            ops.fuse_pending_norms, ops.chain_products = was, was_chain
-        ops.raise_on_device_error()
-        return a, h, f, q, r1, r2
-
-    def rms(v, wt):
-        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * (wt.double() + 1.0)
-
-    before = ops.launch_count()
-    got = run(True)
-    if I % 64 == 0:
-        assert ops.launch_count() - before == 1, "four products, one launch"
-    else:                                                      # a product the chain kernel refuses runs on its own
-        assert ops.launch_count() - before > 1
-    a, h, f, q, r1, r2 = got
-    a_ref = attn.double() @ wo.double().T
-    assert rel_err(a, a_ref) < 2e-6 * math.sqrt(Q) + 1e-6
-    # later stages are checked against their own inputs as the kernel produced them (rounding does not pile up)
-    y1 = resid.double() + rms(a.double(), norms[0])
-    assert rel_err(r1, y1) < 1e-6
-    n1 = rms(y1, norms[1]).to(bf).double()
-    gu = n1 @ wgu.double().T
-    assert rel_err(h, _act("gelu_tanh", gu[:, :I]) * gu[:, I:]) < 6e-3
-    assert rel_err(f, h.double() @ wd.double().T) < 2e-6 * math.sqrt(I) + 1e-6
-    y2 = r1.double() + rms(f.double(), norms[2])
-    assert rel_err(r2, y2) < 1e-6
-    assert rel_err(q, rms(y2, norms[3]).to(bf).double() @ wq.double().T) < 2e-3
-    again = run(True)
-    for x1, x2 in zip(got, again):
-        assert torch.equal(x1, x2)
-    # one by one: the same up to the bfloat16 roundings of h, which fall differently where the split sums differ in order
-    single = run(False)
-    for x1, x2, tol in zip(got, single, (1e-5, 8e-3, 2e-3, 3e-3, 1e-5, 2e-3)):
-        assert rel_err(x1, x2) < tol
-
-
 @pytest.mark.parametrize("act", ["gelu_tanh", "gelu_erf", "silu"])
 def test_linear_gated(ops, act):
     from cpu_ops import _act
@@ -480,14 +349,14 @@ def test_prompt_attention_with_only_the_long_tiles_cut(ops, nh, nkv, d, window, 
     outs = []
     key_tiles = (min(max(lens), window + 128 if window else max(lens)) + 63) // 64
     for split in (True, False):
-        ops.library().kf_set_attention_prefill_plan(2 if split else 1, (key_tiles + 1) // 2 if split else 0)
+        ops.prefill_plan_override = (2 if split else 1, (key_tiles + 1) // 2 if split else 0)
         try:
             out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
             before = ops.launch_count()
             ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, 50.0, window)
             outs.append((out, ops.launch_count() - before))
         finally:
-            ops.library().kf_set_attention_prefill_plan(0, 0)
+            ops.prefill_plan_override = None
     ops.raise_on_device_error()
     assert outs[0][1] == 2 and outs[1][1] == 1, "long tiles cut into runs: the attention kernel and the merge"
     assert not torch.isnan(outs[0][0].float()).any()
