@@ -70,17 +70,29 @@ def random_model(config, seed: int = 0, *, dtype="bfloat16", device="cuda:0", on
 
 def make_runner(cfg, model, *, dtype, device, page_size: int = DEFAULT_PAGE_SIZE, max_tokens: int | None = None,
                 n_pages: int | None = None, max_requests: int = 64, max_context: int | None = None,
-                cuda_graphs: bool = True) -> Runner:
-    """A step runner with a cache pool for `max_tokens` tokens (rounded up to whole pages) per cache group."""
+                cuda_graphs: bool = True, batch: int | None = None, budget_bytes: int | None = None) -> Runner:
+    """A step runner with its cache.  Every group's pool holds `max_tokens` tokens (rounded up to whole pages; default
+    `max_requests * max_context`), except that a windowed group never gets more than its requests can hold when
+    `batch` (the most tokens one step feeds of one request) is given: `max_requests * (window + batch + page)`.
+    `budget_bytes`: the memory the cache may take; pools are cut to fit it (`cache.plan.NoFit` if one request of
+    `max_context` tokens does not fit).  `n_pages` sets every pool to that many pages and skips the sizing."""
+    from .cache.plan import plan_cache
     dtype = parse_dtype(dtype)
     if max_context is None:
         max_context = getattr(cfg, "max_position_embeddings", 8192)
+    needs = model.state_needs()
+    plan = None
     if n_pages is None:
-        if max_tokens is None:
-            max_tokens = max_context
-        n_pages = -(-int(max_tokens) // page_size)
-    cache = CacheManager(model.state_needs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
+        elsize = torch.empty(0, dtype=dtype).element_size()
+        plan = plan_cache(needs, page_size=page_size, parallel=max_requests, ctx=max_context,
+                          batch=batch if batch is not None else max_context, element_size=elsize,
+                          budget_bytes=budget_bytes, pool_tokens=max_tokens)
+        pages = plan.pages_by_window()
+    else:
+        pages = int(n_pages)
+    cache = CacheManager(needs, page_size=page_size, n_pages=pages, max_requests=max_requests,
                          max_context=max_context, dtype=dtype, device=device)
+    cache.plan = plan
     runner = Runner(model, cache, act_dtype=dtype, device=device)
     runner.cuda_graphs = bool(cuda_graphs) and torch.device(device).type == "cuda"
     return runner

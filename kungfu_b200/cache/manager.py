@@ -27,7 +27,7 @@ import ctypes
 import numpy as np
 import torch
 
-from ..parts.base import FixedState, PagedKV
+from .kinds import FixedStateView, PagedKVView, kind_of       # the views are re-exported from here
 
 _OK, _E_NOT_LIVE, _E_ALREADY_LIVE, _E_NO_SLOT, _E_OUT_OF_PAGES, _E_CONTEXT, _E_COMMIT, _E_PAGE, _E_INCONSISTENT = range(9)
 
@@ -155,56 +155,48 @@ class _Group:
         self.tables = _GroupTables(manager, g)
 
 
-class PagedKVView:
-    """What a mixer sees of its cache slot during one step."""
-
-    def __init__(self, pages: torch.Tensor, page_size: int, group: int, writes: bool):
-        self.pages = pages              # [n_pages, 2 (key, value), n_kv_heads, page_size, head_dim]
-        self.page_size = page_size
-        self.group = group
-        self.writes = writes
-
-
-class FixedStateView:
-    def __init__(self, state: torch.Tensor, writes: bool):
-        self.state = state              # [max_requests, *shape]; row = the request's state slot
-        self.writes = writes
-
-
 class CacheManager:
-    def __init__(self, needs: list, *, page_size: int, n_pages: int, max_requests: int, max_context: int,
+    def __init__(self, needs: list, *, page_size: int, n_pages: int | dict, max_requests: int, max_context: int,
                  dtype: torch.dtype, device, n_pages_windowed: int | None = None):
-        """`needs[s]` is the `StateNeed` of cache slot s (or None).  `n_pages` is the size of each group's
-        pool (`n_pages_windowed` for groups with a window, when given)."""
+        """`needs[s]` is the `StateNeed` of cache slot s (or None); what the manager must know about it comes from the
+        state kind registered for its class (`cache/kinds.py`).  `n_pages` is the size of each group's pool, or a
+        dictionary {window or None: pages} as `plan_cache` gives it (`n_pages_windowed`: the size for groups with a
+        window when `n_pages` is one number)."""
         self.page_size = int(page_size)
         self.max_requests = int(max_requests)
         self.max_context = int(max_context)
         self.max_pages_per_request = -(-self.max_context // self.page_size)
         self.dtype, self.device = dtype, torch.device(device)
         self.needs = list(needs)
+        self._kinds = [None if n is None else kind_of(n) for n in self.needs]
         self._lib = host_library()
         self.groups: list[_Group] = []
         self._group_of_slot: dict[int, int] = {}
         self.storage: dict[int, torch.Tensor] = {}
         by_window: dict = {}
         pool_sizes: list[int] = []
-        for s, need in enumerate(self.needs):
-            if isinstance(need, PagedKV):
-                g = by_window.get(need.window)
+        for s, (need, kind) in enumerate(zip(self.needs, self._kinds)):
+            if need is None:
+                continue
+            if kind.paged:
+                window = kind.window(need)
+                g = by_window.get(window)
                 if g is None:
-                    n = n_pages_windowed if (need.window is not None and n_pages_windowed is not None) else n_pages
+                    if isinstance(n_pages, dict):
+                        n = n_pages[window]
+                    else:
+                        n = n_pages_windowed if (window is not None and n_pages_windowed is not None) else n_pages
                     g = len(self.groups)
-                    by_window[need.window] = g
-                    self.groups.append(_Group(self, g, need.window, int(n)))
+                    by_window[window] = g
+                    self.groups.append(_Group(self, g, window, int(n)))
                     pool_sizes.append(int(n))
                 self.groups[g].slots.append(s)
                 self._group_of_slot[s] = g
-                self.storage[s] = torch.zeros((pool_sizes[g], 2, need.n_kv_heads, self.page_size, need.head_dim),
-                                              dtype=dtype, device=self.device)
-            elif isinstance(need, FixedState):
-                self.storage[s] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=self.device)
-            elif need is not None:
-                raise TypeError(f"cache slot {s}: unknown state need {need!r}")
+                self.storage[s] = torch.zeros((pool_sizes[g], *kind.page_shape(need, self.page_size)),
+                                              dtype=kind.dtype(need, dtype), device=self.device)
+            else:
+                self.storage[s] = torch.zeros((self.max_requests, *kind.shape(need)), dtype=kind.dtype(need, dtype),
+                                              device=self.device)
         G = len(self.groups)
         windows = (ctypes.c_int * max(G, 1))(*[(-1 if g.window is None else int(g.window)) for g in self.groups])
         sizes = (ctypes.c_int * max(G, 1))(*pool_sizes)
@@ -255,9 +247,7 @@ class CacheManager:
             raise CacheError(f"request {request!r}: native manager refused admission (code {-slot})")
         self._next_key += 1
         self._key[request] = key
-        for s, need in enumerate(self.needs):
-            if isinstance(need, FixedState):
-                self.storage[s][slot].zero_()
+        self._zero_fixed(slot)
         return slot
 
     def new_key(self) -> int:
@@ -272,8 +262,11 @@ class CacheManager:
         if request in self._key:
             raise CacheError(f"request {request!r} is already live")
         self._key[request] = int(key)
-        for s, need in enumerate(self.needs):
-            if isinstance(need, FixedState):
+        self._zero_fixed(slot)
+
+    def _zero_fixed(self, slot: int) -> None:
+        for s, kind in enumerate(self._kinds):
+            if kind is not None and not kind.paged:
                 self.storage[s][slot].zero_()
 
     def forget(self, request) -> None:
@@ -334,23 +327,27 @@ class CacheManager:
         return self._group_of_slot.get(cache_slot)
 
     def view(self, cache_slot: int, writes: bool):
-        need = self.needs[cache_slot]
-        if isinstance(need, PagedKV):
-            return PagedKVView(self.storage[cache_slot], self.page_size, self._group_of_slot[cache_slot], writes)
-        if isinstance(need, FixedState):
-            return FixedStateView(self.storage[cache_slot], writes)
-        return None
+        need, kind = self.needs[cache_slot], self._kinds[cache_slot]
+        if kind is None:
+            return None
+        if kind.paged:
+            return kind.view(self.storage[cache_slot], self.page_size, self._group_of_slot[cache_slot], writes, need)
+        return kind.view(self.storage[cache_slot], writes, need)
 
     # ---- accounting and self-check -----------------------------------------------------------------------
     def free_pages(self) -> list[int]:
         return [g.pool.n_free for g in self.groups]
 
     def bytes_per_token(self) -> int:
+        """Bytes one token adds over all paged cache slots (windowed slots included, as long as it is in reach)."""
         n = 0
-        for s, need in enumerate(self.needs):
-            if isinstance(need, PagedKV):
-                n += 2 * need.n_kv_heads * need.head_dim * self.storage[s].element_size()
+        for s, (need, kind) in enumerate(zip(self.needs, self._kinds)):
+            if kind is not None and kind.paged:
+                n += kind.page_bytes(need, self.page_size, self.storage[s].element_size()) // self.page_size
         return n
+
+    def storage_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.storage.values())
 
     def check(self) -> None:
         """Every page is either free or in exactly one table; raises CacheError otherwise."""

@@ -136,7 +136,7 @@ def cmd_describe(args) -> int:
            "backends": [{"name": "cuda", "arch": "sm_100a", "devices": devices}],
            "parts": {k: base.known(k) for k in ("mixer", "feed_forward", "norm", "position", "block")},
            "params": [{"name": n, "type": t, "default": d, "flag": f, "description": desc} for n, t, d, f, desc in PARAMS],
-           "events": ["ready", "request"], "finish_reasons": ["eos", "length", "context", "cancelled", "no_fit"],
+           "events": ["plan", "alloc", "ready", "request", "error"], "finish_reasons": ["eos", "length", "context", "cancelled", "no_fit"],
            "errors": ["config", "unknown_arch", "weights", "model_open"],
            "kernel_library": ops.library_path()}
     print(json.dumps(doc, indent=2))

@@ -714,7 +714,7 @@ KF_API int kf_attention_decode_mma_plan(int n_items, int nh, int nkv, int d, int
               : d == 16 ? decode_mma_blocks_per_sm<16>() : 0;
   if (per_sm > 8) per_sm = 8;
   if (per_sm < 1) per_sm = 1;
-  int splits = (int)((148 * per_sm) / blocks);
+  int splits = (int)((kf_sm_count() * per_sm) / blocks);
   const int by_len = (max_keys + 255) / 256;
   if (splits > by_len) splits = by_len;
   if (splits > 64) splits = 64;
@@ -730,8 +730,8 @@ KF_API int kf_attention_decode_plan(int n_items, int nh, int nkv, int d, int max
   const int G = nh / nkv;
   const int ht = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
   const long blocks = (long)n_items * nkv * kf_ceil_div(G, ht);
-  // two blocks of this kernel are resident per SM: fill one wave of 2 x 148 blocks, never a second partial wave
-  int splits = (int)((2 * 148) / blocks);
+  // two blocks of this kernel are resident per SM: fill one wave of two blocks per SM, never a second partial wave
+  int splits = (int)((2 * kf_sm_count()) / blocks);
   const int by_len = (max_keys + 255) / 256;                  // at least 256 keys per split
   if (splits > by_len) splits = by_len;
   if (splits > 32) splits = 32;
@@ -817,6 +817,20 @@ float* g_static_partial_ptr[MAX_DEVICES] = {};
 int* g_static_counters_ptr[MAX_DEVICES] = {};
 }  // namespace
 
+// The size rule of kf_attention_decode_static for a launch of `splits` key splits with `ht` heads per block: KF_OK if the
+// built-in arrays hold its partial results and counters (one split needs neither), else KF_ERR_SIZE with a message.
+KF_API int kf_attention_decode_static_fits(int n_rows, int nh, int nkv, int d, int ht, int splits) {
+  if (n_rows < 0 || nkv < 1 || nh % nkv != 0 || ht < 1 || splits < 1 || !kf_attention_decode_supported(d)) return KF_ERR_SIZE;
+  if (splits == 1) return KF_OK;
+  const long n_counters = (long)n_rows * nkv * kf_ceil_div(nh / nkv, ht);
+  const long n_partial = (long)n_rows * nh * splits * (d + 4);
+  if (n_counters > KF_DECODE_STATIC_MAX_COUNTERS || n_partial > KF_DECODE_STATIC_MAX_PARTIAL_FLOATS) {
+    kf_record_message("kf_attention_decode_static: rows * heads * splits * (head_dim + 4) exceeds the built-in scratch");
+    return KF_ERR_SIZE;
+  }
+  return KF_OK;
+}
+
 KF_API int kf_attention_decode_static(const void* q, void* out, const void* pages, int n_rows, const int* positions,
                                       const int* row_req, const int* table, int table_stride, int page_size, int nh,
                                       int nkv, int d, float scale, float softcap, int window, int max_keys,
@@ -848,16 +862,14 @@ KF_API int kf_attention_decode_static(const void* q, void* out, const void* page
   }
   int ht = 1, splits = 1;
   kf_attention_decode_plan(n_rows, nh, nkv, d, max_keys, &ht, &splits);
-  const long n_counters = (long)n_rows * nkv * kf_ceil_div(nh / nkv, ht);
-  const long n_partial = (long)n_rows * nh * splits * (d + 4);
-  if (n_counters > KF_DECODE_STATIC_MAX_COUNTERS || n_partial > KF_DECODE_STATIC_MAX_PARTIAL_FLOATS) {
-    kf_record_message("kf_attention_decode_static: rows * heads * splits * (head_dim + 4) exceeds the built-in scratch");
-    return KF_ERR_SIZE;
-  }
-  // The arrays keep what the last call left; the counters must start at zero.
-  if (cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream) != cudaSuccess) {
-    kf_record_cuda_error(cudaGetLastError());
-    return KF_ERR_LAUNCH;
+  if (kf_attention_decode_static_fits(n_rows, nh, nkv, d, ht, splits) != KF_OK) return KF_ERR_SIZE;
+  if (splits > 1) {                     // with one split the kernel writes its result directly and touches neither array
+    // The arrays keep what the last call left; the counters must start at zero.
+    const long n_counters = (long)n_rows * nkv * kf_ceil_div(nh / nkv, ht);
+    if (cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_LAUNCH;
+    }
   }
   return kf_attention_decode(q, out, pages, nullptr, n_rows, positions, row_req, table, table_stride, page_size, nh, nkv,
                              d, scale, softcap, window, ht, splits, partial, counters, stream);

@@ -630,8 +630,9 @@ KF_API int kf_attention_prefill_tc_plan(int n_tiles, int nh, int max_keys, int* 
   *run_tiles = 0;
   if (g_forced_parts > 0) { *run_tiles = g_forced_run_tiles; return g_forced_parts; }
   const long blocks = (long)n_tiles * nh;
-  if (blocks <= 0 || 2 * blocks > 148) return 1;
-  int parts = (int)(148 / blocks);
+  const int n_sm = kf_sm_count();
+  if (blocks <= 0 || 2 * blocks > n_sm) return 1;
+  int parts = (int)(n_sm / blocks);
   if (parts > 8) parts = 8;
   const int key_tiles = (max_keys + BKV - 1) / BKV;
   if (parts > key_tiles / 2) parts = key_tiles / 2;

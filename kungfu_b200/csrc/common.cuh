@@ -48,6 +48,7 @@ __device__ __forceinline__ T* kf_produced(T* p) {
 }
 
 extern "C" int kf_pdl_enabled();
+extern "C" int kf_sm_count();           // SMs of the current device
 
 // Launch with the programmatic-dependent-launch attribute when it is switched on (kf_set_pdl).
 template <typename... KArgs, typename... Args>

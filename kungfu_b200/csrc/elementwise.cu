@@ -73,7 +73,7 @@ __global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out
 KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int act, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
   const size_t n = (size_t)T * I;
-  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  const int blocks = (int)((n + 255) / 256 > kf_sm_count() * 16 ? kf_sm_count() * 16 : (n + 255) / 256);
   if (in_dtype == KF_F32 && out_dtype == KF_F32)
     kf_launch(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, T, I, act);
   else if (in_dtype == KF_F32 && out_dtype == KF_BF16)
@@ -95,7 +95,7 @@ __global__ void add_kernel(const float* __restrict__ a, float* __restrict__ x, s
 KF_API int kf_add(const float* a, float* x, long n, cudaStream_t stream) {
   if (n <= 0) return KF_OK;
   const long b = (n + 255) / 256;
-  kf_launch(add_kernel, dim3((int)(b > 148 * 16 ? 148 * 16 : b)), dim3(256), 0, stream, a, x, (size_t)n);
+  kf_launch(add_kernel, dim3((int)(b > kf_sm_count() * 16 ? kf_sm_count() * 16 : b)), dim3(256), 0, stream, a, x, (size_t)n);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -112,7 +112,7 @@ __global__ void convert_kernel(const TI* __restrict__ src, TO* __restrict__ dst,
 KF_API int kf_convert(const void* src, int src_dtype, void* dst, int dst_dtype, long n, cudaStream_t stream) {
   if (n <= 0) return KF_OK;
   const long b = (n + 255) / 256;
-  const int blocks = (int)(b > 148 * 16 ? 148 * 16 : b);
+  const int blocks = (int)(b > kf_sm_count() * 16 ? kf_sm_count() * 16 : b);
   if (src_dtype == KF_BF16 && dst_dtype == KF_F32)
     kf_launch(convert_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)src, (float*)dst, (size_t)n);
   else if (src_dtype == KF_F32 && dst_dtype == KF_BF16)

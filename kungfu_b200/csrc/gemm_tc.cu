@@ -712,6 +712,7 @@ int g_stage_cap_kb = 108;
 int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix the plan of products over more than 64 rows
 
 int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
+  const int n_sm = kf_sm_count();
   int bn = 16;
   while (bn < T && bn < 256) bn *= 2;
   if (gated && bn > 256) bn = 256;
@@ -727,16 +728,16 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
     // memory); up to 256 rows a 128-token tile gives twice the tiles (measured at 256 rows, 9216 x 2304: 29 us against
     // 42 us with one 256-token tile and 220 us split in two).
     bn = T <= 256 ? 128 : 256;
-  } else if (T > 64 && (T <= 512 || (T <= 1024 && K <= 4096 && (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, 64) <= 296))) {
-    // Short portions: 64-token tiles on the weight-streaming kernel, two CTAs per SM, K cut so that about 2 x 148 CTAs
+  } else if (T > 64 && (T <= 512 || (T <= 1024 && K <= 4096 && (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, 64) <= 2 * n_sm))) {
+    // Short portions: 64-token tiles on the weight-streaming kernel, two CTAs per SM, K cut so that about two CTAs per SM
     // run (measured at 2304-wide layers, 128 to 512 rows: 1.3x to 2x faster than one 256-token tile split four ways).
     bn = 64;
     const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
-    while (splits < 8 && tiles * splits * 2 <= 296 && nkb / (splits * 2) >= 8) splits *= 2;
+    while (splits < 8 && tiles * splits * 2 <= 2 * n_sm && nkb / (splits * 2) >= 8) splits *= 2;
   } else {
     const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
-    if (tiles <= 74) {                                 // fewer tiles than half the SMs: cut K so that every SM streams
-      splits = (int)(148 / tiles);                     // weights, in ONE wave (one CTA per SM fits)
+    if (tiles <= n_sm / 2) {                                 // fewer tiles than half the SMs: cut K so that every SM streams
+      splits = (int)(n_sm / tiles);                     // weights, in ONE wave (one CTA per SM fits)
       if (splits > 8) splits = 8;                      // a portable thread-block cluster holds 8 CTAs
       if (splits > nkb) splits = nkb;
     }
@@ -821,14 +822,12 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
   if (stages < 2) return KF_ERR_SIZE;
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
   static bool configured = false;
-  static int n_sm = 148;
+  const int n_sm = kf_sm_count();
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
       kf_record_cuda_error(cudaGetLastError());
       return KF_ERR_SETUP;
     }
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     configured = true;
   }
   const int n_feat = EPI == EPI_GATED ? up_offset : N;
@@ -851,14 +850,12 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, 
   if (stages > 8) stages = 8;
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
   static bool configured = false;
-  static int n_sm = 148;
+  const int n_sm = kf_sm_count();
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
       kf_record_cuda_error(cudaGetLastError());
       return KF_ERR_SETUP;
     }
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     configured = true;
   }
   const int n_feat = EPI == EPI_GATED ? up_offset : N;

@@ -7,13 +7,13 @@ crates/kf-serve/src/engine.rs:375-430); its `generate` command is `Engine.genera
 """
 from __future__ import annotations
 
-import sys
 import time
 from typing import Hashable, Sequence
 
 import numpy as np
 import torch
 
+from .. import events as _events
 from .. import ops
 from ..sampling.sampler import CANDIDATES, Candidates, Sampling, sample, sample_sparse
 from .scheduler import Portion, Request, Scheduler
@@ -22,8 +22,11 @@ from .step import Runner, StepEntry
 
 def emit_event(name: str, **fields) -> None:
     """One structured line on stderr, `kungfu event=<name> k=v ...` (reference: crates/kf-core/src/event.rs:31-44)."""
-    parts = [f"kungfu event={name}"] + [f"{k}={v}" for k, v in fields.items()]
-    print(" ".join(parts), file=sys.stderr, flush=True)
+    was, _events.enabled = _events.enabled, True
+    try:
+        _events.emit(name, **fields)
+    finally:
+        _events.enabled = was
 
 
 class Engine:
@@ -34,7 +37,8 @@ class Engine:
         """`model_dir`: folder with config.json and model.safetensors; or `config` (typed configuration, dictionary
         or config.json path) with `seed` for random weights.  `ctx`: context length per request ('auto' = the
         model's trained length); `batch`: most tokens one step runs; `parallel`: most live requests.
-        `max_tokens_in_cache`: size of each cache group's pool in tokens (default: parallel * ctx).
+        `max_tokens_in_cache`: size of a cache group's pool in tokens (default: parallel * ctx; a windowed group never
+        gets more than parallel * (window + batch + page), and all pools are cut to fit the memory left after the weights).
         `pipeline`: greedy decode steps are launched before the tokens of the step before them have been read (they
         stay on the device as the next step's input), so `step()` returns a step's tokens one call later and the GPU
         does not wait for the host between steps."""
@@ -56,14 +60,26 @@ class Engine:
             trained = getattr(self.cfg, "max_position_embeddings", 8192)
             n_ctx = trained if ctx == "auto" else min(int(ctx), trained) if ctx else trained
             page = page_size or api.DEFAULT_PAGE_SIZE
-            pool_tokens = max_tokens_in_cache or parallel * (-(-n_ctx // page) * page)
-            self.runner = api.make_runner(self.cfg, model, dtype=dtype, device=self.device, page_size=page,
-                                          max_tokens=pool_tokens, max_requests=parallel, max_context=n_ctx,
-                                          cuda_graphs=cuda_graphs)
             if events:
-                emit_event("ready", model=self.cfg.architecture, dtype=str(api.parse_dtype(dtype)).split(".")[-1],
-                           weight_bytes=model.weight_bytes(), cache_bytes_per_token=self.runner.cache.bytes_per_token(),
-                           pool_tokens=pool_tokens, ctx=n_ctx, load_s=f"{time.time() - t0:.2f}")
+                _events.enabled = True
+            pool = f"cuda{self.device.index or 0}"
+            _events.alloc(pool, "weights", model.weight_bytes())
+            # what the cache may take: the memory that is free now, less a reserve for the step's own buffers
+            # (activations of `batch` rows, logits of the wanted rows, split sums) and the allocator's slack
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = max(0, int(free) - max(2 << 30, int(total) // 16))
+            self.runner = api.make_runner(self.cfg, model, dtype=dtype, device=self.device, page_size=page,
+                                          max_tokens=max_tokens_in_cache, max_requests=parallel, max_context=n_ctx,
+                                          cuda_graphs=cuda_graphs, batch=batch, budget_bytes=budget)
+            plan = self.runner.cache.plan
+            _events.emit("plan", **plan.fields())
+            _events.alloc(pool, "cache", plan.paged_bytes)
+            if plan.fixed_bytes:
+                _events.alloc(pool, "state", plan.fixed_bytes)
+            _events.emit("ready", model=self.cfg.architecture, dtype=str(api.parse_dtype(dtype)).split(".")[-1],
+                         weight_bytes=model.weight_bytes(), cache_bytes_per_token=self.runner.cache.bytes_per_token(),
+                         pool_pages=",".join(str(g.pages) for g in plan.groups), ctx=n_ctx,
+                         load_s=f"{time.time() - t0:.2f}")
         self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=batch, max_requests=parallel)
         self._next_id = 0
         self.requests: dict[Hashable, Request] = {}
@@ -96,11 +112,18 @@ class Engine:
         self.scheduler.add(req)
         return request_id
 
-    def cancel(self, request_id: Hashable) -> None:
-        self.flush()
+    def cancel(self, request_id: Hashable) -> list[tuple]:
+        """End a request now.  Returns the events of the step that was in flight (tokens of every request, this one
+        included, and finish reasons that only that step's tokens reveal) followed by (request_id, None, 'cancelled')
+        if the request had not ended by itself; a caller that streams from `step()` must handle them like `step()`'s."""
+        events = self.flush()
         req = self.requests[request_id]
         if req.status != "finished":
             self.scheduler.finish(req, "cancelled")
+            events.append((request_id, None, "cancelled"))
+            if self.events:
+                self._request_event(req)
+        return events
 
     @property
     def idle(self) -> bool:

@@ -26,6 +26,9 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)      # places among `tokens` whose logits are wanted
+    # further integers per token, by stream name, for parts that declare `step_streams` (a second position axis, a
+    # segment id); a stream the entry does not give holds the tokens' positions
+    streams: dict | None = None
 
 
 class StepError(ValueError):
@@ -85,6 +88,7 @@ class StepContext:
         self.tokens = self.positions = self.row_req = self.logit_rows = None
         self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
         self.block_tables: list[torch.Tensor] = []
+        self.streams: dict[str, torch.Tensor] = {}    # extra per-row integers that parts declared (device int32 [rows])
         # host copies
         self.host: dict[str, np.ndarray] = {}
 
@@ -113,6 +117,7 @@ class Runner:
         self.cuda_graphs = False
         self._graphs: dict = {}
         self._graph_safe = model.all_graph_safe() if hasattr(model, "all_graph_safe") else False
+        self.stream_names = tuple(model.step_stream_names()) if hasattr(model, "step_stream_names") else ()
         self.launch_count_hint = 0
 
     # ---- metadata -----------------------------------------------------------------------------------
@@ -160,6 +165,9 @@ class Runner:
         total = lib.kf_step_layout(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, n_want.ctypes.data, b, info.ctypes.data)
         if total < 0:
             raise StepError("a request of the step is not live")
+        T = int(info[1])
+        base = _align4(total)                              # the extra streams follow the native sections, T ints each
+        total = base + len(self.stream_names) * _align4(T) if self.stream_names else total
         slot, dev = self._meta_buffers(total)
         self.last_meta_ints = total
         host = slot[0]
@@ -167,6 +175,24 @@ class Runner:
                               wants.ctypes.data, b, info.ctypes.data, host.data_ptr())
         if rc != 0:
             raise StepError(f"building the step's integer block failed (code {rc})")
+        if self.stream_names:
+            h = host.numpy()
+            pos0 = int(info[12])                           # the positions' section
+            row = 0
+            rows_of = []
+            for e in entries:
+                rows_of.append((row, len(e.tokens)))
+                row += len(e.tokens)
+            for i, name in enumerate(self.stream_names):
+                at = base + i * _align4(T)
+                h[at:at + T] = h[pos0:pos0 + T]
+                for e, (r0, cnt) in zip(entries, rows_of):
+                    vals = (e.streams or {}).get(name)
+                    if vals is not None:
+                        if len(vals) != cnt:
+                            raise StepError(f"request {e.request!r}: stream '{name}' has {len(vals)} values for {cnt} tokens")
+                        h[at + r0:at + r0 + cnt] = np.asarray(vals, dtype=np.int32)
+            info = np.concatenate([info, np.asarray([base], dtype=np.int32)])
         dev[:total].copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
             if slot[1] is None:
@@ -211,6 +237,9 @@ class Runner:
         n_sec = len(self._SECTIONS)
         ctx.block_tables = [dev[int(off[n_sec + g]):int(off[n_sec + g]) + B * width].view(B, width)
                             for g in range(len(self.cache.groups))]
+        if self.stream_names:
+            base = int(info[-1])
+            ctx.streams = {name: dev[base + i * _align4(T):base + i * _align4(T) + T] for i, name in enumerate(self.stream_names)}
         ctx.host = {name: h[where[name][0]:where[name][0] + where[name][1]].copy()
                     for name in ("positions", "row_req", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot")}
         return ctx
@@ -248,6 +277,8 @@ class Runner:
         if not entries:
             return (None, None) if greedy else None
         self.validate(entries)
+        if feedback is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("tokens can only be fed back on the device to a step of single tokens")
         reserved = []
         try:
             for e in entries:
@@ -257,21 +288,24 @@ class Runner:
             for e in reserved:
                 self.cache.cancel_reservation(e.request)
             raise
-        if feedback is not None and any(len(e.tokens) != 1 for e in entries):
-            raise StepError("tokens can only be fed back on the device to a step of single tokens")
-        bucket = self._graph_bucket(entries)
-        picked = None
-        if bucket is None:
-            ctx = self._fill(entries, None, feedback)
-            logits = self._forward(ctx)
-            if greedy and logits is not None:
-                picked = self._argmax(logits)
-        elif greedy and isinstance(bucket, int):
-            logits, picked = self._step_graphed(entries, ("greedy", bucket), feedback)
-        else:
-            logits = self._step_graphed(entries, bucket, feedback)
-            if greedy and logits is not None:
-                picked = self._argmax(logits)
+        try:
+            bucket = self._graph_bucket(entries)
+            picked = None
+            if bucket is None:
+                ctx = self._fill(entries, None, feedback)
+                logits = self._forward(ctx)
+                if greedy and logits is not None:
+                    picked = self._argmax(logits)
+            elif greedy and isinstance(bucket, int):
+                logits, picked = self._step_graphed(entries, ("greedy", bucket), feedback)
+            else:
+                logits = self._step_graphed(entries, bucket, feedback)
+                if greedy and logits is not None:
+                    picked = self._argmax(logits)
+        except BaseException:
+            for e in entries:                              # nothing was committed: the pages taken for this step go back
+                self.cache.cancel_reservation(e.request)
+            raise
         for e in entries:
             self.cache.commit(e.request, len(e.tokens))
         self.steps_run += 1

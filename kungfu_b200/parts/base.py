@@ -49,6 +49,18 @@ class Part:
     # False for a part whose forward does host-side work that depends on the step (loops over requests, reads of
     # ctx.host): steps of a model holding such a part are never captured into CUDA graphs.
     graph_safe = True
+    # Names of further per-row integer streams this part reads from `ctx.streams` (a second position axis, a segment
+    # id, ...).  The step function carries every declared stream in its integer block; a request gives the values with
+    # its tokens (`StepEntry.streams`), and a stream it does not give holds the tokens' positions.
+    step_streams: tuple = ()
+
+    def step_stream_names(self) -> list:
+        names = list(self.step_streams)
+        for c in self.children():
+            for n in c.step_stream_names():
+                if n not in names:
+                    names.append(n)
+        return names
 
     def all_graph_safe(self) -> bool:
         return self.graph_safe and all(c.all_graph_safe() for c in self.children())

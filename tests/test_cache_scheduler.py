@@ -252,3 +252,62 @@ def test_adopted_request_decodes_from_where_its_cache_ends():
     while not s.idle:
         run_plan(s, s.schedule())
     assert req.finish_reason == "length" and len(req.output) == 3 and c.free_pages() == [32] and "r" not in c
+
+
+# ---- sizing of the pools ------------------------------------------------------------------------------------------
+
+def test_plan_gives_windowed_groups_only_what_they_can_hold():
+    from kungfu_b200.cache.plan import NoFit, plan_cache
+    from kungfu_b200.parts.base import FixedState, PagedKV
+    # 4 cache slots: two windowed (window 4096), two global; 8 requests of 8192 tokens, portions of 512, pages of 64
+    needs = [PagedKV(4, 256, 4096), PagedKV(4, 256, None), PagedKV(4, 256, 4096), PagedKV(4, 256, None), FixedState((10,), torch.float32)]
+    plan = plan_cache(needs, page_size=64, parallel=8, ctx=8192, batch=512, element_size=2)
+    by = plan.pages_by_window()
+    assert by[None] == 8 * 8192 // 64
+    assert by[4096] == 8 * (4096 + 512 + 64) // 64 and by[4096] < by[None]
+    page_bytes = 2 * 4 * 64 * 256 * 2
+    assert plan.paged_bytes == 2 * page_bytes * (by[None] + by[4096]) and plan.fixed_bytes == 8 * 40
+    assert not plan.shrunk
+    # a window as long as the context changes nothing
+    same = plan_cache([PagedKV(4, 256, 8192), PagedKV(4, 256, None)], page_size=64, parallel=8, ctx=8192, batch=512, element_size=2)
+    assert same.pages_by_window()[8192] == same.pages_by_window()[None]
+    # a budget below the plan cuts every pool, never below one request's need
+    small = plan_cache(needs, page_size=64, parallel=8, ctx=8192, batch=512, element_size=2, budget_bytes=plan.total_bytes // 2)
+    assert small.shrunk and small.total_bytes <= plan.total_bytes // 2
+    sb = small.pages_by_window()
+    assert sb[None] >= 8192 // 64 and sb[4096] >= (4096 + 512 + 64) // 64 and sb[None] < by[None]
+    with pytest.raises(NoFit, match="no_fit"):
+        plan_cache(needs, page_size=64, parallel=8, ctx=8192, batch=512, element_size=2, budget_bytes=1 << 20)
+    # an explicit pool size is taken as it is (replay makes pools so small that pages are used again)
+    tiny = plan_cache(needs, page_size=64, parallel=8, ctx=8192, batch=8192, element_size=2, pool_tokens=640)
+    assert tiny.pages_by_window() == {4096: 10, None: 10}
+    fields = plan.fields()
+    assert fields["group0"].startswith("window:4096,pages:") and fields["parallel"] == 8
+
+
+def test_manager_takes_the_plans_pool_sizes_and_the_scheduler_lives_with_them():
+    """Pools sized by the plan: the windowed group is smaller than the global one, and requests far longer than the
+    window still run to their end because slid-out pages come back."""
+    from kungfu_b200.cache.plan import plan_cache
+    from kungfu_b200.parts.base import PagedKV
+    needs = [PagedKV(1, 4, 8), PagedKV(1, 4, None)]
+    plan = plan_cache(needs, page_size=4, parallel=2, ctx=64, batch=6, element_size=4)
+    assert plan.pages_by_window() == {8: 2 * 5, None: 2 * 16}
+    cache = CacheManager(needs, page_size=4, n_pages=plan.pages_by_window(), max_requests=2, max_context=64,
+                         dtype=torch.float32, device="cpu")
+    assert [g.pool.n_pages for g in cache.groups] == [10, 32]
+    assert cache.storage[0].shape[0] == 10 and cache.storage[1].shape[0] == 32
+    for rid in ("a", "b"):
+        cache.add_request(rid)
+    fed = {"a": 0, "b": 0}
+    while min(fed.values()) < 64:
+        for rid in ("a", "b"):
+            n = min(6, 64 - fed[rid])
+            if n:
+                cache.reserve(rid, n)
+                cache.commit(rid, n)
+                fed[rid] += n
+        cache.check()
+    cache.release("a")
+    cache.release("b")
+    assert cache.free_pages() == [10, 32]

@@ -137,19 +137,28 @@ def test_requests_that_arrive_or_are_cancelled_while_a_step_is_in_flight(tmp_pat
     e = _engine(folder, cfg_dict, page=8, pool_tokens=512, batch=16, parallel=4)
     a = e.add_request(prompts[0], Sampling(temperature=0.0), max_tokens=10)
     b = e.add_request(prompts[1], Sampling(temperature=0.0), max_tokens=10)
+    events = []
     for _ in range(6):
-        e.step()
+        events += e.step()
     assert e._inflight is not None
     c = e.add_request(prompts[2], Sampling(temperature=0.0), max_tokens=10)      # joins while a step is in flight
-    e.step()
-    e.step()
-    e.cancel(b)
+    events += e.step()
+    events += e.step()
+    assert e._inflight is not None
+    events += e.cancel(b)                        # hands out the tokens of the step that was in flight, then the cancellation
     kept = list(e.requests[b].output)
     assert e.finish_reason(b) == "cancelled" and 0 < len(kept) < 10 and kept == want[1][:len(kept)]
     while not e.idle:
-        e.step()
+        events += e.step()
+    events += e.flush()
     assert e.requests[a].output == want[0] and e.requests[c].output == want[2] and e.requests[b].output == kept
     assert e.runner.cache.n_live == 0
+    # a caller that only reads events sees every token of every request once, in order, and one finish reason each
+    for rid in (a, b, c):
+        mine = [(tok, reason) for r, tok, reason in events if r == rid]
+        assert [tok for tok, _ in mine if tok is not None] == e.requests[rid].output
+        reasons = [reason for _, reason in mine if reason is not None]
+        assert reasons == [e.finish_reason(rid)], (rid, reasons)
 
 
 def test_temperature_sampling_is_reproducible(tmp_path, cpu_ops):
@@ -165,3 +174,38 @@ def test_temperature_sampling_is_reproducible(tmp_path, cpu_ops):
     e = _engine(folder, cfg_dict, page=8, pool_tokens=256, batch=7, parallel=4)
     other = e.generate(prompts, Sampling(temperature=0.8, top_k=0, top_p=1.0), max_tokens=12, seed=10)
     assert other != outs[0]
+
+
+def test_a_step_that_fails_gives_its_pages_back(tmp_path, cpu_ops):
+    """A step that raises after its pages were reserved (here: a kernel error in the pass) leaves the cache as it was:
+    no reservation stays behind, and the same step runs afterwards."""
+    from kungfu_b200 import ops
+    from kungfu_b200.engine import StepEntry
+    cfg_dict = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=3, dtype=torch.float32)
+    runner = _runner(folder, cfg_dict, 4, 64)
+    toks = helpers.random_tokens(13, cfg_dict["vocab_size"], 5)
+    runner.cache.add_request("x")
+    free_before = runner.cache.free_pages()
+    impl = ops._override
+    real_linear = impl.linear
+
+    def broken(*a, **k):
+        raise ops.KernelError("injected")
+    impl.linear = broken
+    try:
+        with pytest.raises(ops.KernelError):
+            runner.step([StepEntry("x", toks, [12])])
+    finally:
+        impl.linear = real_linear
+    assert runner.cache.free_pages() == free_before and runner.cache.length("x") == 0
+    runner.cache.check()
+    from kungfu_b200.engine.step import StepError
+    with pytest.raises(StepError):                 # refused before anything is reserved
+        runner.step([StepEntry("x", toks[:2], [1])], feedback=torch.zeros(1, dtype=torch.int32))
+    assert runner.cache.free_pages() == free_before
+    logits = runner.step([StepEntry("x", toks, [12])])
+    ref = _reference(folder, cfg_dict, {"x": toks})["x"]
+    assert float((logits[0].float().cpu() - ref[12]).abs().max()) < 2e-4
+    runner.cache.release("x")
+    assert runner.cache.free_pages() == [g.pool.n_pages for g in runner.cache.groups]

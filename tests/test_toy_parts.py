@@ -225,3 +225,180 @@ def _run_toy(tmp_path, DEV):
         worst = max(float((row - ref[rid][pos]).abs().max()) for (rid, pos), row in got.items())
         assert len(got) == sum(len(t) for t in reqs.values()) and worst / scale < 2e-4, (mode, worst / scale)
     registry.unregister("ToyForCausalLM")
+
+
+# ---- a third kind of state and a second position axis, both defined here --------------------------------------------
+
+def _define_latent():
+    """`LatentTrail`: a mixer that keeps, for every token, a latent of 24 numbers in pages of its own layout
+    ([page_size, 24], not keys and values), windowed: token i gets W_up . mean(latents of the last `window` tokens).
+    `GridHands`: a position encoding that turns by a SECOND integer stream ('column') the requests give with their
+    tokens.  Neither the state kind nor the stream is known to the framework before this function runs."""
+    from dataclasses import dataclass as dc
+    from kungfu_b200.cache.kinds import register_state_kind
+    from kungfu_b200.parts import Mixer, PositionEncoding
+
+    @dc(frozen=True)
+    class PagedLatent:
+        width: int
+        window: int | None = None
+
+    class LatentView:
+        def __init__(self, pages, page_size, group, writes):
+            self.pages, self.page_size, self.group, self.writes = pages, page_size, group, writes
+
+    class LatentKind:
+        paged = True
+
+        def window(self, need):
+            return need.window
+
+        def page_shape(self, need, page_size):
+            return (page_size, need.width)
+
+        def page_bytes(self, need, page_size, elsize):
+            return page_size * need.width * 4
+
+        def dtype(self, need, cache_dtype):
+            return torch.float32
+
+        def view(self, storage, page_size, group, writes, need):
+            return LatentView(storage, page_size, group, writes)
+
+    register_state_kind(PagedLatent, LatentKind())
+
+    class LatentTrail(Mixer):
+        graph_safe = False
+
+        def __init__(self, w_down, w_up, window, position=None):
+            self.w_down, self.w_up, self.window = w_down, w_up, window          # [24, H], [H, 24]
+            self.position = position
+
+        def state_need(self):
+            return PagedLatent(self.w_down.shape[0], self.window)
+
+        def forward(self, x, ctx, cache):
+            P = cache.page_size
+            lat = x.float() @ self.w_down.float().T                              # [rows, 24]
+            if self.position is not None:                                        # scaled by the second position axis
+                cos, _ = self.position.rotation(ctx)
+                lat = lat * cos[:, :1]
+            table = ctx.block_tables[cache.group]
+            pos = ctx.positions[:ctx.n_rows].long()
+            req = ctx.row_req[:ctx.n_rows].long()
+            page = table[req, pos // P].long()
+            if cache.writes:
+                cache.pages[page, pos % P] = lat
+            out = torch.empty(x.shape[0], self.w_up.shape[0], dtype=torch.float32, device=x.device)
+            for r in range(x.shape[0]):
+                p = int(ctx.host["positions"][r])
+                q = int(ctx.host["row_req"][r])
+                js = torch.arange(max(0, p - self.window + 1), p + 1, device=x.device)
+                pj = table[q, js // P].long()
+                assert bool((pj >= 0).all()), "a page inside the window was given back"
+                out[r] = cache.pages[pj, js % P].mean(0) @ self.w_up.float().T
+            return out
+
+    class GridHands(PositionEncoding):
+        graph_safe = False
+        step_streams = ("column",)
+
+        def rotation(self, ctx):
+            col = ctx.streams["column"][:ctx.n_rows].to(torch.float32)
+            angle = col[:, None] * 0.37
+            return torch.cos(angle).contiguous(), torch.sin(angle).contiguous()
+
+    return PagedLatent, LatentTrail, GridHands
+
+
+def _run_latent(DEV):
+    from kungfu_b200.cache import CacheManager
+    from kungfu_b200.cache.plan import plan_cache
+    from kungfu_b200.engine import Runner, StepEntry
+    from kungfu_b200.parts import DecoderModel, Embedding, FixedState, LayerCall, LmHead, PagedKV, RmsNorm, SandwichBlock
+    PagedLatent, LatentTrail, GridHands = _define_latent()
+    _define()
+    from kungfu_b200.parts import make
+    g = torch.Generator().manual_seed(5)
+    H, V, W, P = 32, 50, 6, 4
+
+    def rnd(*shape, s=0.3):
+        return (torch.randn(*shape, generator=g) * s).to(DEV)
+    emb = Embedding(rnd(V, H, s=1.0))
+    grid = GridHands()
+    ones = torch.zeros(H, device=DEV)
+    layers = []
+    for l in range(2):
+        mixer = LatentTrail(rnd(24, H), rnd(H, 24), W, position=grid if l == 1 else None)
+        ffn = make("feed_forward", "routed", rnd(2, H, s=0.5), rnd(2, 40, H), rnd(2, H, 40))
+        layers.append(SandwichBlock(RmsNorm(ones, 1e-5, True), mixer, None, RmsNorm(ones, 1e-5, True), ffn, None))
+    model = DecoderModel(emb, layers, LmHead(RmsNorm(ones, 1e-5, True), emb.table), [LayerCall(0, 0), LayerCall(1, 1)])
+    needs = model.state_needs()
+    assert [type(n).__name__ for n in needs] == ["PagedLatent", "PagedLatent"] and model.step_stream_names() == ["column"]
+    plan = plan_cache(needs, page_size=P, parallel=2, ctx=40, batch=5, element_size=4)
+    assert plan.pages_by_window() == {W: 2 * 4}                    # ceil((6 + 5 + 4) / 4) pages per request
+    cache = CacheManager(needs, page_size=P, n_pages=plan.pages_by_window(), max_requests=2, max_context=40,
+                         dtype=torch.float32, device=DEV)
+    assert cache.storage[0].shape == (8, P, 24)
+    runner = Runner(model, cache, act_dtype=torch.float32, device=DEV)
+    reqs = {"a": (helpers.random_tokens(23, V, 1), [i % 5 for i in range(23)]), "b": (helpers.random_tokens(9, V, 2), None)}
+
+    def plain(tokens, cols):
+        cols = list(range(len(tokens))) if cols is None else cols
+        x = emb.table.double().cpu()[torch.tensor(tokens)]
+        norm = lambda v: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5)
+        for l, blk in enumerate(layers):
+            lat = norm(x) @ blk.mixer.w_down.double().cpu().T
+            if l == 1:
+                lat = lat * torch.cos(torch.tensor(cols, dtype=torch.float64) * 0.37)[:, None]
+            m = torch.stack([lat[max(0, i - W + 1):i + 1].mean(0) for i in range(len(tokens))])
+            x = x + m @ blk.mixer.w_up.double().cpu().T
+            n = norm(x)
+            choice = torch.argmax(n @ blk.ffn.router.double().cpu().T, -1)
+            y = torch.zeros_like(x)
+            for e in range(2):
+                sel = choice == e
+                y[sel] = torch.relu(n[sel] @ blk.ffn.w_in[e].double().cpu().T) @ blk.ffn.w_out[e].double().cpu().T
+            x = x + y
+        return (norm(x) @ emb.table.double().cpu().T).float()
+    ref = {rid: plain(t, c) for rid, (t, c) in reqs.items()}
+    for rid in reqs:
+        cache.add_request(rid)
+    fed = {rid: 0 for rid in reqs}
+    sizes = [5, 1, 3, 2, 4, 1, 1, 5]
+    k = 0
+    worst = 0.0
+    while any(fed[r] < len(reqs[r][0]) for r in reqs):
+        entries = []
+        for rid, (toks, cols) in reqs.items():
+            n = min(sizes[k % len(sizes)], len(toks) - fed[rid])
+            k += 1
+            if n:
+                st = None if cols is None else {"column": cols[fed[rid]:fed[rid] + n]}
+                entries.append(StepEntry(rid, toks[fed[rid]:fed[rid] + n], list(range(n)), streams=st))
+        logits = runner.step(entries).float().cpu()
+        row = 0
+        for e in entries:
+            for w in e.want:
+                worst = max(worst, float((logits[row] - ref[e.request][fed[e.request] + w]).abs().max()))
+                row += 1
+            fed[e.request] += len(e.tokens)
+        cache.check()
+    scale = max(float(r.abs().max()) for r in ref.values())
+    assert worst / scale < 2e-4, worst / scale
+    assert max(g.pool.n_pages - g.pool.n_free for g in cache.groups) <= 8
+    cache.release("a")
+    cache.add_request("c")
+    free = cache.free_pages()
+    with pytest.raises(Exception, match="stream 'column' has 1 values for 2 tokens"):
+        runner.step([StepEntry("c", [1, 2], [], streams={"column": [0]})])
+    assert cache.free_pages() == free and cache.length("c") == 0
+
+
+@pytest.mark.gpu
+def test_a_third_state_kind_and_a_second_position_axis_from_a_test_file():
+    _run_latent(DEV)
+
+
+def test_a_third_state_kind_and_a_second_position_axis_host_logic(cpu_ops):
+    _run_latent("cpu")
