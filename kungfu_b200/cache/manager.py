@@ -52,6 +52,8 @@ def host_library():
         lib.kf_pool_create.restype = ctypes.c_void_p
         lib.kf_cache_create.restype = ctypes.c_void_p
         lib.kf_cache_mirror.restype = ctypes.POINTER(ctypes.c_int)
+        lib.kf_cache_pool_n_taken.restype = ctypes.c_long
+        lib.kf_cache_pool_n_taken.argtypes = [ctypes.c_void_p, ctypes.c_int]
         for name in ("kf_pool_destroy", "kf_pool_take", "kf_pool_give_back", "kf_pool_n_free", "kf_pool_is_held",
                      "kf_cache_destroy", "kf_cache_width", "kf_cache_n_live", "kf_cache_pool_n_free",
                      "kf_cache_pool_is_held", "kf_cache_mirror", "kf_cache_check"):
@@ -337,6 +339,11 @@ class CacheManager:
     # ---- accounting and self-check -----------------------------------------------------------------------
     def free_pages(self) -> list[int]:
         return [g.pool.n_free for g in self.groups]
+
+    def pages_handed_out(self) -> list[int]:
+        """Per group, how many pages the pool has handed out so far; more than the pool holds means pages were given
+        back and used again."""
+        return [int(self._lib.kf_cache_pool_n_taken(self._h, g)) for g in range(len(self.groups))]
 
     def bytes_per_token(self) -> int:
         """Bytes one token adds over all paged cache slots (windowed slots included, as long as it is in reach)."""

@@ -259,7 +259,8 @@ def cmd_random_weights(args) -> int:
     from .api import load_config
     from .weights import write_random_model
     cfg = load_config(args.config)
-    write_random_model(args.out, cfg, args.seed, dtype=torch.float32 if args.dtype == "float32" else torch.bfloat16)
+    write_random_model(args.out, cfg, args.seed, dtype=torch.float32 if args.dtype == "float32" else torch.bfloat16,
+                       device="cuda:0" if torch.cuda.is_available() else None)
     print(args.out)
     return 0
 

@@ -122,3 +122,50 @@ KF_API int kf_convert(const void* src, int src_dtype, void* dst, int dst_dtype, 
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
+
+// ---- random weights: a counter-based generator that the host restates bit for bit ---------------------------------
+// Element i of a tensor with 64-bit key k: three 64-bit words w_j = mix(k + (3 i + j) * 0x9E3779B97F4A7C15), j = 0..2
+// (the splitmix64 finaliser), cut into twelve 16-bit numbers whose sum s has mean 393210 and standard deviation 65536
+// (to 1e-10); value = float(s - 393210) * (std / 65536).  Integer arithmetic, one exact conversion and one 32-bit
+// multiplication: the same bits on any machine (kungfu_b200/weights/store.py restates it with numpy).  The sum of
+// twelve uniforms is bell-shaped within +-6 standard deviations, which is all random test weights need.
+// The reference's tests draw their tensors from a small generator of their own the same way
+// (crates/kf-backend-cuda/tests/common/mod.rs:71-97).
+__host__ __device__ __forceinline__ unsigned long long kf_mix64(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename TO>
+__global__ void random_normal_kernel(TO* __restrict__ out, size_t n, unsigned long long key, float step) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    int s = 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const unsigned long long w = kf_mix64(key + (3ull * i + j) * 0x9E3779B97F4A7C15ull);
+      s += (int)(w & 0xFFFF) + (int)((w >> 16) & 0xFFFF) + (int)((w >> 32) & 0xFFFF) + (int)(w >> 48);
+    }
+    kf_store(out, i, __fmul_rn((float)(s - 393210), step));
+  }
+}
+
+__global__ void random_table_kernel(int* __restrict__ out, size_t n, unsigned long long key) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = (int)(kf_mix64(key + (3ull * i) * 0x9E3779B97F4A7C15ull) & 0x7FFF);
+}
+
+// out[i] = the i-th value of stream `key` times std (32-bit or bfloat16, rounded to nearest even), or, for
+// dtype -1, a 15-bit integer.
+KF_API int kf_random_fill(void* out, int dtype, long n, unsigned long long key, float std, cudaStream_t stream) {
+  if (n <= 0) return KF_OK;
+  const long b = (n + 255) / 256;
+  const int blocks = (int)(b > kf_sm_count() * 32 ? kf_sm_count() * 32 : b);
+  const float step = std / 65536.0f;
+  if (dtype == KF_F32) random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (size_t)n, key, step);
+  else if (dtype == KF_BF16) random_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (size_t)n, key, step);
+  else if (dtype == -1) random_table_kernel<<<blocks, 256, 0, stream>>>((int*)out, (size_t)n, key);
+  else return KF_ERR_DTYPE;
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

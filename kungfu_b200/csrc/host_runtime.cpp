@@ -23,6 +23,7 @@ struct Pool {
   int n = 0;
   std::vector<int> free_list;           // pop_back hands out low ids first
   std::vector<char> held;
+  long n_taken = 0;                     // pages handed out so far (more than n: pages were used again)
   explicit Pool(int n_pages) : n(n_pages), held(n_pages, 0) {
     free_list.reserve(n_pages);
     for (int i = n_pages - 1; i >= 0; --i) free_list.push_back(i);
@@ -33,6 +34,7 @@ struct Pool {
     const int p = free_list.back();
     free_list.pop_back();
     held[p] = 1;
+    ++n_taken;
     return p;
   }
   bool give_back(int p) {
@@ -117,6 +119,7 @@ KF_HOST_API int kf_cache_pool_is_held(void* h, int g, int page) {
   Pool& p = ((Cache*)h)->groups[g].pool;
   return page >= 0 && page < p.n && p.held[page];
 }
+KF_HOST_API long kf_cache_pool_n_taken(void* h, int g) { return ((Cache*)h)->groups[g].pool.n_taken; }
 KF_HOST_API const int* kf_cache_mirror(void* h, int g) { return ((Cache*)h)->groups[g].mirror.data(); }
 
 // state slot (>= 0) or -(error code)

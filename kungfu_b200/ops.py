@@ -59,6 +59,21 @@ def library_path() -> str:
 
 
 _launches = 0
+_fallbacks: dict[str, int] = {}
+
+
+def note_fallback(what: str) -> None:
+    """A bfloat16 operation that ran on a slower generic kernel because the fast one refuses its shape."""
+    _fallbacks[what] = _fallbacks.get(what, 0) + 1
+
+
+def fallbacks() -> dict[str, int]:
+    """How often, and why, bfloat16 work left the tensor-core kernels (shown by `describe` and the bench)."""
+    return dict(_fallbacks)
+
+
+def fallback_count() -> int:
+    return sum(_fallbacks.values())
 
 
 def launch_count() -> int:
@@ -268,8 +283,10 @@ def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> b
     """Launch the tcgen05 product if it takes these operands; False if the generic kernel must run."""
     T, K = x.shape
     lib = library()
-    if not (use_tensor_cores and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and lib.kf_linear_tc_supported(_p(x), _p(weight), K)):
+    if not (use_tensor_cores and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16):
+        return False
+    if not lib.kf_linear_tc_supported(_p(x), _p(weight), K):
+        note_fallback(f"linear: rows of {K} bfloat16 elements are no multiple of 16 bytes (or a base is unaligned)")
         return False
     plan = _linear_plans.get((T, N, K, mode))
     if plan is None:
@@ -281,6 +298,7 @@ def _linear_tc(x, weight, out, mode: int, N: int, softcap: float, act: int) -> b
     partial = None
     if splits > 1:
         if -(-N // 128) * -(-T // bn) > sc["counters"].numel():
+            note_fallback("linear: more output tiles than split counters")
             return False
         partial = _partial(x.device, splits * T * (2 * N if mode == 2 else N))
     _check(lib.kf_linear_tc(_p(x), _p(weight), _p(out), mode, T, N, K, _f(softcap), act, bn, splits,
@@ -395,6 +413,8 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         _check(lib.kf_attention_prefill(_p(q), _p(out), _p(pages), _p(ctx.tile_row0), _p(ctx.tile_nrows), ctx.n_tiles,
                                         *common, _stream()), "attention (prefill)")
         return
+    if fast and use_fast_attention:
+        note_fallback(f"attention: head size {head_dim} or page size {cache.page_size} has no tensor-core kernel")
     _check(lib.kf_attention_generic(_p(q), _p(out), _dt(q), _p(pages), _dt(pages), _p(rest), *common, n_rest, _stream()),
            "attention (generic)")
 

@@ -150,29 +150,86 @@ class WeightStore:
             raise WeightError(self.where, self.missing, unexpected, self.wrong_shape)
 
 
-# ---- random weights ---------------------------------------------------------------------------
+# ---- random weights ---------------------------------------------------------------------------------------------
+# A counter-based generator keyed by (seed, tensor name, element index), so that any tensor can be drawn on the host or
+# on the device, whole or in part, with the same bits (the kernel is `random_normal_kernel` in csrc/elementwise.cu):
+#   w_j = mix(key + (3 i + j) * 0x9E3779B97F4A7C15) for j = 0, 1, 2   (splitmix64's finaliser, arithmetic modulo 2^64)
+#   s   = the sum of the twelve 16-bit pieces of w_0, w_1, w_2         (mean 393210, standard deviation 65536)
+#   x_i = float32(s - 393210) * float32(std / 65536), then rounded to the stored type
+# Only integers, one exact conversion and one correctly rounded product: no library function whose last bit could
+# differ between machines.  The reference's tests draw tensors from a small generator of their own in the same spirit
+# (crates/kf-backend-cuda/tests/common/mod.rs:71-97).
+
+_GOLDEN = 0x9E3779B97F4A7C15
+_M1, _M2 = 0xBF58476D1CE4E5B9, 0x94D049BB133111EB
+
 
 def _tensor_seed(seed: int, name: str) -> int:
     h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF
+    return int.from_bytes(h[:8], "little")
+
+
+def _mix64(z):
+    import numpy as np
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(_M1)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(_M2)
+    return z ^ (z >> np.uint64(31))
+
+
+def random_values(key: int, start: int, count: int, std: float):
+    """Elements start..start+count-1 of stream `key` as a float32 numpy array (the host restatement of the kernel)."""
+    import numpy as np
+    out = np.empty(count, dtype=np.float32)
+    step = np.float32(np.float32(std) / np.float32(65536.0))
+    chunk = 1 << 22
+    with np.errstate(over="ignore"):
+        for a in range(0, count, chunk):
+            n = min(chunk, count - a)
+            i3 = (np.arange(start + a, start + a + n, dtype=np.uint64) * np.uint64(3))
+            s = np.zeros(n, dtype=np.int64)
+            for j in range(3):
+                w = _mix64(np.uint64(key) + (i3 + np.uint64(j)) * np.uint64(_GOLDEN))
+                s += ((w & np.uint64(0xFFFF)) + ((w >> np.uint64(16)) & np.uint64(0xFFFF))
+                      + ((w >> np.uint64(32)) & np.uint64(0xFFFF)) + (w >> np.uint64(48))).astype(np.int64)
+            out[a:a + n] = (s - 393210).astype(np.float32) * step
+    return out
+
+
+def random_table_values(key: int, count: int):
+    import numpy as np
+    with np.errstate(over="ignore"):
+        i3 = np.arange(count, dtype=np.uint64) * np.uint64(3)
+        return (_mix64(np.uint64(key) + i3 * np.uint64(_GOLDEN)) & np.uint64(0x7FFF)).astype(np.int32)
 
 
 def random_tensor(spec: TensorSpec, seed: int, stored_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """The host tensor random-weights mode stores for `spec`: N(0, std), its own stream per tensor name."""
-    g = torch.Generator(device="cpu")
-    g.manual_seed(_tensor_seed(seed, spec.name))
+    """The host tensor random-weights mode stores for `spec`: bell-shaped around 0 with spread `spec.std`, its own
+    stream per tensor name."""
+    import math
+    key = _tensor_seed(seed, spec.name)
+    n = int(math.prod(spec.shape))
     if spec.kind == "table":
-        return torch.randint(0, 2 ** 15, tuple(spec.shape), generator=g, dtype=torch.int32)
-    t = torch.empty(tuple(spec.shape), dtype=torch.float32)
-    t.normal_(0.0, spec.std, generator=g)
-    return t.to(stored_dtype)
+        return torch.from_numpy(random_table_values(key, n)).view(tuple(spec.shape))
+    return torch.from_numpy(random_values(key, 0, n, spec.std)).view(tuple(spec.shape)).to(stored_dtype)
 
 
 def random_tensor_device(spec: TensorSpec, seed: int, stored_dtype: torch.dtype, device) -> torch.Tensor:
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, spec.name))
+    """The same values as `random_tensor`, drawn on the device by the library's own kernel."""
+    import ctypes
+    from .. import ops
+    key = _tensor_seed(seed, spec.name)
     if spec.kind == "table":
-        return torch.randint(0, 2 ** 15, tuple(spec.shape), generator=g, dtype=torch.int32, device=device)
-    t = torch.empty(tuple(spec.shape), dtype=stored_dtype, device=device)
-    t.normal_(0.0, spec.std, generator=g)
+        t = torch.empty(tuple(spec.shape), dtype=torch.int32, device=device)
+        code = -1
+    else:
+        if stored_dtype not in (torch.float32, torch.bfloat16):
+            return random_tensor(spec, seed, stored_dtype).to(device)
+        t = torch.empty(tuple(spec.shape), dtype=stored_dtype, device=device)
+        code = ops.F32 if stored_dtype == torch.float32 else ops.BF16
+    with torch.cuda.device(device):
+        rc = ops.library().kf_random_fill(ctypes.c_void_p(t.data_ptr()), code, ctypes.c_long(t.numel()),
+                                          ctypes.c_ulonglong(key), ctypes.c_float(spec.std),
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise ops.KernelError(f"random weights on the device failed (status {rc})")
     return t

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import json
+import math
 import os
 import random
 
@@ -53,21 +54,101 @@ TINY_E = {
     "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
     "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
     "intermediate_size": 1536, "vocab_size": 3000, "rope_theta": 10000.0, "sliding_window": 100,
-    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 128,
+    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 144,
     "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 1024,
     "hidden_activation": "gelu_pytorch_tanh",
 }
 
 
-def write_model(folder: str, cfg_dict: dict, seed: int, dtype=torch.bfloat16, matrix_scale: float = 1.0):
-    """A model folder with random weights through the framework's random-weights mode."""
+def write_model(folder: str, cfg_dict: dict, seed: int, dtype=torch.bfloat16, sharp: bool = False):
+    """A model folder with random weights through the framework's random-weights mode.  `sharp`: see `sharpen`."""
     from kungfu_b200.api import load_config
     from kungfu_b200.weights import write_random_model
     cfg = load_config(dict(cfg_dict))
     write_random_model(folder, cfg, seed, dtype=dtype)
     with open(os.path.join(folder, "config.json"), "w") as f:      # keep the test's own dictionary
         json.dump(cfg_dict, f)
+    if sharp:
+        sharpen(folder, cfg_dict, seed)
     return folder
+
+
+LOUD_FRACTION = 0.1     # of the vocabulary, at its end: ids that prompts of sharp models never hold
+
+
+def quiet_vocab(cfg_dict: dict) -> int:
+    """Prompts of a sharpened model draw their ids below this, so that the loud output rows are never inputs."""
+    return int(cfg_dict["vocab_size"] * (1.0 - LOUD_FRACTION))
+
+
+def sharpen(folder: str, cfg_dict: dict, seed: int) -> None:
+    """`sharpen_tensors` applied to a model folder (model.safetensors is rewritten)."""
+    from safetensors.torch import save_file
+    tensors = {k: v.clone() for k, v in read_tensors(folder).items()}
+    sharpen_tensors(cfg_dict, tensors, seed)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+
+
+def sharpen_tensors(cfg_dict: dict, tensors: dict, seed: int, device="cpu") -> None:
+    """Change random weights (a dictionary of tensors by file name, in place) so that the model's constants matter.
+    With matrices of spread 0.02 every attention score is about 0.05 and every logit below 1: a softcap of 20 to 50
+    is then the identity to 1e-6, and a wrong attention scale or rotation base moves the logits by less than the
+    bfloat16 tolerance.  Here
+    * the query and key matrices of every layer are scaled until the largest scores before the cap (three spreads)
+      lose about 3 to the cap, s - cap tanh(s / cap) ~ s^3 / (3 cap^2) = 3, i.e. a factor of e^3 in their softmax
+      weight: a spread of 9.4 for a cap of 50, 5.1 for 20 (8 where the configuration has no cap).  Sharper than that
+      and the softmax turns into an argmax that the rounding of a bfloat16 key can flip, which says nothing about
+      the engine;
+    * the last tenth of the output rows (the embedding's rows when tied; those ids are kept out of the prompts) is
+      scaled row by row so that the largest logit of a row before the final cap lies between 0.3 and 2 caps on the
+      probe sequence (louder rows would only multiply the rounding of the hidden state into the result).
+    The factors are found with the plain implementation on a probe sequence, layer after layer."""
+    import plain_gemma2
+    probe_tokens = random_tokens(min(96, cfg_dict["max_position_embeddings"]), quiet_vocab(cfg_dict), seed + 9000)
+    cap = cfg_dict.get("attn_logit_softcapping") or 0.0
+    spread = (9.0 * cap * cap) ** (1.0 / 3.0) / 3.0 if cap > 0 else 8.0
+    for _ in range(4):                                     # later layers see what earlier ones now produce: iterate
+        pr: dict = {}
+        plain_gemma2.forward(cfg_dict, tensors, probe_tokens, probe=pr, device=device)
+        for l, sc in enumerate(pr["scores"]):
+            f = math.sqrt(spread / max(float(sc.std()), 1e-9))
+            for n in ("q_proj", "k_proj"):
+                name = f"model.layers.{l}.self_attn.{n}.weight"
+                tensors[name] = (tensors[name].float() * f).to(tensors[name].dtype)
+    pr = {}
+    plain_gemma2.forward(cfg_dict, tensors, probe_tokens, probe=pr, device=device)
+    out_name = "lm_head.weight" if "lm_head.weight" in tensors else "model.embed_tokens.weight"
+    fcap = cfg_dict.get("final_logit_softcapping") or 30.0
+    V = cfg_dict["vocab_size"]
+    lo = quiet_vocab(cfg_dict)
+    peak = pr["logits"][:, lo:].abs().max(0).values.clamp_min(1e-9)                       # per loud row
+    target = fcap * (0.3 + 1.7 * torch.arange(V - lo, dtype=torch.float64) / max(V - lo - 1, 1))
+    w = tensors[out_name]
+    w[lo:] = (w[lo:].float() * (target / peak).float().to(w.device)[:, None]).to(w.dtype)
+
+
+# What a test must notice: each entry changes one constant of the architecture in a copy of the configuration.
+def mutations(cfg_dict: dict) -> dict:
+    n = cfg_dict["num_hidden_layers"]
+    out = {"attention softcap off": {"attn_logit_softcapping": 0.0},
+           "final softcap off": {"final_logit_softcapping": 0.0},
+           "scale from head_dim": {"query_pre_attn_scalar": cfg_dict["head_dim"]},
+           "rope base x 10": {"rope_theta": cfg_dict["rope_theta"] * 10.0},
+           "window + 1": {"sliding_window": cfg_dict["sliding_window"] + 1},
+           "sliding on odd layers": {"layer_types": ["full_attention" if l % 2 == 0 else "sliding_attention" for l in range(n)]}}
+    base_types = cfg_dict.get("layer_types") or ["sliding_attention" if l % 2 == 0 else "full_attention" for l in range(n)]
+    live = {}
+    for name, change in out.items():
+        if all(cfg_dict.get(k, base_types if k == "layer_types" else None) == v for k, v in change.items()):
+            continue                                   # the configuration already has this value: nothing to notice
+        if name == "attention softcap off" and not cfg_dict.get("attn_logit_softcapping"):
+            continue
+        if name == "final softcap off" and not cfg_dict.get("final_logit_softcapping"):
+            continue
+        if name == "window + 1" and "sliding_attention" not in base_types:
+            continue
+        live[name] = {**cfg_dict, **change}
+    return live
 
 
 def read_tensors(folder: str) -> dict:

@@ -34,7 +34,7 @@ def rope_angles(positions: torch.Tensor, head_dim: int, base: float, dtype) -> t
     crates/kf-backend-cuda/src/exec.rs:1412-1426 (inverse frequencies held as 32-bit numbers)."""
     i = torch.arange(head_dim // 2, dtype=torch.float64)
     inv_freq = (base ** (-2.0 * i / head_dim)).to(torch.float32).to(dtype)
-    ang = positions.to(dtype)[:, None] * inv_freq[None, :]
+    ang = positions.to(dtype)[:, None] * inv_freq.to(positions.device)[None, :]
     return torch.cos(ang), torch.sin(ang)
 
 
@@ -63,26 +63,38 @@ def visible(n: int, window: int | None) -> torch.Tensor:
     return m
 
 
-def attention(x, wq, wk, wv, wo, *, n_heads, n_kv_heads, head_dim, scale, cap, window, base):
+def rounded(x: torch.Tensor, to) -> torch.Tensor:
+    """x as it is after being stored in element type `to` (None: unchanged).  The reference rounds activations to the
+    weights' companion type before a product and keeps the cache in 16 bits (crates/kf-quant/src/lib.rs:154-175,
+    crates/kf-backend-cpu/src/lib.rs:95-110); with `to=torch.bfloat16` this file rounds at the same places as an
+    engine that computes in bfloat16: product inputs, and queries, keys and values as attention reads them."""
+    return x if to is None else x.to(to).to(x.dtype)
+
+
+def attention(x, wq, wk, wv, wo, *, n_heads, n_kv_heads, head_dim, scale, cap, window, base, rounding=None, probe=None):
     """Grouped-query attention over the whole sequence.  crates/kf-layers/src/attention.rs:118-150,211-283;
     scores, cap, mask and softmax crates/kf-backend-cpu/src/attention.rs:79-147; head h reads kv head
-    h / (n_heads / n_kv_heads) (:79,92)."""
+    h / (n_heads / n_kv_heads) (:79,92).  `probe`: a list that receives the scores before the cap (visible ones)."""
     T = x.shape[0]
     dt = x.dtype
     q = (x @ wq.to(dt).T).view(T, n_heads, head_dim)
     k = (x @ wk.to(dt).T).view(T, n_kv_heads, head_dim)
     v = (x @ wv.to(dt).T).view(T, n_kv_heads, head_dim)
-    cos, sin = rope_angles(torch.arange(T), head_dim, base, dt)
-    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    cos, sin = rope_angles(torch.arange(T, device=x.device), head_dim, base, dt)
+    q, k = rounded(apply_rope(q, cos, sin), rounding), rounded(apply_rope(k, cos, sin), rounding)
+    v = rounded(v, rounding)
     group = n_heads // n_kv_heads
-    mask = visible(T, window)
-    out = torch.empty(T, n_heads, head_dim, dtype=dt)
+    mask = visible(T, window).to(x.device)
+    out = torch.empty(T, n_heads, head_dim, dtype=dt, device=x.device)
     for h in range(n_heads):
         kh, vh = k[:, h // group], v[:, h // group]
-        s = softcap((q[:, h] @ kh.T) * scale, cap)
+        raw = (q[:, h] @ kh.T) * scale
+        if probe is not None:
+            probe.append(raw[mask])
+        s = softcap(raw, cap)
         s = s.masked_fill(~mask, float("-inf"))
         out[:, h] = torch.softmax(s, dim=-1) @ vh
-    return out.reshape(T, n_heads * head_dim) @ wo.to(dt).T
+    return rounded(out.reshape(T, n_heads * head_dim), rounding) @ wo.to(dt).T
 
 
 def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
@@ -100,10 +112,10 @@ def activation(name: str, x: torch.Tensor) -> torch.Tensor:
     raise ValueError(name)
 
 
-def feed_forward(x, w_gate, w_up, w_down, act: str) -> torch.Tensor:
+def feed_forward(x, w_gate, w_up, w_down, act: str, rounding=None) -> torch.Tensor:
     """y = (act(x Wgate^T) * (x Wup^T)) Wdown^T.  crates/kf-layers/src/ffn.rs:24-47."""
     dt = x.dtype
-    return (activation(act, x @ w_gate.to(dt).T) * (x @ w_up.to(dt).T)) @ w_down.to(dt).T
+    return rounded(activation(act, x @ w_gate.to(dt).T) * (x @ w_up.to(dt).T), rounding) @ w_down.to(dt).T
 
 
 def is_sliding(cfg: dict, layer: int) -> bool:
@@ -115,37 +127,48 @@ def is_sliding(cfg: dict, layer: int) -> bool:
     return layer % 2 == 0
 
 
-def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64) -> torch.Tensor:
+def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, rounding=None, probe: dict | None = None,
+            device="cpu") -> torch.Tensor:
     """Logits [T, vocab] for the whole token sequence.  `cfg` is the config.json dictionary, `tensors` maps
     file names to tensors.  Block arrangement: crates/kf-layers/src/basic.rs:241-253 and gemma2.rs:39-41:
       h = x + post_attn_norm(attn(input_norm(x)));  out = h + post_ffn_norm(ffn(pre_ffn_norm(h)))
-    Head: final norm, tied output matrix, final cap (crates/kf-layers/src/model.rs:155-175)."""
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
+    Head: final norm, tied output matrix, final cap (crates/kf-layers/src/model.rs:155-175).
+    `rounding`: see `rounded`.  `probe`: a dictionary that receives 'scores' (per layer, the visible scores before the
+    cap) and 'logits' (before the cap).  `device`: where the arithmetic runs (tensors are moved there as they are used)."""
+    tokens = torch.as_tensor(tokens, dtype=torch.long, device=device)
     H = cfg["hidden_size"]
     eps = cfg["rms_norm_eps"]
     nh, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     d = cfg.get("head_dim", H // nh)
     scale = 1.0 / math.sqrt(cfg.get("query_pre_attn_scalar", d))
     act = cfg.get("hidden_activation") or cfg.get("hidden_act") or "gelu_pytorch_tanh"
-    x = embed(tensors["model.embed_tokens.weight"], tokens, H, dtype)
+
+    def t(name):
+        return tensors[name].to(device)
+    x = embed(t("model.embed_tokens.weight"), tokens, H, dtype)
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
-        n = rms_norm(x, tensors[p + "input_layernorm.weight"], eps)
-        a = attention(n, tensors[p + "self_attn.q_proj.weight"], tensors[p + "self_attn.k_proj.weight"],
-                      tensors[p + "self_attn.v_proj.weight"], tensors[p + "self_attn.o_proj.weight"],
+        n = rounded(rms_norm(x, t(p + "input_layernorm.weight"), eps), rounding)
+        scores = [] if probe is not None else None
+        a = attention(n, t(p + "self_attn.q_proj.weight"), t(p + "self_attn.k_proj.weight"),
+                      t(p + "self_attn.v_proj.weight"), t(p + "self_attn.o_proj.weight"),
                       n_heads=nh, n_kv_heads=nkv, head_dim=d, scale=scale,
                       cap=cfg.get("attn_logit_softcapping", 50.0) or 0.0,
                       window=(cfg.get("sliding_window", 4096) or None) if is_sliding(cfg, l) else None,
-                      base=cfg.get("rope_theta", 10000.0))
-        x = x + rms_norm(a, tensors[p + "post_attention_layernorm.weight"], eps)
-        n = rms_norm(x, tensors[p + "pre_feedforward_layernorm.weight"], eps)
-        f = feed_forward(n, tensors[p + "mlp.gate_proj.weight"], tensors[p + "mlp.up_proj.weight"],
-                         tensors[p + "mlp.down_proj.weight"], act)
-        x = x + rms_norm(f, tensors[p + "post_feedforward_layernorm.weight"], eps)
-    n = rms_norm(x, tensors["model.norm.weight"], eps)
-    out = tensors.get("lm_head.weight", tensors["model.embed_tokens.weight"])
+                      base=cfg.get("rope_theta", 10000.0), rounding=rounding, probe=scores)
+        if probe is not None:
+            probe.setdefault("scores", []).append(torch.cat([s.reshape(-1) for s in scores]).cpu())
+        x = x + rms_norm(a, t(p + "post_attention_layernorm.weight"), eps)
+        n = rounded(rms_norm(x, t(p + "pre_feedforward_layernorm.weight"), eps), rounding)
+        f = feed_forward(n, t(p + "mlp.gate_proj.weight"), t(p + "mlp.up_proj.weight"),
+                         t(p + "mlp.down_proj.weight"), act, rounding)
+        x = x + rms_norm(f, t(p + "post_feedforward_layernorm.weight"), eps)
+    n = rounded(rms_norm(x, t("model.norm.weight"), eps), rounding)
+    out = t("lm_head.weight") if "lm_head.weight" in tensors else t("model.embed_tokens.weight")
     logits = n @ out.to(dtype).T
-    return softcap(logits, cfg.get("final_logit_softcapping", 30.0) or 0.0)
+    if probe is not None:
+        probe["logits"] = logits.cpu()
+    return softcap(logits, cfg.get("final_logit_softcapping", 30.0) or 0.0).cpu()
 
 
 def greedy(cfg: dict, tensors: dict, prompt, n_new: int, dtype=torch.float64) -> list[int]:

@@ -170,3 +170,22 @@ def test_tied_and_untied_head(tmp_path):
     with pytest.raises(WeightError) as e:
         api.load_model(folder, dtype="float32", device="cpu")
     assert e.value.missing == ["lm_head.weight"]
+
+
+def test_random_generator_is_counter_based():
+    """Any part of a tensor can be drawn alone; the first values of one stream are pinned so that a change of the
+    generator (which would silently change every test model) shows."""
+    from kungfu_b200.weights.store import TensorSpec, _tensor_seed, random_tensor, random_values
+    spec = TensorSpec("model.layers.3.mlp.up_proj.weight", (37, 53), 0.02)
+    whole = random_tensor(spec, 7, torch.float32).view(-1)
+    part = torch.from_numpy(random_values(_tensor_seed(7, spec.name), 1000, 61, 0.02))
+    assert torch.equal(part, whole[1000:1061])
+    big = random_tensor(TensorSpec("x", (200000,), 1.0), 1, torch.float32)
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01 and float(big.abs().max()) < 6.0
+    assert 0.66 < float((big.abs() < 1.0).float().mean()) < 0.70          # bell-shaped: about 68 % within one spread
+    first = random_values(0x0123456789ABCDEF, 0, 4, 65536.0).tolist()
+    assert first == [float(v) for v in first] and len(set(first)) == 4
+    assert [int(v) for v in first] == PINNED_FIRST_VALUES
+
+
+PINNED_FIRST_VALUES = [-11654, -90132, -84309, 221047]

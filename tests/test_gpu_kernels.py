@@ -609,3 +609,61 @@ def test_argmax_and_topk(ops, V):
         assert ids.cpu().tolist() == order.tolist()
         assert torch.equal(vals.cpu(), torch.gather(logits, 1, order))
         assert float((lse.cpu().double() - torch.logsumexp(logits.double(), -1)).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_random_weights_are_the_same_bits_on_host_and_device(ops, dtype):
+    """The counter-based generator of random-weights mode: the kernel and its numpy restatement give equal tensors."""
+    from kungfu_b200.weights.store import TensorSpec, random_tensor, random_tensor_device
+    for spec in (TensorSpec("model.layers.0.mlp.up_proj.weight", (333, 517), 0.02), TensorSpec("n", (2304,), 0.1, "norm"),
+                 TensorSpec("big", (1 << 21,), 1.7)):
+        host = random_tensor(spec, 11, dtype)
+        dev = random_tensor_device(spec, 11, dtype, torch.device(DEV))
+        assert dev.dtype == dtype and torch.equal(dev.cpu(), host), spec.name
+    table = TensorSpec("ids", (1000,), 1.0, "table")
+    assert torch.equal(random_tensor_device(table, 5, torch.int32, torch.device(DEV)).cpu(), random_tensor(table, 5))
+
+
+@pytest.mark.parametrize("ratio", [0.5, 1.0, 3.0])
+@pytest.mark.parametrize("path,nh,nkv,d,P,cap", [("prefill tcgen05", 8, 4, 256, 64, 50.0), ("prefill tcgen05", 6, 2, 128, 64, 20.0),
+                                                 ("prefill tcgen05 cut", 4, 2, 64, 64, 30.0), ("prefill mma.sync", 6, 2, 32, 16, 20.0),
+                                                 ("decode mma", 8, 4, 256, 64, 50.0), ("decode mma", 32, 16, 128, 64, 20.0),
+                                                 ("decode simt", 8, 4, 256, 64, 50.0), ("generic", 9, 3, 48, 8, 30.0)])
+def test_softcap_where_it_bends(ops, path, nh, nkv, d, P, cap, ratio):
+    """Every bfloat16 attention kernel with queries scaled so that the largest scores before the cap reach `ratio` caps:
+    half a cap (the polynomial branch of the tcgen05 kernel), one cap, and three caps (its exponential branch, and
+    saturation), against float64.  The same reference without the cap is far outside the tolerance, so a kernel that
+    dropped or misplaced the cap would fail here."""
+    lens = [300, 90, 1] if path.startswith("prefill") or path == "generic" else [300, 2100, 65, 1]
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=61)
+    if path.startswith("prefill") or path == "generic":
+        rows = [(r, p) for r, n in enumerate(lens[:2]) for p in range(n)]
+        dec, pre = [], list(range(len(rows)))
+    else:
+        rows = [(r, n - 1) for r, n in enumerate(lens)]
+        dec, pre = list(range(len(rows))), []
+    g = torch.Generator().manual_seed(62)
+    scale = 1.0 / math.sqrt(d)
+    # scale * q.k has spread 1 for unit-variance q and k: three spreads reach ratio * cap
+    q = (torch.randn(len(rows), nh, d, generator=g) * (ratio * cap / 3.0)).to(torch.bfloat16)
+    ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+               torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
+    out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    was = (ops.prefill_on_tcgen05, ops.decode_on_tensor_cores, ops.use_fast_attention, ops.prefill_plan_override)
+    ops.prefill_on_tcgen05 = path.startswith("prefill tcgen05")
+    ops.decode_on_tensor_cores = path == "decode mma"
+    ops.use_fast_attention = path != "generic"
+    ops.prefill_plan_override = (2, 0) if path == "prefill tcgen05 cut" else None
+    try:
+        ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, cap, None)
+    finally:
+        ops.prefill_on_tcgen05, ops.decode_on_tensor_cores, ops.use_fast_attention, ops.prefill_plan_override = was
+    ops.raise_on_device_error()
+    pick = list(range(0, len(rows), 5)) + [len(rows) - 1]
+    ref = torch.stack([_attn_ref(q[i], ks[rows[i][0]], vs[rows[i][0]], rows[i][1], nh, nkv, scale, cap, None) for i in pick])
+    nocap = torch.stack([_attn_ref(q[i], ks[rows[i][0]], vs[rows[i][0]], rows[i][1], nh, nkv, scale, 0.0, None) for i in pick])
+    got = out.view(len(rows), nh, d)[pick]
+    assert bool(torch.isfinite(got.float()).all())
+    assert rel_err(got, ref) < 1e-2
+    if ratio >= 1.0:
+        assert rel_err(nocap, ref) > 0.1, "the case must be one in which the cap matters"
