@@ -32,7 +32,11 @@ KF_API int kf_embed(const int* tokens, const void* table, int table_dtype, float
 }
 
 // cos/sin of position * inv_freq[i], all in 32-bit (accurate sincosf: no fast-math in this library).
-// Reference: crates/kf-backend-cuda/src/kernels/rope.cu:4-14.
+// The product of a position and a 32-bit frequency has up to 48 significant bits; rounded to 32-bit it is off by up to
+// 2.4e-4 rad at position 4,000, which a 32-bit engine with scores of 40 shows in its logits.  So the product is kept as
+// an unevaluated sum hi + lo (lo = fma(p, f, -hi) is its exact rounding error) and the tables are
+// cos(hi) - lo sin(hi) and sin(hi) + lo cos(hi): exact to first order in lo, which is below 2^-12 for any position.
+// Reference: crates/kf-backend-cuda/src/kernels/rope.cu:4-14 (angle as one 32-bit product).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
   kf_pdl_trigger();
@@ -40,11 +44,13 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   const int t = idx / half, i = idx - t * half;
-  const float angle = (float)positions[t] * inv_freq[i];
+  const float p = (float)positions[t], f = inv_freq[i];
+  const float hi = __fmul_rn(p, f);
+  const float lo = __fmaf_rn(p, f, -hi);
   float s, c;
-  sincosf(angle, &s, &c);
-  cos_out[idx] = c;
-  sin_out[idx] = s;
+  sincosf(hi, &s, &c);
+  cos_out[idx] = __fmaf_rn(-lo, s, c);
+  sin_out[idx] = __fmaf_rn(lo, c, s);
 }
 
 KF_API int kf_rope_table(const int* positions, const float* inv_freq, float* cos_out, float* sin_out,

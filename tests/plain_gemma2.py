@@ -93,7 +93,14 @@ def attention(x, wq, wk, wv, wo, *, n_heads, n_kv_heads, head_dim, scale, cap, w
             probe.append(raw[mask])
         s = softcap(raw, cap)
         s = s.masked_fill(~mask, float("-inf"))
-        out[:, h] = torch.softmax(s, dim=-1) @ vh
+        if rounding is None:
+            out[:, h] = torch.softmax(s, dim=-1) @ vh
+        else:
+            # an engine that multiplies the softmax weights with the values on 16-bit tensor cores rounds the weights
+            # e^(s - max) too (the sum that divides them stays exact); the reference does so as well
+            # (crates/kf-backend-cuda/src/kernels/flash.cu:193-199)
+            e = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+            out[:, h] = (rounded(e, rounding) @ vh) / e.sum(dim=-1, keepdim=True)
     return rounded(out.reshape(T, n_heads * head_dim), rounding) @ wo.to(dt).T
 
 

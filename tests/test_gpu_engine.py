@@ -15,44 +15,32 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# rel = max|got - ref| / max|ref| over all wanted rows.  32-bit: rounding of sums only, against float64.
-# bfloat16 on plainly drawn weights, against float64: activations and cached keys/values are rounded to 8 bits of
-# mantissa at every product (the reference's own bound for half-precision caches is 2e-2,
-# crates/kf-backend-cuda/tests/common/mod.rs:181-187).  bfloat16 on sharpened weights (helpers.sharpen_tensors):
-# against the plain model rounded to bfloat16 at the same places (product inputs, queries, keys, values), because
-# scores of 30 and logits beyond their cap multiply the rounding of a hidden state by more than the tolerance;
-# what is left is the order of sums and the rounding of the softmax weights, and the bound is tighter.
-# tests/test_oracle_sensitivity.py shows that every constant of the architecture moves the sharp models' logits by
-# more than ten times these bounds.
+# rel = max|got - ref| / max|ref| over all wanted rows, always against float64.  32-bit: rounding of sums only.
+# bfloat16: activations, cached keys/values and softmax weights are rounded to 8 bits of mantissa at every product
+# (the reference's own bound for half-precision caches is 2e-2, crates/kf-backend-cuda/tests/common/mod.rs:181-187).
+# Draws of the weights (helpers.sharpen_tensors): 'plain' for both precisions; 'sharp' (scores at the attention cap,
+# logits beyond the final cap) for 32-bit; 'loud' (logits at the final cap) for bfloat16.
+# tests/test_oracle_sensitivity.py shows which constant of the architecture each combination would notice.
 TOL = {"float32": 2e-4, "bfloat16": 2e-2}
-TOL_SHARP = {"float32": 2e-4, "bfloat16": 1e-2}
+DRAWS = [("plain", "float32"), ("plain", "bfloat16"), ("sharp", "float32"), ("loud", "bfloat16")]
 
 # six requests each, at most four live in the mixed traces: what the first ones give back the last ones take
 CASES = {"A": (helpers.TINY_A, [5, 17, 23, 40, 11, 30], 4), "B": (helpers.TINY_B, [1, 31, 40, 70, 9, 50], 8),
          "C": (helpers.TINY_C, [3, 50, 64, 29, 120, 77], 16), "D": (helpers.TINY_D, [2, 40, 17, 90, 33, 8], 4)}
 
 
-def _references(cfg, tensors, reqs, sharp):
-    """{dtype: {request: logits}}: float64 for the 32-bit engine; for bfloat16 the same, or on sharp weights the
-    plain model rounded where a bfloat16 engine rounds."""
-    exact = {rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
-    if not sharp:
-        return {"float32": exact, "bfloat16": exact}
-    return {"float32": exact,
-            "bfloat16": {rid: plain_gemma2.forward(cfg, tensors, toks, rounding=torch.bfloat16).float() for rid, toks in reqs.items()}}
-
-
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
     out = {}
     for name, (cfg, lengths, page) in CASES.items():
-        for sharp in (False, True):
-            folder = helpers.write_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=21, dtype=torch.bfloat16, sharp=sharp)
-            vocab = helpers.quiet_vocab(cfg) if sharp else cfg["vocab_size"]
+        for draw in ("plain", "loud", "sharp"):
+            folder = helpers.write_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=21, dtype=torch.bfloat16, draw=draw)
+            vocab = cfg["vocab_size"] if draw == "plain" else helpers.quiet_vocab(cfg)
             reqs = {f"r{i}": helpers.random_tokens(n, vocab, 300 + i) for i, n in enumerate(lengths)}
-            ref = _references(cfg, helpers.read_tensors(folder), reqs, sharp)
-            out[(name, sharp)] = (folder, cfg, reqs, ref, page)
-        out[name] = out[(name, False)]
+            tensors = helpers.read_tensors(folder)
+            ref = {rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+            out[(name, draw)] = (folder, cfg, reqs, ref, page)
+        out[name] = out[(name, "plain")]
     return out
 
 
@@ -71,13 +59,12 @@ def _steps(mode, reqs):
             "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=5)}[mode](reqs)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("draw,dtype", DRAWS)
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
-@pytest.mark.parametrize("draw", ["plain", "sharp"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
-def test_modes_match_plain(models, name, draw, mode, dtype):
+def test_modes_match_plain(models, name, mode, draw, dtype):
     from kungfu_b200 import api
-    folder, cfg, reqs, ref, page = models[(name, draw == "sharp")]
+    folder, cfg, reqs, ref, page = models[(name, draw)]
     steps = _steps(mode, reqs)
     c, model = api.load_model(folder, dtype=dtype, device=DEV)
     runner = api.make_runner(c, model, dtype=dtype, device=DEV, page_size=page,
@@ -85,29 +72,28 @@ def test_modes_match_plain(models, name, draw, mode, dtype):
                              max_context=cfg["max_position_embeddings"])
     got = helpers.run_trace_with_runner(runner, steps)
     assert len(got) == sum(len(t) for t in reqs.values())
-    _check(got, ref[dtype], (TOL_SHARP if draw == "sharp" else TOL)[dtype])
+    _check(got, ref, TOL[dtype])
     assert runner.cache.n_live == 0
     if mode == "mixed":                                # the pool is smaller than what the trace hands out: pages came back
         assert all(n > g.pool.n_pages for n, g in zip(runner.cache.pages_handed_out(), runner.cache.groups)), \
             (runner.cache.pages_handed_out(), [g.pool.n_pages for g in runner.cache.groups])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("draw,dtype", DRAWS)
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
-@pytest.mark.parametrize("draw", ["plain", "sharp"])
-def test_fast_kernel_sizes_match_plain(tmp_path_factory, draw, mode, dtype):
+def test_fast_kernel_sizes_match_plain(tmp_path_factory, mode, draw, dtype):
     """Configuration E: sizes at which the tcgen05 products (pairs included), the tcgen05 prompt attention and the
     tensor-core decode attention all run, with pages of 64, prompts longer than the window and than a CTA tile, and a
     pool small enough that pages come back and are used again."""
     from kungfu_b200 import api
     cfg = helpers.TINY_E
-    sharp = draw == "sharp"
     cache = test_fast_kernel_sizes_match_plain.__dict__.setdefault("cache", {})
     if draw not in cache:
-        folder = helpers.write_model(str(tmp_path_factory.mktemp("E") / "m"), cfg, seed=31, dtype=torch.bfloat16, sharp=sharp)
-        vocab = helpers.quiet_vocab(cfg) if sharp else cfg["vocab_size"]
+        folder = helpers.write_model(str(tmp_path_factory.mktemp("E") / "m"), cfg, seed=31, dtype=torch.bfloat16, draw=draw)
+        vocab = cfg["vocab_size"] if draw == "plain" else helpers.quiet_vocab(cfg)
         reqs = {f"r{i}": helpers.random_tokens(n, vocab, 700 + i) for i, n in enumerate([300, 70, 513, 129, 2])}
-        cache[draw] = (folder, reqs, _references(cfg, helpers.read_tensors(folder), reqs, sharp))
+        tensors = helpers.read_tensors(folder)
+        cache[draw] = (folder, reqs, {rid: plain_gemma2.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()})
     folder, reqs, ref = cache[draw]
     steps = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 32),
              "chunks": lambda r: helpers.trace_chunks(r, sizes=(150, 2, 64, 131, 7, 300, 3)),
@@ -117,7 +103,7 @@ def test_fast_kernel_sizes_match_plain(tmp_path_factory, draw, mode, dtype):
                              max_tokens=helpers.trace_max_tokens(steps, 64), max_requests=8, max_context=1024)
     got = helpers.run_trace_with_runner(runner, steps)
     assert len(got) == sum(len(t) for t in reqs.values())
-    _check(got, ref[dtype], (TOL_SHARP if sharp else TOL)[dtype])
+    _check(got, ref, TOL[dtype])
     from kungfu_b200 import ops
     ops.raise_on_device_error()
     if mode == "mixed":
@@ -145,8 +131,7 @@ def test_weights_stored_in_32_bit_stay_so(tmp_path, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(models, tmp_path, dtype):
     """bin/trace_run as a user runs it: steps on standard input, logits files out, `done` after every step."""
-    folder, cfg, reqs, ref, _ = models[("B", True)]
-    ref = ref[dtype]
+    folder, cfg, reqs, ref, _ = models[("B", "sharp" if dtype == "float32" else "loud")]
     steps = helpers.trace_mixed(reqs, seed=9)
     out = tmp_path / "out"
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
@@ -166,7 +151,7 @@ def test_trace_run_program(models, tmp_path, dtype):
                 got[(e["id"], start + w)] = torch.from_numpy(arr[k].copy())
                 k += 1
             fed[e["id"]] = start + len(e["tokens"])
-    _check(got, ref, TOL_SHARP[dtype])
+    _check(got, ref, TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

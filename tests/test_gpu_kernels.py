@@ -632,8 +632,9 @@ def test_random_weights_are_the_same_bits_on_host_and_device(ops, dtype):
 def test_softcap_where_it_bends(ops, path, nh, nkv, d, P, cap, ratio):
     """Every bfloat16 attention kernel with queries scaled so that the largest scores before the cap reach `ratio` caps:
     half a cap (the polynomial branch of the tcgen05 kernel), one cap, and three caps (its exponential branch, and
-    saturation), against float64.  The same reference without the cap is far outside the tolerance, so a kernel that
-    dropped or misplaced the cap would fail here."""
+    saturation), against float64, with a scale that is not 1/sqrt(head size) (Gemma 2 27B: 1/sqrt(144) with heads of
+    128).  The same reference without the cap, or with 1/sqrt(head size), is far outside the tolerance, so a kernel
+    that dropped or misplaced the cap or derived the scale from the head size would fail here."""
     lens = [300, 90, 1] if path.startswith("prefill") or path == "generic" else [300, 2100, 65, 1]
     pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, lens, seed=61)
     if path.startswith("prefill") or path == "generic":
@@ -643,9 +644,9 @@ def test_softcap_where_it_bends(ops, path, nh, nkv, d, P, cap, ratio):
         rows = [(r, n - 1) for r, n in enumerate(lens)]
         dec, pre = list(range(len(rows))), []
     g = torch.Generator().manual_seed(62)
-    scale = 1.0 / math.sqrt(d)
-    # scale * q.k has spread 1 for unit-variance q and k: three spreads reach ratio * cap
-    q = (torch.randn(len(rows), nh, d, generator=g) * (ratio * cap / 3.0)).to(torch.bfloat16)
+    scale = 0.6 / math.sqrt(d)
+    # scale * q.k has spread 0.6 for unit-variance q and k: three spreads reach ratio * cap
+    q = (torch.randn(len(rows), nh, d, generator=g) * (ratio * cap / 1.8)).to(torch.bfloat16)
     ctx = _Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
                torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec, pre)
     out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -662,8 +663,27 @@ def test_softcap_where_it_bends(ops, path, nh, nkv, d, P, cap, ratio):
     pick = list(range(0, len(rows), 5)) + [len(rows) - 1]
     ref = torch.stack([_attn_ref(q[i], ks[rows[i][0]], vs[rows[i][0]], rows[i][1], nh, nkv, scale, cap, None) for i in pick])
     nocap = torch.stack([_attn_ref(q[i], ks[rows[i][0]], vs[rows[i][0]], rows[i][1], nh, nkv, scale, 0.0, None) for i in pick])
+    by_d = torch.stack([_attn_ref(q[i], ks[rows[i][0]], vs[rows[i][0]], rows[i][1], nh, nkv, 1.0 / math.sqrt(d), cap, None) for i in pick])
     got = out.view(len(rows), nh, d)[pick]
     assert bool(torch.isfinite(got.float()).all())
     assert rel_err(got, ref) < 1e-2
     if ratio >= 1.0:
         assert rel_err(nocap, ref) > 0.1, "the case must be one in which the cap matters"
+        assert rel_err(by_d, ref) > 0.1, "and one in which the scale matters"
+
+
+def test_rope_table_far_positions(ops):
+    """cos and sin of position x frequency at positions where the 32-bit product alone is off by 1e-4 rad and more:
+    the table keeps the product's rounding error and stays within 1e-6 of float64."""
+    d, base = 256, 10000.0
+    i = torch.arange(d // 2, dtype=torch.float64)
+    inv = (base ** (-2.0 * i / d)).to(torch.float32)
+    pos = torch.tensor([0, 1, 777, 4095, 4199, 8191, 131071], dtype=torch.int32)
+    cos = torch.empty(len(pos), d // 2, device=DEV)
+    sin = torch.empty(len(pos), d // 2, device=DEV)
+    ops.rope_table(pos.to(DEV), inv.to(DEV), cos, sin)
+    ang = pos.double()[:, None] * inv.double()[None, :]
+    assert float((cos.cpu().double() - torch.cos(ang)).abs().max()) < 1e-6
+    assert float((sin.cpu().double() - torch.sin(ang)).abs().max()) < 1e-6
+    one_product = (pos.float()[:, None] * inv[None, :]).double()           # what a single 32-bit product would give
+    assert float((torch.cos(one_product) - torch.cos(ang)).abs().max()) > 1e-4
