@@ -169,7 +169,7 @@ def test_rope_table(ops):
     cos = torch.empty(5, 24, device=DEV)
     sin = torch.empty(5, 24, device=DEV)
     ops.rope_table(pos, inv, cos, sin)
-    ang = (pos.float()[:, None] * inv[None, :]).double()          # the 32-bit angle is the contract
+    ang = pos.double()[:, None] * inv.double()[None, :]           # 32-bit frequencies, their product with the position exact
     assert float((cos.double() - torch.cos(ang)).abs().max()) < 1e-6
     assert float((sin.double() - torch.sin(ang)).abs().max()) < 1e-6
 
