@@ -175,14 +175,24 @@ def cmd_score(args) -> int:
     head = ids[:prefix]
     chunks = [head[i:i + args.batch] for i in range(0, prefix, args.batch)] + [[t] for t in ids[prefix:]]
     eos = set(getattr(eng.cfg, "eos_token_id", ()) or ())
+    from . import ops
+    if args.topk > 64:
+        raise SystemExit("error: --topk is at most 64 (the candidates the device ranks per row)")
     for chunk in chunks:
         logits = runner.step([StepEntry("score", chunk, list(range(len(chunk))))]).clone()
         if args.ignore_eos and eos:
             logits[:, sorted(eos)] = float("-inf")
+        n = logits.shape[0]
         if args.topk > 0:
-            rows += torch.topk(logits, args.topk, dim=-1).indices.cpu().tolist()
+            ids = torch.empty((n, args.topk), dtype=torch.int32, device=logits.device)
+            vals = torch.empty((n, args.topk), dtype=torch.float32, device=logits.device)
+            lse = torch.empty((n,), dtype=torch.float32, device=logits.device)
+            ops.topk_lse(logits, args.topk, ids, vals, lse)
+            rows += ids.cpu().tolist()
         else:
-            rows += torch.argmax(logits, dim=-1).cpu().tolist()
+            ids = torch.empty((n,), dtype=torch.int32, device=logits.device)
+            ops.argmax(logits, ids)
+            rows += ids.cpu().tolist()
     runner.cache.release("score")
     print(json.dumps({"ids": ids, "predictions": rows}))
     return 0

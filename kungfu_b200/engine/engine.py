@@ -15,7 +15,7 @@ import torch
 
 from .. import events as _events
 from .. import ops
-from ..sampling.sampler import CANDIDATES, Candidates, Sampling, sample, sample_sparse
+from ..sampling.sampler import STATE_WORDS, Sampling, pack_state
 from .scheduler import Portion, Request, Scheduler
 from .step import Runner, StepEntry
 
@@ -39,9 +39,9 @@ class Engine:
         model's trained length); `batch`: most tokens one step runs; `parallel`: most live requests.
         `max_tokens_in_cache`: size of a cache group's pool in tokens (default: parallel * ctx; a windowed group never
         gets more than parallel * (window + batch + page), and all pools are cut to fit the memory left after the weights).
-        `pipeline`: greedy decode steps are launched before the tokens of the step before them have been read (they
-        stay on the device as the next step's input), so `step()` returns a step's tokens one call later and the GPU
-        does not wait for the host between steps."""
+        `pipeline`: decode steps are launched before the tokens of the step before them have been read (tokens are
+        drawn on the device and stay there as the next step's input), so `step()` returns a step's tokens one call
+        later and the GPU does not wait for the host between steps."""
         from .. import api
         self.events = events
         if runner is not None:
@@ -84,9 +84,8 @@ class Engine:
         self._next_id = 0
         self.requests: dict[Hashable, Request] = {}
         self._t_start: dict = {}
-        dev = self.runner.device
-        self._ids_dev = None
-        self._cand_k = CANDIDATES
+        # what the device needs to draw a request's tokens (rules, generator, recent tokens), one block per state slot
+        self._states = torch.zeros((self.runner.cache.max_requests, STATE_WORDS), dtype=torch.int32, device=self.runner.device)
         self.pipeline = bool(pipeline)
         self._inflight = None                  # (requests and their output places, picked ids on the device, fetch)
 
@@ -182,9 +181,8 @@ class Engine:
         plan = self.scheduler.schedule()
         events += [(r.id, None, r.finish_reason) for r in self.scheduler.finished[n_fin:]]
         wanting = [p for p in plan if p.wants_logits]
-        greedy = bool(wanting) and all(p.request.sampling.greedy for p in wanting)
-        # a step of one token per request, all greedy: its tokens can stay on the device for the step after it
-        decode_only = self.pipeline and greedy and len(wanting) == len(plan) and all(p.n == 1 for p in plan)
+        # a step of one token per request: its tokens can stay on the device for the step after it
+        decode_only = self.pipeline and bool(wanting) and len(wanting) == len(plan) and all(p.n == 1 for p in plan)
         feedback = None
         if self._inflight is not None:
             if decode_only and [id(p.request) for p in plan] == [id(r) for r, _ in self._inflight[0]]:
@@ -199,8 +197,10 @@ class Engine:
         for p in plan:
             toks = p.request.slice(p.start, p.n)
             entries.append(StepEntry(p.request.id, toks, [p.n - 1] if p.wants_logits else []))
-        if greedy:                                       # the largest logit is found in the step's own pass
-            logits, picked = self.runner.step(entries, greedy=True, feedback=feedback)
+        if wanting:                                      # tokens are drawn in the step's own pass, on the device
+            self._upload_sampler_states(wanting)
+            whole = any(p.request.sampling.needs_whole_ranking for p in wanting)
+            logits, picked = self.runner.step(entries, sample=(self._states, whole), feedback=feedback)
         else:
             logits, picked = self.runner.step(entries), None
         for p in plan:
@@ -216,7 +216,7 @@ class Engine:
                 events += self._collect(before)
             return events
         if wanting:
-            tokens = picked.cpu().tolist() if picked is not None else self._pick(logits, [p.request for p in wanting])
+            tokens = picked.cpu().tolist()
             for p, tok in zip(wanting, tokens):
                 reason = self.scheduler.on_token(p.request, tok)
                 events.append((p.request.id, tok, reason))
@@ -224,28 +224,24 @@ class Engine:
                     self._request_event(p.request)
         return events
 
-    def _pick(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
-        """One token per row of `logits` under each request's sampling."""
-        n = len(reqs)
-        if all(r.sampling.greedy for r in reqs):
-            out = self.runner.buffers.get("picked_ids", (n,), torch.int32)
-            ops.argmax(logits, out)
-            return out.cpu().tolist()
-        k = min(self._cand_k, logits.shape[1])
-        ids = self.runner.buffers.get("cand_ids", (n, k), torch.int32)
-        vals = self.runner.buffers.get("cand_vals", (n, k), torch.float32)
-        lse = self.runner.buffers.get("cand_lse", (n,), torch.float32)
-        ops.topk_lse(logits, k, ids, vals, lse)
-        ids_h, vals_h, lse_h = ids.cpu().numpy(), vals.cpu().numpy(), lse.cpu().numpy()
-        picked = []
-        for i, r in enumerate(reqs):
-            recent = r.output
-            c = Candidates(ids_h[i], vals_h[i], float(lse_h[i]), logits.shape[1])
-            tok = sample_sparse(c, r.sampling, recent, r.rng)
-            if tok is None:                              # the candidates do not settle it: take the whole row
-                tok = sample(logits[i].cpu().numpy(), r.sampling, recent, r.rng)
-            picked.append(int(tok))
-        return picked
+    def _upload_sampler_states(self, wanting) -> None:
+        """Write the sampler state of every request that is about to draw its first token since it was (re)admitted:
+        its rules, its generator advanced past the draws it has already made, and the tokens it has produced."""
+        for p in wanting:
+            r = p.request
+            if r.sampler_epoch == r.n_preempted:
+                continue
+            st = pack_state(r.sampling, r.seed, recent=r.output)
+            if r.sampling.temperature > 0.0 and r.output:        # after a preemption: one draw per token so far
+                x = max(int(r.seed), 1) & ((1 << 64) - 1)
+                for _ in r.output:
+                    x ^= (x << 13) & ((1 << 64) - 1)
+                    x ^= x >> 7
+                    x ^= (x << 17) & ((1 << 64) - 1)
+                st[0:2] = np.array([x & 0xFFFFFFFF, x >> 32], dtype=np.uint32).view(np.int32)
+            slot = self.runner.cache.state_slot(r.id)
+            self._states[slot].copy_(torch.from_numpy(st))
+            r.sampler_epoch = r.n_preempted
 
     def _request_event(self, r: Request) -> None:
         dt = max(time.time() - self._t_start.get(r.id, time.time()), 1e-9)

@@ -27,7 +27,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Hashable
 
-from ..sampling.sampler import Rng, Sampling
+from ..sampling.sampler import Sampling
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
@@ -47,12 +47,10 @@ class Request:
     n_cached: int = 0                  # tokens of `tokens()` whose keys/values are in the cache
     finish_reason: str | None = None
     n_preempted: int = 0
-    rng: Rng | None = None
+    sampler_epoch: int = -1            # the admission (count of preemptions) for which the device holds its sampler state
 
     def __post_init__(self):
         self.prompt = [int(t) for t in self.prompt]
-        if self.rng is None:
-            self.rng = Rng(self.seed)
 
     def tokens(self) -> list:
         return self.prompt + self.output

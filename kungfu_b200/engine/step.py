@@ -263,17 +263,19 @@ class Runner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry], greedy: bool = False, feedback: torch.Tensor | None = None):
+    def step(self, entries: Sequence[StepEntry], sample=None, feedback: torch.Tensor | None = None):
         """Run the tokens of `entries` as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
         in the order of the entries and of each entry's `want`, or None when nothing is wanted.  The result
         lives in a buffer the next step overwrites.  Raises OutOfPages before touching anything when the
         pages for the new tokens cannot all be had.
-        With `greedy` the index of the largest logit of every wanted row is computed in the same pass (inside the
-        replayed graph for decode steps) and the result is (logits, int32 token ids [wanted]).
+        `sample`: (sampler states [max_requests, STATE_WORDS] int32 on the device, whole_ranking); the token of every
+        wanted row is then drawn in the same pass under its request's rules (inside the replayed graph for decode
+        steps) and the result is (logits, int32 token ids [wanted]).
         `feedback`: for a step in which every entry brings one token, a device tensor with those tokens in the order
-        of the entries (the ids an earlier greedy step picked, which the host has not read yet); the entries' own
-        token values are then ignored."""
+        of the entries (the ids an earlier step drew, which the host has not read yet); the entries' own token values
+        are then ignored."""
         entries = list(entries)
+        greedy = sample is not None
         if not entries:
             return (None, None) if greedy else None
         self.validate(entries)
@@ -295,13 +297,11 @@ class Runner:
                 ctx = self._fill(entries, None, feedback)
                 logits = self._forward(ctx)
                 if greedy and logits is not None:
-                    picked = self._argmax(logits)
-            elif greedy and isinstance(bucket, int):
-                logits, picked = self._step_graphed(entries, ("greedy", bucket), feedback)
+                    picked = self._sample(logits, ctx, sample)
+            elif greedy:
+                logits, picked = self._step_graphed(entries, ("sample", bucket, bool(sample[1])), feedback, sample)
             else:
                 logits = self._step_graphed(entries, bucket, feedback)
-                if greedy and logits is not None:
-                    picked = self._argmax(logits)
         except BaseException:
             for e in entries:                              # nothing was committed: the pages taken for this step go back
                 self.cache.cancel_reservation(e.request)
@@ -333,11 +333,14 @@ class Runner:
             return buf[:n].tolist()
         return wait
 
-    def _argmax(self, logits):
+    def _sample(self, logits, ctx, sample):
+        """Draw the token of every wanted row on the device (ops.sample) from its request's sampler state."""
         from .. import ops
-        out = self.buffers.get("greedy_ids", (logits.shape[0],), torch.int32)
-        ops.argmax(logits, out)
-        return out
+        states, whole = sample
+        out = self.buffers.get("sampled_ids", (max(logits.shape[0], 1),), torch.int32)
+        ops.sample(logits, states, out, logit_rows=ctx.logit_rows, row_req=ctx.row_req, req_slot=ctx.req_state_slot,
+                   whole_ranking=bool(whole))
+        return out[:logits.shape[0]]
 
     # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
     MAX_PORTION_GRAPHS = 8
@@ -355,7 +358,8 @@ class Runner:
             return None
         if len(entries) == 1 and 64 <= len(entries[0].tokens) <= 256:
             key = ("portion", len(entries[0].tokens), len(entries[0].want))
-            if key in self._graphs or sum(1 for k in self._graphs if isinstance(k, tuple) and k[0] == "portion") < self.MAX_PORTION_GRAPHS:
+            held = {k[1] if k[0] == "sample" else k for k in self._graphs if isinstance(k, tuple)}
+            if key in held or sum(1 for k in held if isinstance(k, tuple) and k[0] == "portion") < self.MAX_PORTION_GRAPHS:
                 return key
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
@@ -373,29 +377,31 @@ class Runner:
                 return self.model.forward(ctx)
         return self.model.forward(ctx)
 
-    def _step_graphed(self, entries, key, feedback=None):
+    def _step_graphed(self, entries, key, feedback=None, sample=None):
         """First time a key is seen the step runs eagerly (that also sizes every buffer); the second time the
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
-        pick = isinstance(key, tuple) and key[0] == "greedy"   # a decode bucket whose graph also holds the argmax
-        if pick:
-            n, bucket = len(entries), key[1]
-        elif isinstance(key, tuple):                       # one portion of one prompt: the entries as they are, fixed layout
-            n, bucket = key[2], -1
+        pick = isinstance(key, tuple) and key[0] == "sample"   # a graph that also holds the draw of the tokens
+        shape = key[1] if pick else key
+        if isinstance(shape, tuple):                       # one portion of one prompt: the entries as they are, fixed layout
+            n, bucket = shape[2], -1
         else:
-            n, bucket = len(entries), key
+            n, bucket = len(entries), shape
         state = self._graphs.get(key)
         if state is not None and state["generation"] != self.buffers.generation:
             state = None                                   # a buffer moved: the old graph points at freed memory
             self._graphs.pop(key)
+        if state is not None and pick and state.get("states_ptr") != sample[0].data_ptr():
+            state = None                                   # another engine's sampler states
+            self._graphs.pop(key)
 
         def result(logits, picked=None):
             out = None if (logits is None or n == 0) else logits[:n]
-            return (out, picked[:n]) if pick else out
+            return (out, None if picked is None else picked[:n]) if pick else out
 
         def run(ctx):
             logits = self._forward(ctx)
-            return (logits, self._argmax(logits)) if pick else (logits, None)
+            return (logits, self._sample(logits, ctx, sample)) if (pick and logits is not None) else (logits, None)
 
         if state is not None and state["graph"] is not None:
             self._build_block(entries, bucket, feedback)  # same layout as at capture; a replay needs no context object
@@ -404,7 +410,8 @@ class Runner:
             return result(state["logits"], state["picked"])
         ctx = self._fill(entries, bucket, feedback)
         if state is None:
-            self._graphs[key] = {"generation": None, "graph": None, "seen": 1}
+            self._graphs[key] = {"generation": None, "graph": None, "seen": 1,
+                                 "states_ptr": sample[0].data_ptr() if pick else None}
             logits, picked = run(ctx)
             self._graphs[key]["generation"] = self.buffers.generation
             return result(logits, picked)

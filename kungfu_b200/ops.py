@@ -467,11 +467,59 @@ def argmax(logits, out) -> None:
     _check(library().kf_argmax(_p(logits), _p(out), rows, V, _p(sc["argmax"]), _stream()), "argmax")
 
 
+def _sample_scratch(device, rows: int, V: int, full: bool) -> dict:
+    lib = library()
+    sc = _dev_scratch(device)
+    n_slices = lib.kf_sample_slices(V)
+    need = rows * n_slices
+    if sc.get("sample_rows", 0) < need:
+        for k in ("sample_keys", "sample_stats", "sample_flags"):
+            if k in sc:
+                sc["retired"].append(sc[k])
+        cap = max(need, 64 * n_slices)
+        sc["sample_keys"] = torch.empty(cap * 64, dtype=torch.int64, device=device)
+        sc["sample_stats"] = torch.empty(cap * 2, dtype=torch.float32, device=device)
+        sc["sample_flags"] = torch.zeros(max(rows, 64) * 2, dtype=torch.int32, device=device)
+        sc["sample_rows"] = cap
+    if sc["sample_flags"].numel() < rows:
+        sc["retired"].append(sc["sample_flags"])
+        sc["sample_flags"] = torch.zeros(rows * 2, dtype=torch.int32, device=device)
+    if full and sc.get("sample_pen_n", 0) < rows * V:
+        if "sample_pen" in sc:
+            sc["retired"].append(sc["sample_pen"])
+        sc["sample_pen"] = torch.empty(rows * V, dtype=torch.float32, device=device)
+        sc["sample_pen_n"] = rows * V
+    return sc
+
+
+@_dispatch("sample")
+def sample(logits, states, out_ids, *, logit_rows=None, row_req=None, req_slot=None, whole_ranking: bool = False,
+           cand_ids=None, cand_vals=None, cand_lse=None) -> None:
+    """The end of a step, on the device: out_ids[i] = the token row i of `logits` yields under the rules, generator and
+    recent tokens of its request's state (`states` [requests, STATE_WORDS] int32, see sampling/sampler.py), which the
+    kernels update.  The request of row i is req_slot[row_req[logit_rows[i]]] (each map None for the identity; rows of
+    a negative request are skipped).  `whole_ranking`: some request's rules reach below the 64th candidate (top_k of 0
+    or above 64 at a temperature above 0); one more kernel then runs.  cand_*: also write the ranked candidates."""
+    rows, V = logits.shape
+    sc = _sample_scratch(logits.device, rows, V, whole_ranking)
+    k = 0 if cand_ids is None else cand_ids.shape[1]
+    _check(library().kf_sample(_p(logits), rows, V, _p(sc["sample_keys"]), _p(sc["sample_stats"]), _p(cand_ids), _p(cand_vals),
+                               _p(cand_lse), k, _p(logit_rows), _p(row_req), _p(req_slot), _p(states), _p(out_ids),
+                               _p(sc["sample_flags"]), _p(sc["sample_pen"]) if whole_ranking else None,
+                               int(whole_ranking), _stream()), "sample")
+    add_launches(2 if whole_ranking else 1)
+
+
 @_dispatch("topk_lse")
 def topk_lse(logits, k: int, out_ids, out_vals, out_lse) -> None:
-    """Top-k ids (falling value, lower id first among equals), their values, and the row's log-sum-exp."""
+    """Top-k ids (falling value, lower id first among equals), their values, and the row's log-sum-exp; k <= 64."""
     rows, V = logits.shape
-    _check(library().kf_topk_lse(_p(logits), _p(out_ids), _p(out_vals), _p(out_lse), rows, V, k, _stream()), "topk_lse")
+    if k < 1 or k > 64 or k > V:
+        raise KernelError(f"topk_lse: k = {k} is not in 1..min(64, {V})")
+    sc = _sample_scratch(logits.device, rows, V, False)
+    _check(library().kf_sample(_p(logits), rows, V, _p(sc["sample_keys"]), _p(sc["sample_stats"]), _p(out_ids), _p(out_vals),
+                               _p(out_lse), k, None, None, None, None, None, None, None, 0, _stream()), "topk_lse")
+    add_launches(1)
 
 
 def device_arch() -> int:

@@ -1,1 +1,1 @@
-from .sampler import CANDIDATES, Candidates, Rng, Sampling, argmax, draw, sample, sample_sparse
+from .sampler import CANDIDATES, RING, STATE_WORDS, Sampling, generator_state, pack_state

@@ -114,6 +114,34 @@ class CpuOps:
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(torch.int32))
 
+    def sample(self, logits, states, out_ids, *, logit_rows=None, row_req=None, req_slot=None, whole_ranking=False,
+               cand_ids=None, cand_vals=None, cand_lse=None):
+        """The device sampler's stand-in: the plain sampler of tests/plain_sampler.py on each row, reading and updating
+        the per-request state words as the kernels do."""
+        import numpy as np
+        import plain_sampler
+        from kungfu_b200.sampling import RING, generator_state
+        st_all = states.numpy()
+        for i in range(logits.shape[0]):
+            lr = i if logit_rows is None else int(logit_rows[i])
+            rq = 0 if row_req is None else int(row_req[lr])
+            if rq < 0:
+                out_ids[i] = 0
+                continue
+            st = st_all[rq if req_slot is None else int(req_slot[rq])]
+            f = st[2:6].view(np.float32)
+            count = int(st[8])
+            recent = [int(st[16 + j % RING]) for j in range(max(0, count - RING), count)]
+            rng = plain_sampler.Rng(1)
+            rng.state = generator_state(st)
+            tok, _ = plain_sampler.sample(logits[i].float().numpy(), temperature=float(f[0]), top_k=int(st[6]), top_p=float(f[1]),
+                                          min_p=float(f[2]), repeat_penalty=float(f[3]), repeat_window=int(st[7]),
+                                          recent=recent, rng=rng)
+            st[0:2] = np.array([rng.state & 0xFFFFFFFF, rng.state >> 32], dtype=np.uint32).view(np.int32)
+            st[16 + count % RING] = tok
+            st[8] = count + 1
+            out_ids[i] = tok
+
     def topk_lse(self, logits, k, out_ids, out_vals, out_lse):
         V = logits.shape[1]
         # falling value, lower id first among equals

@@ -78,6 +78,38 @@ def test_generate_matches_plain_greedy_and_survives_preemption(tmp_path, cpu_ops
     assert tight.runner.cache.n_live == 0 and tight.runner.cache.free_pages() == [9, 9]
 
 
+def _plain_generate(cfg_dict, tensors, prompt, n_new, rules, seed):
+    """Token by token with the plain model and the plain sampler (whole sequence recomputed each step)."""
+    import plain_sampler
+    rng = plain_sampler.Rng(seed)
+    out = []
+    for _ in range(n_new):
+        row = plain_gemma2.forward(cfg_dict, tensors, list(prompt) + out)[-1].float().numpy()
+        tok, _margin = plain_sampler.sample(row, recent=out, rng=rng, **rules)
+        out.append(tok)
+    return out
+
+
+def test_sampled_tokens_equal_the_plain_sampler_on_plain_logits_and_survive_preemption(tmp_path, cpu_ops):
+    """Temperature, top-k beyond and within the candidates, top-p and a repeat penalty through the scheduler: the ids
+    are those of the plain sampler applied to the plain model's logits with the same seed, request by request, with
+    and without the pipeline, and also when a request is preempted and recomputed (its generator goes on where it was)."""
+    from kungfu_b200.sampling import Sampling
+    cfg_dict = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=4, dtype=torch.float32)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg_dict["vocab_size"], 90 + n) for n in (5, 7, 6)]
+    for rules in (dict(temperature=0.8, top_k=0, top_p=1.0), dict(temperature=1.1, top_k=40, top_p=0.9, repeat_penalty=1.3),
+                  dict(temperature=0.0, repeat_penalty=1.5, repeat_window=4)):
+        want = [_plain_generate(cfg_dict, tensors, p, 8, rules, seed=9 + i) for i, p in enumerate(prompts)]
+        for pipeline in (True, False):
+            roomy = _engine(folder, cfg_dict, page=4, pool_tokens=256, batch=16, parallel=4, pipeline=pipeline)
+            assert roomy.generate(prompts, Sampling(**rules), max_tokens=8, seed=9) == want, (rules, pipeline)
+        tight = _engine(folder, cfg_dict, page=4, pool_tokens=36, batch=16, parallel=4)
+        assert tight.generate(prompts, Sampling(**rules), max_tokens=8, seed=9) == want, rules
+        assert tight.scheduler.n_preemptions > 0
+
+
 def test_tokens_read_one_step_late_end_requests_where_they_should(tmp_path, cpu_ops):
     """Greedy decode steps are launched before the step before them has been read.  A request that an end-of-sequence id
     ends has then run one step too many: its output must still end with that id, with reason eos, the others go on to

@@ -687,3 +687,86 @@ def test_rope_table_far_positions(ops):
     assert float((sin.cpu().double() - torch.sin(ang)).abs().max()) < 1e-6
     one_product = (pos.float()[:, None] * inv[None, :]).double()           # what a single 32-bit product would give
     assert float((torch.cos(one_product) - torch.cos(ang)).abs().max()) > 1e-4
+
+
+def _device_sample(ops, logits, rules, seeds, recents, whole):
+    """Rows of `logits` through ops.sample, row i under rules[i]; returns ids, states after, candidates."""
+    import numpy as np
+    from kungfu_b200.sampling import Sampling, pack_state
+    n = logits.shape[0]
+    st = np.stack([pack_state(Sampling(**rules[i]), seeds[i], recents[i]) for i in range(n)])
+    states = torch.from_numpy(st).to(DEV)
+    out = torch.full((n,), -7, dtype=torch.int32, device=DEV)
+    # a permutation between rows and state slots, as a step has it
+    slot_of = torch.arange(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, states, out, logit_rows=torch.arange(n, dtype=torch.int32, device=DEV), row_req=slot_of, req_slot=slot_of,
+               whole_ranking=whole)
+    return out.cpu().tolist(), states.cpu().numpy()
+
+
+@pytest.mark.parametrize("V", [300, 5000, 70001])
+def test_device_sampler_equals_the_plain_sampler(ops, V):
+    """400 fuzzed rows per vocabulary size: every combination of temperature, top-k (within and beyond the 64
+    candidates, and none), top-p, min-p and repeat penalty, logits with many equal values, tokens repeated in the window.
+    The token, the generator state after the draw and the recorded token equal the plain sampler's
+    (the reference checks its two samplers against each other the same way, crates/kf-engine/src/sampler.rs:229-321).
+    Where the drawn number lies within 1e-5 of the kept mass from the edge of a token's share, the neighbouring token
+    is accepted too: the device's exponential and numpy's may differ in the last bit."""
+    import numpy as np
+    import plain_sampler
+    from kungfu_b200.sampling import RING, generator_state
+    g = np.random.default_rng(V)
+    rows_per_round, rounds = 8, 50
+    exact = close = 0
+    for rnd in range(rounds):
+        l = (g.normal(size=(rows_per_round, V)) * g.choice([1.0, 3.0, 8.0])).astype(np.float32)
+        if rnd % 3 == 0:
+            l = np.round(l * 2) / 2                          # many equal values: the lower id ranks first
+        if rnd % 7 == 0:
+            l = np.clip(l, -2.0, 2.0)                       # hundreds of tokens share the maximum
+        rules, seeds, recents = [], [], []
+        for i in range(rows_per_round):
+            rules.append(dict(temperature=float(g.choice([0.0, 0.7, 1.3])), top_k=int(g.choice([0, 1, 40, 64, 100, V])),
+                              top_p=float(g.choice([1.0, 0.9, 0.5])), min_p=float(g.choice([0.0, 0.1])),
+                              repeat_penalty=float(g.choice([1.0, 1.3, 0.8])), repeat_window=int(g.choice([0, 5, 64, 256]))))
+            seeds.append(int(g.integers(0, 2 ** 62)))
+            n_recent = int(g.choice([0, 3, 70, 300]))
+            top = np.argsort(-l[i])[:5]
+            recents.append([int(t) for t in g.choice(np.concatenate([top, g.integers(0, V, size=20)]), size=n_recent)])
+        whole = any(r["temperature"] > 0 and (r["top_k"] == 0 or r["top_k"] > 64) for r in rules)
+        got, states = _device_sample(ops, torch.from_numpy(l).to(DEV), rules, seeds, recents, whole)
+        for i in range(rows_per_round):
+            rng = plain_sampler.Rng(seeds[i])
+            want, margin = plain_sampler.sample(l[i], recent=recents[i], rng=rng, **rules[i])
+            assert generator_state(states[i]) == rng.state, (rnd, i, rules[i])
+            assert states[i][8] == len(recents[i]) + 1 and states[i][16 + len(recents[i]) % RING] == got[i]
+            if got[i] == want:
+                exact += 1
+                continue
+            assert margin is not None and margin < 1e-5, (rnd, i, rules[i], got[i], want, margin)
+            close += 1
+    ops.raise_on_device_error()
+    assert exact + close == rows_per_round * rounds and close <= 2, (exact, close)
+
+
+def test_device_sampler_skips_padding_rows_and_follows_the_maps(ops):
+    """Rows reach their request's state through logit_rows -> row_req -> req_slot; a row of request -1 (padding of a
+    replayed graph) is skipped and touches no state."""
+    import numpy as np
+    import plain_sampler
+    from kungfu_b200.sampling import Sampling, pack_state
+    g = np.random.default_rng(1)
+    V = 1000
+    l = torch.from_numpy(g.normal(size=(3, V)).astype(np.float32) * 4).to(DEV)
+    st = np.stack([pack_state(Sampling(temperature=1.0, top_k=40, top_p=1.0), 100 + s) for s in range(5)])
+    states = torch.from_numpy(st).to(DEV)
+    out = torch.full((3,), -7, dtype=torch.int32, device=DEV)
+    logit_rows = torch.tensor([4, 0, 2], dtype=torch.int32, device=DEV)          # rows of the step whose logits these are
+    row_req = torch.tensor([1, 9, -1, 9, 0], dtype=torch.int32, device=DEV)      # request of each row of the step
+    req_slot = torch.tensor([3, 2], dtype=torch.int32, device=DEV)               # state slot of each request
+    ops.sample(l, states, out, logit_rows=logit_rows, row_req=row_req, req_slot=req_slot)
+    after = states.cpu().numpy()
+    want0, _ = plain_sampler.sample(l[0].cpu().numpy(), temperature=1.0, top_k=40, rng=plain_sampler.Rng(103))
+    want1, _ = plain_sampler.sample(l[1].cpu().numpy(), temperature=1.0, top_k=40, rng=plain_sampler.Rng(102))
+    assert out.cpu().tolist() == [want0, want1, 0]
+    assert after[3][8] == 1 and after[2][8] == 1 and (after[[0, 1, 4]] == st[[0, 1, 4]]).all()

@@ -177,6 +177,18 @@ def test_generate_through_the_entry_point(tmp_path, name):
         assert e.generate(prompts, Sampling(temperature=0.0), max_tokens=20, eos=[eos]) == cut
         assert [e.finish_reason(i) for i in range(len(prompts))] == ["eos" if eos in seq else "length" for seq in long]
         assert e.runner.cache.n_live == 0 and e.idle
+    # temperature sampling in 32-bit: the ids of the plain sampler applied to the plain model's logits, same seeds
+    import plain_sampler
+    for rules in (dict(temperature=0.8, top_k=0, top_p=1.0), dict(temperature=1.2, top_k=40, top_p=0.9, repeat_penalty=1.3)):
+        want_s = []
+        for i, p in enumerate(prompts):
+            rng, out = plain_sampler.Rng(5 + i), []
+            for _ in range(10):
+                row = pg.forward(cfg, tensors, p + out)[-1].float().numpy()
+                out.append(plain_sampler.sample(row, recent=out, rng=rng, **rules)[0])
+            want_s.append(out)
+        e = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], parallel=4, page_size=8)
+        assert e.generate(prompts, Sampling(**rules), max_tokens=10, seed=5) == want_s, rules
     # temperature sampling with a fixed seed is reproducible and differs between seeds
     s = Sampling(temperature=0.8, top_k=0, top_p=1.0)
     a = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], parallel=4, page_size=8).generate(prompts, s, max_tokens=12, seed=5)
