@@ -110,6 +110,7 @@ KF_API int kf_argmax(const float* logits, int* out, int rows, int V, float* scra
 
 // ---- keys ------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned long long kf_key(float v, unsigned id) {
+  if (v == 0.f) v = 0.f;                                 // -0 and +0 are one value: the lower id ranks first among them
   return ((unsigned long long)kf_orderable(v) << 32) | (unsigned long long)(0xFFFFFFFFu - id);
 }
 __device__ __forceinline__ float kf_key_value(unsigned long long key) {
