@@ -68,9 +68,9 @@ def host_library():
             getattr(lib, name).argtypes = [ctypes.c_void_p, i64] + extra
         lib.kf_cache_table.argtypes = [ctypes.c_void_p, ctypes.c_int, i64, ctypes.c_void_p, ctypes.c_int]
         lib.kf_step_layout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-                                       ctypes.c_int, ctypes.c_void_p]
-        lib.kf_step_fill.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_void_p,
-                                                                                               ctypes.c_void_p]
+                                       ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.kf_step_fill.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p,
+                                                                                                   ctypes.c_void_p]
         vp, ci = ctypes.c_void_p, ctypes.c_int
         lib.kf_sched_create.restype = vp
         lib.kf_sched_create.argtypes = [vp, ci, ci]

@@ -43,7 +43,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int tile = blockIdx.x, h = blockIdx.y;
   const int row0 = tile_row0[tile], nrows = tile_nrows[tile];
   const int req = row_req[row0];
-  if (req < 0) return;
+  if (req < 0 || nrows <= 0) return;                          // padding, or a tile without rows
   const int kvh = h / (nh / nkv);
   const int pos0 = positions[row0];                               // rows of a request are consecutive positions
   const int pos_last = pos0 + nrows - 1;

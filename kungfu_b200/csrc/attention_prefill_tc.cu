@@ -181,7 +181,7 @@ __device__ __forceinline__ int tile_key_tiles(int row0, int nrows, const int* po
   const int pos0 = positions[row0];
   const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   *kt_first = (lo / BKV) * BKV;
-  return row_req[row0] < 0 ? 0 : (pos0 + nrows - 1 - *kt_first) / BKV + 1;
+  return (row_req[row0] < 0 || nrows <= 0) ? 0 : (pos0 + nrows - 1 - *kt_first) / BKV + 1;   // padding, or a tile without rows
 }
 __device__ __forceinline__ int tile_runs(int n_key_tiles, int n_parts, int run_tiles) {
   if (n_parts <= 1) return 1;

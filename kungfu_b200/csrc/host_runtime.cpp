@@ -268,36 +268,52 @@ KF_HOST_API int kf_cache_check(void* h) {
 // Sections, each starting on a 16-byte boundary, in this order (n = ints):
 //   tokens T | positions T | row_req T | logit_rows max(n_out,1) | dec_rows T | pre_rows T | tile_row0, tile_nrows
 //   (T/64 + B + 1 each) | wide_row0, wide_nrows (T/128 + B + 1 each) | req_row_start, req_n_rows, req_kv_len,
-//   req_state_slot (B each) | one block table [B][width] per group.
+//   req_state_slot (B each) | logit_req max(n_out,1): the request whose logits row i of the output is, -1 for none |
+//   one block table [B][width] per group.
 // `info` receives: [0] total ints, [1] T, [2] B, [3] n_out, [4] width, [5] n_dec, [6] n_pre, [7] n_tiles, [8] n_wide,
-// [9] max_kv, [10] max rows of a request, then the offset of every section in the order above (14 + n_groups).
-// With bucket > 0 the layout is that of `bucket` single-row requests with full-width tables; rows beyond the real
-// entries are padding (request -1).  With bucket < 0 the entries are laid out as they are but with full-width tables
-// and the longest context as max_kv, so that the layout depends only on the entries' token and wanted counts (steps of
-// the same shape can then be replayed from one CUDA graph).
+// [9] max_kv, [10] max rows of a request, then the offset of every section in the order above (15 + n_groups).
+// Layouts (steps of one layout can be replayed from one CUDA graph, because nothing but the block's contents changes):
+//   bucket = 0, pre = 0   the entries as they are, tables as wide as the longest request needs;
+//   bucket > 0, pre = 0   `bucket` single-row requests with full-width tables; rows beyond the real entries are padding
+//                         (request -1) that every kernel skips;
+//   bucket < 0, pre = 0   the entries as they are but with full-width tables and the longest context as max_kv;
+//   pre > 0               a mixed step: `bucket` (>= 0) rows of single-token requests first, then `pre` rows for up to
+//                         `pre_reqs` prompt portions; entries must come in that order; every count a kernel is launched
+//                         with (rows, requests, tiles, wanted rows) is the bucket's, unused rows are padding, unused
+//                         tiles have no rows, and a portion has one output row (its last row if wanted).
 enum { SEC_TOKENS, SEC_POSITIONS, SEC_ROW_REQ, SEC_LOGIT_ROWS, SEC_DEC_ROWS, SEC_PRE_ROWS, SEC_TILE_ROW0, SEC_TILE_NROWS,
-       SEC_WIDE_ROW0, SEC_WIDE_NROWS, SEC_REQ_ROW_START, SEC_REQ_N_ROWS, SEC_REQ_KV_LEN, SEC_REQ_STATE_SLOT, SEC_TABLE0 };
+       SEC_WIDE_ROW0, SEC_WIDE_NROWS, SEC_REQ_ROW_START, SEC_REQ_N_ROWS, SEC_REQ_KV_LEN, SEC_REQ_STATE_SLOT, SEC_LOGIT_REQ,
+       SEC_TABLE0 };
 constexpr int INFO_FIXED = 11;
 
 // Size of the block for a step, so that the caller can provide the buffer: returns total ints, fills info[0..].
 KF_HOST_API int kf_step_layout(void* h, int n_entries, const int64_t* reqs, const int* n_tokens, const int* n_want, int bucket,
-                               int* info) {
+                               int pre, int pre_reqs, int* info) {
   Cache* c = (Cache*)h;
   const int G = (int)c->groups.size();
   int T = 0, n_out = 0, width = 1;
+  int n_single = 0, n_multi = 0, multi_rows = 0;
+  bool ordered = true;
   for (int e = 0; e < n_entries; ++e) {
     T += n_tokens[e];
     n_out += n_want[e];
     auto it = c->reqs.find(reqs[e]);
     if (it == c->reqs.end()) return -E_NOT_LIVE;
     width = std::max(width, ceil_div(it->second.length + n_tokens[e], c->page_size));
+    if (n_tokens[e] == 1) { ++n_single; if (n_multi > 0) ordered = false; }
+    else { ++n_multi; multi_rows += n_tokens[e]; }
   }
   int B = n_entries;
-  if (bucket > 0) { T = B = n_out = bucket; width = c->max_pages; }
-  if (bucket < 0) width = c->max_pages;
+  if (pre > 0) {
+    if (!ordered || bucket < 0 || n_single > bucket || multi_rows > pre || n_multi > pre_reqs) return -E_INCONSISTENT;
+    T = bucket + pre; B = bucket + pre_reqs; n_out = B; width = c->max_pages;
+  } else {
+    if (bucket > 0) { T = B = n_out = bucket; width = c->max_pages; }
+    if (bucket < 0) width = c->max_pages;
+  }
   width = align4(width);
   const int sizes[SEC_TABLE0] = {T, T, T, std::max(n_out, 1), T, T, T / 64 + B + 1, T / 64 + B + 1, T / 128 + B + 1,
-                                 T / 128 + B + 1, B, B, B, B};
+                                 T / 128 + B + 1, B, B, B, B, std::max(n_out, 1)};
   int o = 0;
   for (int s = 0; s < SEC_TABLE0; ++s) { info[INFO_FIXED + s] = o; o += align4(sizes[s]); }
   for (int g = 0; g < G; ++g) { info[INFO_FIXED + SEC_TABLE0 + g] = o; o += align4(B * width); }
@@ -307,36 +323,49 @@ KF_HOST_API int kf_step_layout(void* h, int n_entries, const int64_t* reqs, cons
 
 // Fill `block` (info from kf_step_layout).  tokens / wants are the entries' lists laid end to end.
 KF_HOST_API int kf_step_fill(void* h, int n_entries, const int64_t* reqs, const int* n_tokens, const int* tokens,
-                             const int* n_want, const int* wants, int bucket, int* info, int* block) {
+                             const int* n_want, const int* wants, int bucket, int pre, int pre_reqs, int* info, int* block) {
   Cache* c = (Cache*)h;
   const int G = (int)c->groups.size();
   const int total = info[0], T = info[1], B = info[2], width = info[4];
   const int* off = info + INFO_FIXED;
   memset(block, 0, (size_t)total * sizeof(int));
-  if (bucket > 0) {
-    for (int t = n_entries; t < T; ++t) block[off[SEC_ROW_REQ] + t] = -1;
+  const bool mixed = pre > 0;
+  if (bucket > 0 || mixed) {
+    for (int t = 0; t < T; ++t) block[off[SEC_ROW_REQ] + t] = -1;              // real rows are overwritten below
   }
+  for (int i = 0; i < std::max(info[3], 1); ++i) block[off[SEC_LOGIT_REQ] + i] = -1;
   for (int g = 0; g < G; ++g) std::fill(block + off[SEC_TABLE0 + g], block + off[SEC_TABLE0 + g] + (size_t)B * width, -1);
   int r = 0, k = 0, tok_at = 0, want_at = 0, n_dec = 0, n_pre = 0, n_tiles = 0, n_wide = 0, max_kv = 0, max_rows = 0;
+  int n_single = 0, n_multi = 0;
   for (int e = 0; e < n_entries; ++e) {
     auto it = c->reqs.find(reqs[e]);
     if (it == c->reqs.end()) return E_NOT_LIVE;
     const Request& rq = it->second;
     const int n = n_tokens[e], start = rq.length;
+    int ri = e;                                                               // the entry's request index in the block
+    if (mixed) {
+      if (n == 1) { ri = n_single; r = n_single; ++n_single; }
+      else { ri = bucket + n_multi; if (n_multi == 0) r = bucket; ++n_multi; }
+    }
     for (int i = 0; i < n; ++i) {
       block[off[SEC_TOKENS] + r + i] = tokens[tok_at + i];
       block[off[SEC_POSITIONS] + r + i] = start + i;
-      block[off[SEC_ROW_REQ] + r + i] = e;
+      block[off[SEC_ROW_REQ] + r + i] = ri;
     }
     tok_at += n;
-    block[off[SEC_REQ_ROW_START] + e] = r;
-    block[off[SEC_REQ_N_ROWS] + e] = n;
-    block[off[SEC_REQ_KV_LEN] + e] = start + n;
-    block[off[SEC_REQ_STATE_SLOT] + e] = rq.slot;
-    for (int i = 0; i < n_want[e]; ++i) block[off[SEC_LOGIT_ROWS] + k++] = r + wants[want_at + i];
+    block[off[SEC_REQ_ROW_START] + ri] = r;
+    block[off[SEC_REQ_N_ROWS] + ri] = n;
+    block[off[SEC_REQ_KV_LEN] + ri] = start + n;
+    block[off[SEC_REQ_STATE_SLOT] + ri] = rq.slot;
+    if (mixed) {                                                              // one output row per request slot of the bucket
+      if (n_want[e] > 1 || (n_want[e] == 1 && wants[want_at] != n - 1)) return E_INCONSISTENT;
+      if (n_want[e] == 1) { block[off[SEC_LOGIT_ROWS] + ri] = r + n - 1; block[off[SEC_LOGIT_REQ] + ri] = ri; }
+    } else {
+      for (int i = 0; i < n_want[e]; ++i) { block[off[SEC_LOGIT_ROWS] + k] = r + wants[want_at + i]; block[off[SEC_LOGIT_REQ] + k++] = ri; }
+    }
     want_at += n_want[e];
     for (int g = 0; g < G; ++g)
-      memcpy(block + off[SEC_TABLE0 + g] + (size_t)e * width, c->row(g, rq.slot), (size_t)std::min(width, c->width) * sizeof(int));
+      memcpy(block + off[SEC_TABLE0 + g] + (size_t)ri * width, c->row(g, rq.slot), (size_t)std::min(width, c->width) * sizeof(int));
     max_rows = std::max(max_rows, n);
     max_kv = std::max(max_kv, start + n);
     if (n == 1) {
@@ -354,7 +383,7 @@ KF_HOST_API int kf_step_fill(void* h, int n_entries, const int64_t* reqs, const 
     }
     r += n;
   }
-  if (bucket > 0) {                                       // every row of the bucket is a decode row that wants its logits
+  if (bucket > 0 && !mixed) {                             // every row of the bucket is a decode row that wants its logits
     n_dec = bucket;
     for (int t = 0; t < bucket; ++t) {
       block[off[SEC_DEC_ROWS] + t] = t;
@@ -362,7 +391,19 @@ KF_HOST_API int kf_step_fill(void* h, int n_entries, const int64_t* reqs, const 
     }
     max_kv = c->max_context;                              // a captured graph's split plan must not depend on the step
   }
-  if (bucket < 0) max_kv = c->max_context;
+  if (mixed) {
+    // counts are the bucket's: decode rows 0..bucket-1, prompt rows bucket..T-1, and as many tiles as `pre` rows in
+    // `pre_reqs` portions can ever make; tiles beyond the real ones have no rows (their first row is the first prompt row)
+    for (int t = 0; t < bucket; ++t) block[off[SEC_DEC_ROWS] + t] = t;
+    for (int t = 0; t < pre; ++t) block[off[SEC_PRE_ROWS] + t] = bucket + t;
+    const int tiles_fixed = pre / 64 + pre_reqs, wide_fixed = pre / 128 + pre_reqs;
+    for (int t = n_tiles; t < tiles_fixed; ++t) { block[off[SEC_TILE_ROW0] + t] = bucket; block[off[SEC_TILE_NROWS] + t] = 0; }
+    for (int t = n_wide; t < wide_fixed; ++t) { block[off[SEC_WIDE_ROW0] + t] = bucket; block[off[SEC_WIDE_NROWS] + t] = 0; }
+    n_dec = bucket; n_pre = pre; n_tiles = tiles_fixed; n_wide = wide_fixed;
+    max_kv = c->max_context;
+    max_rows = std::max(max_rows, 2);
+  }
+  if (bucket < 0 && !mixed) max_kv = c->max_context;
   info[5] = n_dec; info[6] = n_pre; info[7] = n_tiles; info[8] = n_wide; info[9] = max_kv; info[10] = max_rows;
   return OK;
 }

@@ -216,7 +216,8 @@ class Engine:
                 events += self._collect(before)
             return events
         if wanting:
-            tokens = picked.cpu().tolist()
+            drawn = picked.cpu().tolist()
+            tokens = [drawn[i] for i in self.runner.last_logit_index]
             for p, tok in zip(wanting, tokens):
                 reason = self.scheduler.on_token(p.request, tok)
                 events.append((p.request.id, tok, reason))

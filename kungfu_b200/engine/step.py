@@ -85,7 +85,7 @@ class StepContext:
         self.wide_row0 = self.wide_nrows = None   # the same rows cut into tiles of up to 128
         self.n_wide = 0
         # device views, set by Runner._fill
-        self.tokens = self.positions = self.row_req = self.logit_rows = None
+        self.tokens = self.positions = self.row_req = self.logit_rows = self.logit_req = None
         self.req_row_start = self.req_n_rows = self.req_kv_len = self.req_state_slot = None
         self.block_tables: list[torch.Tensor] = []
         self.streams: dict[str, torch.Tensor] = {}    # extra per-row integers that parts declared (device int32 [rows])
@@ -114,6 +114,7 @@ class Runner:
         self._meta_dev: torch.Tensor | None = None
         self.steps_run = 0
         self.last_meta_ints = 0
+        self.last_logit_index: list[int] = []             # where in the last step's logits each wanted place stands
         self.cuda_graphs = False
         self._graphs: dict = {}
         self._graph_safe = model.all_graph_safe() if hasattr(model, "all_graph_safe") else False
@@ -139,7 +140,7 @@ class Runner:
         return slot, self._meta_dev
 
     _SECTIONS = ("tokens", "positions", "row_req", "logit_rows", "dec_rows", "pre_rows", "tile_row0", "tile_nrows",
-                 "wide_row0", "wide_nrows", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot")
+                 "wide_row0", "wide_nrows", "req_row_start", "req_n_rows", "req_kv_len", "req_state_slot", "logit_req")
 
     def _build_block(self, entries: Sequence[StepEntry], bucket: int | None, feedback: torch.Tensor | None = None):
         """The step's integer block, built by the native host runtime (`kf_step_layout` / `kf_step_fill` in
@@ -155,16 +156,18 @@ class Runner:
         reqs = np.fromiter((cache.key_of(e.request) for e in entries), dtype=np.int64, count=n)
         n_tokens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=n)
         n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n)
-        if (bucket is not None and bucket > 0) or int(n_tokens.max(initial=0)) == 1:
+        mixed = isinstance(bucket, tuple)                  # ("mixed", decode rows, prompt rows, prompt portions)
+        b, pre, pre_reqs = (int(bucket[1]), int(bucket[2]), int(bucket[3])) if mixed else (int(bucket or 0), 0, 0)
+        if (not mixed and b > 0) or int(n_tokens.max(initial=0)) == 1:
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
         else:
             tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]) if n else np.zeros(0, np.int32)
         wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(n_want.sum()))
         info = np.zeros(32 + len(cache.groups), dtype=np.int32)
-        b = int(bucket or 0)
-        total = lib.kf_step_layout(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, n_want.ctypes.data, b, info.ctypes.data)
+        total = lib.kf_step_layout(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, n_want.ctypes.data, b, pre, pre_reqs,
+                                   info.ctypes.data)
         if total < 0:
-            raise StepError("a request of the step is not live")
+            raise StepError("a request of the step is not live" if total == -1 else f"the step does not fit its layout (code {-total})")
         T = int(info[1])
         base = _align4(total)                              # the extra streams follow the native sections, T ints each
         total = base + len(self.stream_names) * _align4(T) if self.stream_names else total
@@ -172,7 +175,7 @@ class Runner:
         self.last_meta_ints = total
         host = slot[0]
         rc = lib.kf_step_fill(cache._h, n, reqs.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data, n_want.ctypes.data,
-                              wants.ctypes.data, b, info.ctypes.data, host.data_ptr())
+                              wants.ctypes.data, b, pre, pre_reqs, info.ctypes.data, host.data_ptr())
         if rc != 0:
             raise StepError(f"building the step's integer block failed (code {rc})")
         if self.stream_names:
@@ -215,7 +218,8 @@ class Runner:
         h = host.numpy()
         sizes = {"tokens": T, "positions": T, "row_req": T, "logit_rows": max(n_out, 1), "dec_rows": T, "pre_rows": T,
                  "tile_row0": T // 64 + B + 1, "tile_nrows": T // 64 + B + 1, "wide_row0": T // 128 + B + 1,
-                 "wide_nrows": T // 128 + B + 1, "req_row_start": B, "req_n_rows": B, "req_kv_len": B, "req_state_slot": B}
+                 "wide_nrows": T // 128 + B + 1, "req_row_start": B, "req_n_rows": B, "req_kv_len": B, "req_state_slot": B,
+                 "logit_req": max(n_out, 1)}
         where = {name: (int(off[i]), sizes[name]) for i, name in enumerate(self._SECTIONS)}
 
         def dview(name):
@@ -227,6 +231,7 @@ class Runner:
         ctx.decode_only = max_rows == 1
         ctx.tokens, ctx.positions, ctx.row_req = dview("tokens"), dview("positions"), dview("row_req")
         ctx.logit_rows = dview("logit_rows")[:n_out] if n_out else dview("logit_rows")[:0]
+        ctx.logit_req = dview("logit_req")[:n_out] if n_out else dview("logit_req")[:0]
         ctx.dec_rows, ctx.n_dec_rows = dview("dec_rows"), n_dec
         ctx.pre_rows, ctx.n_pre_rows = dview("pre_rows"), n_pre
         ctx.max_kv_len = max_kv
@@ -269,8 +274,9 @@ class Runner:
         lives in a buffer the next step overwrites.  Raises OutOfPages before touching anything when the
         pages for the new tokens cannot all be had.
         `sample`: (sampler states [max_requests, STATE_WORDS] int32 on the device, whole_ranking); the token of every
-        wanted row is then drawn in the same pass under its request's rules (inside the replayed graph for decode
-        steps) and the result is (logits, int32 token ids [wanted]).
+        wanted row is then drawn in the same pass under its request's rules (inside the replayed graph when the step has
+        one) and the result is (logits, int32 token ids), both with one row per wanted place EXCEPT under a padded mixed
+        layout, where `last_logit_index` says which row holds which wanted place.
         `feedback`: for a step in which every entry brings one token, a device tensor with those tokens in the order
         of the entries (the ids an earlier step drew, which the host has not read yet); the entries' own token values
         are then ignored."""
@@ -291,7 +297,8 @@ class Runner:
                 self.cache.cancel_reservation(e.request)
             raise
         try:
-            bucket = self._graph_bucket(entries)
+            bucket = self._graph_bucket(entries, greedy)
+            self.last_logit_index = self._logit_index(entries, bucket)
             picked = None
             if bucket is None:
                 ctx = self._fill(entries, None, feedback)
@@ -338,36 +345,69 @@ class Runner:
         from .. import ops
         states, whole = sample
         out = self.buffers.get("sampled_ids", (max(logits.shape[0], 1),), torch.int32)
-        ops.sample(logits, states, out, logit_rows=ctx.logit_rows, row_req=ctx.row_req, req_slot=ctx.req_state_slot,
-                   whole_ranking=bool(whole))
+        # row i of the logits belongs to request ctx.logit_req[i] of the step (-1: a row of a padded layout that nobody wants)
+        ops.sample(logits, states, out, row_req=ctx.logit_req, req_slot=ctx.req_state_slot, whole_ranking=bool(whole))
         return out[:logits.shape[0]]
 
-    # ---- decode steps replayed from CUDA graphs ---------------------------------------------------------------
-    MAX_PORTION_GRAPHS = 8
+    # ---- steps replayed from CUDA graphs -------------------------------------------------------------------------
+    MAX_MIXED_GRAPHS = 24
 
-    def _graph_bucket(self, entries):
-        """The key of the CUDA graph that runs this step, or None if the step runs eagerly.  A pure decode step: the
-        padded batch size (an int).  A step that is one short portion (64 to 256 rows) of one prompt: ("portion", rows,
-        wanted rows): such steps repeat with the same shape while a long prompt is fed under a small token budget, and
-        at that size launching their two hundred kernels one by one takes the host longer than the GPU needs to run
-        them (longer portions keep the GPU busy for longer than the host needs, so a graph would gain nothing)."""
+    def _graph_bucket(self, entries, sampled: bool):
+        """The layout under which this step can be replayed from a CUDA graph, or None if it runs eagerly.
+        A pure decode step: the padded batch size (an int).  A step that holds prompt portions, with or without decode
+        rows before them (what the scheduler plans while prompts are being fed under a token budget): ("mixed", decode
+        rows, prompt rows, portions), each rounded up to a bucket; such steps repeat with the same shape, and launching
+        their two hundred kernels one by one takes the host longer than the GPU needs to run them.  Mixed layouts have
+        one output row per request, so they serve steps whose tokens are drawn on the device (`sampled`) and whose
+        portions want their last row or none."""
         if not self.cuda_graphs or self.device.type != "cuda" or not self._graph_safe:
             return None
         from .. import ops
         if ops.tracing():                                  # per-kernel timing needs eager launches
             return None
-        if len(entries) == 1 and 64 <= len(entries[0].tokens) <= 256:
-            key = ("portion", len(entries[0].tokens), len(entries[0].want))
-            held = {k[1] if k[0] == "sample" else k for k in self._graphs if isinstance(k, tuple)}
-            if key in held or sum(1 for k in held if isinstance(k, tuple) and k[0] == "portion") < self.MAX_PORTION_GRAPHS:
-                return key
+        nd = 0
+        while nd < len(entries) and len(entries[nd].tokens) == 1 and list(entries[nd].want) == [0]:
+            nd += 1
+        rest = entries[nd:]
+        if not rest:
+            b = 1
+            while b < nd:
+                b *= 2
+            return b if b <= max(self.cache.max_requests, 1) * 2 else None
+        if not sampled or self.stream_names or len(rest) > 4:
             return None
-        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+        rows = 0
+        for e in rest:
+            n = len(e.tokens)
+            if n < 2 or list(e.want) not in ([], [n - 1]):
+                return None
+            rows += n
+        if rows > 2048:
             return None
-        b = 1
-        while b < len(entries):
-            b *= 2
-        return b if b <= max(self.cache.max_requests, 1) * 2 else None
+        d = 0
+        if nd:
+            d = 1
+            while d < nd:
+                d *= 2
+        unit = 64 if rows <= 512 else 128 if rows <= 1024 else 256
+        key = ("mixed", d, -(-rows // unit) * unit, 1 if len(rest) == 1 else 2 if len(rest) == 2 else 4)
+        held = {k[1] for k in self._graphs if isinstance(k, tuple) and isinstance(k[1], tuple)}
+        return key if (key in held or len(held) < self.MAX_MIXED_GRAPHS) else None
+
+    @staticmethod
+    def _logit_index(entries, bucket) -> list[int]:
+        """For every wanted place of the step, in the order of the entries, the row of the step's logits that holds it."""
+        if not isinstance(bucket, tuple):
+            return list(range(sum(len(e.want) for e in entries)))
+        d, out, j = bucket[1], [], 0
+        for i, e in enumerate(entries):
+            if len(e.tokens) == 1:
+                out.append(i)
+            else:
+                if e.want:
+                    out.append(d + j)
+                j += 1
+        return out
 
     def _forward(self, ctx):
         """The model's pass over the step, every launch on the stream that is current now."""
@@ -382,11 +422,11 @@ class Runner:
         launches are captured into a graph; from then on the step is one copy of integers and one replay."""
         from .. import ops
         pick = isinstance(key, tuple) and key[0] == "sample"   # a graph that also holds the draw of the tokens
-        shape = key[1] if pick else key
-        if isinstance(shape, tuple):                       # one portion of one prompt: the entries as they are, fixed layout
-            n, bucket = shape[2], -1
+        bucket = key[1] if pick else key
+        if isinstance(bucket, tuple):                      # a mixed layout: one output row per request of the bucket
+            n = bucket[1] + bucket[3]
         else:
-            n, bucket = len(entries), shape
+            n = len(entries)
         state = self._graphs.get(key)
         if state is not None and state["generation"] != self.buffers.generation:
             state = None                                   # a buffer moved: the old graph points at freed memory

@@ -241,3 +241,50 @@ def test_a_step_that_fails_gives_its_pages_back(tmp_path, cpu_ops):
     assert float((logits[0].float().cpu() - ref[12]).abs().max()) < 2e-4
     runner.cache.release("x")
     assert runner.cache.free_pages() == [g.pool.n_pages for g in runner.cache.groups]
+
+
+def test_padded_mixed_layout_gives_the_same_logits_as_the_natural_one(tmp_path, cpu_ops):
+    """The layout that mixed steps are replayed under on the GPU (decode rows first, then prompt rows, every count
+    rounded up to a bucket, unused rows and tiles empty): its sections are what the kernels expect, and the model run
+    over it yields, at the wanted places, the logits of the same step laid out as it is."""
+    from kungfu_b200.engine import StepEntry
+    cfg_dict = helpers.TINY_B
+    folder = helpers.write_model(str(tmp_path / "m"), cfg_dict, seed=6, dtype=torch.float32)
+    toks = {r: helpers.random_tokens(n, cfg_dict["vocab_size"], 30 + i) for i, (r, n) in enumerate((("a", 20), ("b", 9), ("c", 100), ("d", 31)))}
+
+    def make():
+        runner = _runner(folder, cfg_dict, 8, 512)
+        for r in toks:
+            runner.cache.add_request(r)
+        runner.step([StepEntry("a", toks["a"][:19], []), StepEntry("b", toks["b"][:8], []), StepEntry("c", toks["c"][:30], [])])
+        return runner
+    entries = [StepEntry("a", [toks["a"][19]], [0]), StepEntry("b", [toks["b"][8]], [0]),
+               StepEntry("c", toks["c"][30:], [69]), StepEntry("d", toks["d"], [])]
+    natural = make()
+    want = natural.step(entries).clone()
+    padded = make()
+    for e in entries:
+        padded.cache.reserve(e.request, len(e.tokens))
+    bucket = ("mixed", 4, 128, 2)
+    ctx = padded._fill(entries, bucket)
+    assert (ctx.n_rows, ctx.n_reqs, ctx.n_logits, ctx.n_dec_rows, ctx.n_pre_rows) == (132, 6, 6, 4, 128)
+    assert ctx.n_tiles == 128 // 64 + 2 and ctx.n_wide == 128 // 128 + 2
+    assert ctx.row_req.tolist() == [0, 1, -1, -1] + [4] * 70 + [5] * 31 + [-1] * 27
+    assert ctx.positions.tolist()[:2] == [19, 8] and ctx.positions.tolist()[4:7] == [30, 31, 32] and ctx.positions.tolist()[74] == 0
+    assert ctx.dec_rows.tolist()[:4] == [0, 1, 2, 3] and ctx.pre_rows.tolist()[:128] == list(range(4, 132))
+    assert ctx.tile_row0.tolist()[:4] == [4, 68, 74, 4] and ctx.tile_nrows.tolist()[:4] == [64, 6, 31, 0]
+    assert ctx.wide_row0.tolist()[:3] == [4, 74, 4] and ctx.wide_nrows.tolist()[:3] == [70, 31, 0]
+    assert ctx.logit_rows.tolist() == [0, 1, 0, 0, 73, 0] and ctx.logit_req.tolist() == [0, 1, -1, -1, 4, -1]
+    assert ctx.req_n_rows.tolist() == [1, 1, 0, 0, 70, 31] and ctx.req_kv_len.tolist() == [20, 9, 0, 0, 100, 31]
+    assert padded._logit_index(entries, bucket) == [0, 1, 4]
+    logits = padded.model.forward(ctx)
+    got = logits[padded._logit_index(entries, bucket)]
+    assert float((got - want).abs().max()) < 1e-5
+    # a step that does not fit the layout is refused, not squeezed in
+    from kungfu_b200.engine.step import StepError
+    for e in entries:
+        padded.cache.cancel_reservation(e.request)
+    with pytest.raises(StepError, match="does not fit its layout"):
+        padded._fill(entries, ("mixed", 1, 128, 2))
+    with pytest.raises(StepError, match="does not fit its layout"):
+        padded._fill([entries[2], entries[0]], ("mixed", 4, 128, 2))       # a prompt portion before a decode row

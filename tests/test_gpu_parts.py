@@ -195,3 +195,33 @@ def test_generate_through_the_entry_point(tmp_path, name):
     b = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], parallel=4, page_size=8).generate(prompts, s, max_tokens=12, seed=5)
     c = Engine(folder, dtype="float32", device=DEV, ctx=cfg["max_position_embeddings"], parallel=4, page_size=8).generate(prompts, s, max_tokens=12, seed=6)
     assert a == b and a != c
+
+
+def test_mixed_steps_replayed_from_graphs_give_the_plain_tokens(tmp_path):
+    """Long prompts fed under a small token budget while other requests decode: the scheduler's steps (decode rows
+    beside a prompt portion) repeat in shape and are replayed from CUDA graphs under a padded layout.  Greedy ids in
+    32-bit equal the plain implementation's, and equal the engine that launches every step eagerly."""
+    from kungfu_b200 import Engine, ops
+    from kungfu_b200.sampling import Sampling
+    cfg = helpers.TINY_E
+    folder = helpers.write_model(str(tmp_path / "m"), cfg, seed=14, dtype=torch.bfloat16)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 60 + n) for n in (40, 700, 2, 513, 330)]
+    want = [pg.greedy(cfg, tensors, p, 6) for p in prompts]
+    outs = {}
+    for graphs in (True, False):
+        e = Engine(folder, dtype="float32", device=DEV, ctx=1024, batch=96, parallel=4, page_size=64, cuda_graphs=graphs)
+        outs[graphs] = e.generate(prompts, Sampling(temperature=0.0), max_tokens=6, ignore_eos=True)
+        ops.raise_on_device_error()
+        mixed = [k for k, st in e.runner._graphs.items() if isinstance(k, tuple) and isinstance(k[1], tuple) and st["graph"] is not None]
+        assert bool(mixed) == graphs, list(e.runner._graphs)
+        assert e.runner.cache.n_live == 0
+    assert outs[True] == want and outs[False] == want
+    # bfloat16 through the same path: every token within the bfloat16 bound of the plain model's best, given the engine's own tokens
+    e = Engine(folder, dtype="bfloat16", device=DEV, ctx=1024, batch=96, parallel=4, page_size=64)
+    got = e.generate(prompts, Sampling(temperature=0.0), max_tokens=6, ignore_eos=True)
+    for p, out in zip(prompts, got):
+        logits = pg.forward(cfg, tensors, p + out).float()
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[tok]) <= 2 * 2e-2 * float(logits.abs().max())
