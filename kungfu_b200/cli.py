@@ -184,15 +184,15 @@ def cmd_score(args) -> int:
             logits[:, sorted(eos)] = float("-inf")
         n = logits.shape[0]
         if args.topk > 0:
-            ids = torch.empty((n, args.topk), dtype=torch.int32, device=logits.device)
+            best = torch.empty((n, args.topk), dtype=torch.int32, device=logits.device)
             vals = torch.empty((n, args.topk), dtype=torch.float32, device=logits.device)
             lse = torch.empty((n,), dtype=torch.float32, device=logits.device)
-            ops.topk_lse(logits, args.topk, ids, vals, lse)
-            rows += ids.cpu().tolist()
+            ops.topk_lse(logits, args.topk, best, vals, lse)
+            rows += best.cpu().tolist()
         else:
-            ids = torch.empty((n,), dtype=torch.int32, device=logits.device)
-            ops.argmax(logits, ids)
-            rows += ids.cpu().tolist()
+            best = torch.empty((n,), dtype=torch.int32, device=logits.device)
+            ops.argmax(logits, best)
+            rows += best.cpu().tolist()
     runner.cache.release("score")
     print(json.dumps({"ids": ids, "predictions": rows}))
     return 0
