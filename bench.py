@@ -704,7 +704,9 @@ def micro_reference() -> int:
             kc.normal_(0.0, 0.5, generator=gen)
             vc.normal_(0.0, 0.5, generator=gen)
         q32 = torch.randn(T, nh * d, device=device, generator=gen)
-        us_ref = _graph_us(torch, lambda: [ref.flash_prefill(q32, kc, vc, pos, seq0, [(0, 0, T)], nh, nkv, d, scale, None, 50.0) for kc, vc in caches], copies, reps=5)
+        tiles = ref.flash_tiles(pos, [(0, 0, T)], device)
+        us_ref = _graph_us(torch, lambda: [ref.flash_prefill(q32, kc, vc, pos, seq0, [(0, 0, T)], nh, nkv, d, scale, None, 50.0, tiles=tiles)
+                                           for kc, vc in caches], copies, reps=5)
         per_req = T // page
         pages = torch.empty(copies * per_req, 2, nkv, page, d, device=device, dtype=torch.bfloat16).normal_(0.0, 0.5, generator=gen)
         ctxs = []

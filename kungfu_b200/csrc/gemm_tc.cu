@@ -28,6 +28,10 @@ namespace {
 
 using namespace kf_tc;
 
+// A test can make the weight-streaming kernel's producer leave out the loads of every stage from this one on (-1: never),
+// so that a wait on operands that never arrive runs into its limit; see kf_test_gemm_give_up.
+static __device__ int g_test_drop_from_stage = -1;
+
 template <int BN>
 struct Tile {
   static constexpr int COLS = BN < 32 ? 32 : BN;                 // tensor-memory columns per accumulator
@@ -88,7 +92,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
-      const int pre = nkb < stages ? nkb : stages;
+      const int drop = g_test_drop_from_stage;
+      const int pre_all = nkb < stages ? nkb : stages;
+      const int pre = (drop >= 0 && drop < pre_all) ? drop : pre_all;      // a test leaves later loads out
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + (size_t)i * STAGE_BYTES;
         mbar_expect_tx(&full[i], STAGE_BYTES);
@@ -99,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       kf_pdl_wait();                                               // activations come from the previous kernel
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem + (size_t)i * STAGE_BYTES + Tile<BN>::A_BYTES * NACC, &tm_x, &full[i], (kb_begin + i) * BK, t0);
-      for (int i = pre; i < nkb; ++i) {
+      for (int i = pre_all; i < nkb && drop < 0; ++i) {
         const int s = i % stages;
         if (!mbar_wait(&empty[s], ((i / stages) - 1) & 1)) {
           atomicExch(error_flag, ERR_WAIT_EMPTY);
@@ -910,6 +916,20 @@ KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
 KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 #endif
+
+// For tests of the give-up path: every bounded wait of this file's kernels gives up after `limit_ns` nanoseconds (0: the
+// built-in two seconds), and the weight-streaming kernel's producer issues no load for stages `drop_from_stage` and
+// later (-1: all loads, the normal state).  A kernel whose wait runs out records a code in the error word it was
+// given, skips its stores, still meets every barrier, frees its tensor memory and returns; the context stays usable.
+KF_API int kf_test_gemm_give_up(unsigned long long limit_ns, int drop_from_stage) {
+  const unsigned long long lim = limit_ns ? limit_ns : WAIT_LIMIT_NS;
+  if (cudaMemcpyToSymbol(g_wait_limit_ns, &lim, sizeof(lim)) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_test_drop_from_stage, &drop_from_stage, sizeof(int)) != cudaSuccess) {
+    kf_record_cuda_error(cudaGetLastError());
+    return KF_ERR_SETUP;
+  }
+  return KF_OK;
+}
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
 KF_API int kf_linear_tc_supported(const void* x, const void* w, int K) {

@@ -30,6 +30,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // the hardware chooses, so the limit is a time (about two seconds on the global timer, looked at every 256 turns)
 // as well as a count.
 constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;
+// The limit in force (one copy per translation unit).  A test shortens it through the translation unit's hook to see a
+// wait give up; nothing else writes it.
+static __device__ unsigned long long g_wait_limit_ns = WAIT_LIMIT_NS;
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -49,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((i & 255) == 255) {
       const unsigned long long now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
+      else if (now - t0 > g_wait_limit_ns) return false;
     }
   }
   return false;

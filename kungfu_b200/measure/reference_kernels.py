@@ -242,9 +242,9 @@ class Reference:
         self.module("attention.cu").launch(f"attention_decode_hd{d}", (rows * n_kv, parts, nsplit), 256, 0, args)
         return out
 
-    def flash_prefill(self, q, kc, vc, pos, seq, runs, n_head, n_kv, d, scale, window, softcap):
-        """flash_prefill_hd{d}: tiles of 64 rows of one slot, heaviest first (exec.rs:1825-1848); `runs` is a list of
-        (slot, first row, row count)."""
+    def flash_tiles(self, pos, runs, device):
+        """The tile table of flash_prefill: tiles of 64 rows of one slot, heaviest first (exec.rs:1825-1848); `runs` is a
+        list of (slot, first row, row count).  Returns (device table, tile count)."""
         import torch
         tiles = []
         pos_h = pos.tolist()
@@ -258,13 +258,19 @@ class Reference:
         table = [len(tiles), 0, 0, 0]
         for _, r, m, slot in tiles:
             table += [r, m, slot, 0]
-        tiles_dev = torch.tensor(table, dtype=torch.int32, device=q.device)
-        out = torch.zeros(q.shape[0], n_head * d, dtype=torch.float32, device=q.device)
+        return torch.tensor(table, dtype=torch.int32, device=device), len(tiles)
+
+    def flash_prefill(self, q, kc, vc, pos, seq, runs, n_head, n_kv, d, scale, window, softcap, tiles=None):
+        """flash_prefill_hd{d} over the rows of `runs` (see flash_tiles; pass its result as `tiles` to keep the call free
+        of host reads, e.g. under graph capture)."""
+        import torch
+        tiles_dev, n_tiles = tiles if tiles is not None else self.flash_tiles(pos, runs, q.device)
+        out = torch.empty(q.shape[0], n_head * d, dtype=torch.float32, device=q.device)
         nch = -(-(d // 8) // 8) * 8
         bk = 64 if d <= 128 else 32
         smem = (64 + 4 * bk) * nch * 16
         self._keep = tiles_dev
-        self.module("flash.cu").launch(f"flash_prefill_hd{d}", (len(tiles), n_head, 1), 128, smem,
+        self.module("flash.cu").launch(f"flash_prefill_hd{d}", (n_tiles, n_head, 1), 128, smem,
                                        [ptr(q), ptr(kc), ptr(vc), ptr(pos), ptr(seq), ptr(pos), ptr(tiles_dev), P(0), ptr(out),
                                         I(n_head), I(n_kv), F(scale), I(window or 0), F(softcap), I(kc.shape[1])])
         return out

@@ -166,11 +166,37 @@ def tracing() -> bool:
     return _trace is not None
 
 
+# NVTX ranges around every part and operation, for timelines of a profiler (KUNGFU_NVTX=1 or ops.nvtx_ranges = True).
+nvtx_ranges = os.environ.get("KUNGFU_NVTX", "0") == "1"
+
+
+class nvtx_range:
+    """`with ops.nvtx_range("layer 3"):` opens an NVTX range when ranges are switched on, and costs a test otherwise."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.on = False
+
+    def __enter__(self):
+        self.on = nvtx_ranges and _override is None
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def _dispatch(name):
     def deco(fn):
         def wrapper(*a, **k):
             if _override is not None:
                 return getattr(_override, name)(*a, **k)
+            if nvtx_ranges:
+                with nvtx_range(name):
+                    return fn(*a, **k)
             if _trace is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -267,6 +293,15 @@ def device_error(device=None) -> int:
         device = torch.device("cuda", torch.cuda.current_device())
     sc = _scratch.get((device.type, device.index))
     return 0 if sc is None else int(sc["error"].item())
+
+
+def clear_device_error(device=None) -> None:
+    """Set the error word back to 0 (after a failure that was looked at)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    sc = _scratch.get((device.type, device.index))
+    if sc is not None:
+        sc["error"].zero_()
 
 
 def raise_on_device_error(device=None) -> None:

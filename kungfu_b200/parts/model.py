@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from .. import ops
 from .base import Block, Part, StateNeed
 from .embedding import Embedding, LmHead
 
@@ -57,18 +58,21 @@ class DecoderModel(Part):
 
     def forward(self, ctx):
         """Runs exactly the rows in `ctx`; returns 32-bit logits for `ctx.logit_rows` (None if none wanted)."""
-        x = self.embedding.forward(ctx)
+        with ops.nvtx_range("embedding"):
+            x = self.embedding.forward(ctx)
         normed = None
         for i, call in enumerate(self.schedule):
             block = self.layers[call.layer]
             view = ctx.cache_view(call.cache, call.writes)
-            if getattr(block, "fuses_next_norm", False):
-                # the last kernel of this block also computes the next block's first norm, when both can
-                nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
-                then = nxt.pre_mixer if nxt is not None and getattr(nxt, "fuses_next_norm", False) else None
-                x, normed = block.forward(x, ctx, view, normed=normed, then=then)
-            else:
-                x, normed = block.forward(x, ctx, view), None
+            with ops.nvtx_range(f"layer {call.layer} ({type(block.mixer).__name__})"):
+                if getattr(block, "fuses_next_norm", False):
+                    # the last kernel of this block also computes the next block's first norm, when both can
+                    nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+                    then = nxt.pre_mixer if nxt is not None and getattr(nxt, "fuses_next_norm", False) else None
+                    x, normed = block.forward(x, ctx, view, normed=normed, then=then)
+                else:
+                    x, normed = block.forward(x, ctx, view), None
         if ctx.n_logits == 0:
             return None
-        return self.head.forward(x, ctx)
+        with ops.nvtx_range("head"):
+            return self.head.forward(x, ctx)

@@ -770,3 +770,55 @@ def test_device_sampler_skips_padding_rows_and_follows_the_maps(ops):
     want1, _ = plain_sampler.sample(l[1].cpu().numpy(), temperature=1.0, top_k=40, rng=plain_sampler.Rng(102))
     assert out.cpu().tolist() == [want0, want1, 0]
     assert after[3][8] == 1 and after[2][8] == 1 and (after[[0, 1, 4]] == st[[0, 1, 4]]).all()
+
+
+@pytest.mark.parametrize("T,N,K", [(8, 2304, 2304), (300, 4096, 2304), (16, 256, 2048)])
+def test_a_wait_that_runs_out_leaves_a_status_and_a_usable_device(ops, T, N, K):
+    """Every wait of the tensor-core kernels on a barrier is bounded.  Here one runs out: a test hook makes the
+    weight-streaming product's producer leave out its loads from the second stage on and shortens the limit to 2 ms, so
+    the thread that issues the MMAs waits for operands that never arrive.  The kernel must come back by itself (error
+    word set, nothing trapped, tensor memory freed, every cluster barrier met), and the same product must be right
+    again once the hook is off."""
+    import ctypes
+    import time
+    lib = ops.library()
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.zeros(T, N, device=DEV)
+    ops.linear(x, w, out)                                    # builds tensor maps and the scratch before the hook is on
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    assert lib.kf_test_gemm_give_up(ctypes.c_ulonglong(2_000_000), 1) == 0
+    try:
+        t0 = time.perf_counter()
+        ops.linear(x, w, out)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        code = ops.device_error()
+    finally:
+        assert lib.kf_test_gemm_give_up(ctypes.c_ulonglong(0), -1) == 0
+    assert code in (1, 2, 3), code                           # operands never arrived / stage never freed / accumulator
+    assert waited < 2.0
+    with pytest.raises(ops.KernelError, match="gave up waiting"):
+        ops.raise_on_device_error()
+    ops.clear_device_error()
+    again = torch.full((T, N), float("nan"), device=DEV)
+    ops.linear(x, w, again)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    assert rel_err(again, x.double() @ w.double().T) < 2e-6 * math.sqrt(K) + 1e-6
+
+
+def test_nvtx_ranges_can_be_switched_on(ops):
+    x = torch.randn(4, 64, device=DEV)
+    w = torch.zeros(64, device=DEV)
+    out = torch.empty(4, 64, device=DEV)
+    ops.nvtx_ranges = True
+    try:
+        ops.rmsnorm(x, w, 1e-6, True, out)
+        with ops.nvtx_range("a part"):
+            ops.rmsnorm(x, w, 1e-6, True, out)
+    finally:
+        ops.nvtx_ranges = False
+    assert rel_err(out, x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-6)) < 1e-5

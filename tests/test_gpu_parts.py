@@ -225,3 +225,37 @@ def test_mixed_steps_replayed_from_graphs_give_the_plain_tokens(tmp_path):
         for i, tok in enumerate(out):
             row = logits[len(p) + i - 1]
             assert float(row.max() - row[tok]) <= 2 * 2e-2 * float(logits.abs().max())
+
+
+def test_preemption_and_recompute_on_the_device(tmp_path):
+    """Pages run out while three requests decode: the scheduler preempts the one admitted last, which is recomputed later
+    from its prompt and the tokens it had produced.  The engine must read the tokens of the step in flight before it
+    plans such a step (a preempted request's tokens become a prompt), and the ids, greedy and sampled, must equal those
+    of an engine with room, in 32-bit those of the plain implementation."""
+    import plain_sampler
+    from kungfu_b200 import Engine, ops
+    from kungfu_b200.sampling import Sampling
+    cfg = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg, seed=4, dtype=torch.bfloat16)
+    tensors = helpers.read_tensors(folder)
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 90 + n) for n in (5, 7, 6)]
+    want = [pg.greedy(cfg, tensors, p, 8) for p in prompts]
+    rules = dict(temperature=0.9, top_k=30, top_p=0.95, repeat_penalty=1.2)
+    want_s = []
+    for i, p in enumerate(prompts):
+        rng, out = plain_sampler.Rng(7 + i), []
+        for _ in range(8):
+            row = pg.forward(cfg, tensors, p + out)[-1].float().numpy()
+            out.append(plain_sampler.sample(row, recent=out, rng=rng, **rules)[0])
+        want_s.append(out)
+    for pipeline in (True, False):
+        tight = Engine(folder, dtype="float32", device=DEV, ctx=64, batch=16, parallel=4, page_size=4, max_tokens_in_cache=36,
+                       pipeline=pipeline)
+        assert tight.generate(prompts, Sampling(temperature=0.0), max_tokens=8) == want
+        assert tight.scheduler.n_preemptions > 0 and tight.runner.cache.n_live == 0
+        tight = Engine(folder, dtype="float32", device=DEV, ctx=64, batch=16, parallel=4, page_size=4, max_tokens_in_cache=36,
+                       pipeline=pipeline)
+        assert tight.generate(prompts, Sampling(**rules), max_tokens=8, seed=7) == want_s
+        assert tight.scheduler.n_preemptions > 0
+        assert tight.runner.cache.free_pages() == [g.pool.n_pages for g in tight.runner.cache.groups]
+    ops.raise_on_device_error()
