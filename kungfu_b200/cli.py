@@ -35,8 +35,17 @@ def _device(args) -> str:
 
 def _engine(args, parallel: int = 1):
     from .engine.engine import Engine
-    return Engine(args.model, dtype=args.dtype, device=_device(args), ctx=args.ctx if args.ctx == "auto" else int(args.ctx),
+    common = dict(dtype=args.dtype, device=_device(args), ctx=args.ctx if args.ctx == "auto" else int(args.ctx),
                   batch=args.batch, parallel=parallel, page_size=args.page_size, events=getattr(args, "events", False))
+    if getattr(args, "random_weights", False):
+        # no file: weights are drawn on the device from the configuration and the seed (the same values that
+        # `random-weights` would write into a model folder)
+        if not getattr(args, "config", None):
+            raise SystemExit("error: --random-weights needs --config (a config.json)")
+        return Engine(config=args.config, seed=args.weights_seed, **common)
+    if not args.model:
+        raise SystemExit("error: give --model DIR, or --config FILE --random-weights")
+    return Engine(args.model, **common)
 
 
 # ---- inspect ------------------------------------------------------------------------------------------------
@@ -137,8 +146,10 @@ def cmd_describe(args) -> int:
            "parts": {k: base.known(k) for k in ("mixer", "feed_forward", "norm", "position", "block")},
            "params": [{"name": n, "type": t, "default": d, "flag": f, "description": desc} for n, t, d, f, desc in PARAMS],
            "events": ["plan", "alloc", "ready", "request", "error"], "finish_reasons": ["eos", "length", "context", "cancelled", "no_fit"],
-           "errors": ["config", "unknown_arch", "weights", "model_open"],
-           "kernel_library": ops.library_path()}
+           "errors": ["config", "unknown_arch", "weights", "model_open", "no_fit"],
+           "kernel_library": ops.library_path(),
+           # how often bfloat16 work of this process left the tensor-core kernels for a generic one, by reason
+           "slow_kernel_fallbacks": ops.fallbacks()}
     print(json.dumps(doc, indent=2))
     return 0
 
@@ -285,9 +296,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("describe", help="capabilities and parameters of this build as JSON")
     p.set_defaults(fn=cmd_describe)
     p = sub.add_parser("generate", help="complete a prompt of token ids")
-    p.add_argument("--model", required=True)
+    p.add_argument("--model", default=None, help="folder with config.json and model.safetensors")
     p.add_argument("--prompt", default="", help="text prompts need a tokenizer, which this build lacks: use --ids")
     p.add_argument("--ids", default=None, help="prompt as a JSON array of token ids")
+    p.add_argument("--config", default=None, help="with --random-weights: the config.json to build from")
+    p.add_argument("--random-weights", action="store_true", help="no model folder: draw weights from --config and --weights-seed")
+    p.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
     p.add_argument("--emit-ids", action="store_true", help="print prompt and generated ids as JSON (always so here)")
     p.add_argument("--max-tokens", type=int, default=64)
     p.add_argument("--ignore-eos", action="store_true")

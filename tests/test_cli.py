@@ -85,3 +85,11 @@ def test_generate_score_bench(model_dir):
     p = run(["generate", "--model", model_dir, "--ids", json.dumps(ids), "--max-tokens", "5", "--temperature", "0.8", "--seed", "3",
              "--ctx", "128", "--events"])
     assert p.returncode == 0 and "kungfu event=ready" in p.stderr and "kungfu event=request" in p.stderr
+    assert "kungfu event=plan " in p.stderr and "kungfu event=alloc pool=cuda0 kind=weights" in p.stderr
+    assert "kind=cache" in p.stderr
+    # no model folder: the weights a folder written with the same seed would hold, drawn on the device
+    cfg_path = os.path.join(model_dir, "config.json")
+    p = run(["generate", "--config", cfg_path, "--random-weights", "--weights-seed", "17", "--ids", json.dumps(ids), "--max-tokens", "6",
+             "--dtype", "float32", "--ctx", "128", "--ignore-eos"])
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert json.loads(p.stdout.strip().split("\n")[-1])["generated"] == plain_gemma2.greedy(cfg, tensors, ids, 6)
