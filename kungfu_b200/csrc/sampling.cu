@@ -129,15 +129,18 @@ constexpr int ST_WORDS = 272, ST_RNG = 0, ST_TEMP = 2, ST_TOP_P = 3, ST_MIN_P = 
 constexpr int CAND = 64;               // candidates kept per slice and per row (reference: TOP = 64, session.rs:80)
 constexpr int SLICE = 4096;            // columns per block of the first kernel
 constexpr int SL_THREADS = 256;
+constexpr int MG_THREADS = 1024;        // the second kernel: one block per row, its loads from L2 are the cost
 
 __device__ __forceinline__ float st_f(const int* st, int w) { return __int_as_float(st[w]); }
 
-// Among `n` 64-bit keys in shared memory (all different, or zero for "absent"), the key that has exactly `want - 1`
-// larger ones: an 8-bit radix walk from the top byte.  Called by all threads of a block of 256; hist: 256 ints,
-// sh: 2 u64 + 2 ints.  Returns 0 when fewer than `want` keys are present.
+// Among `n` 64-bit keys in shared memory (all different, or zero for "absent"), a threshold that exactly `want` keys
+// reach: an 8-bit radix walk from the top byte, which ends as soon as a bin is wanted whole (the threshold is then that
+// bin's lowest possible key, not a key of the set).  Called by all threads of a block (a multiple of 32, at least 256); hist: 256 ints,
+// sh: 1 u64 + 1 int.  Returns 0 when fewer than `want` keys are present.  Logits of one row share their top bytes, so
+// a warp first finds which of its lanes hold the same bin and adds to the histogram once per bin.
 __device__ __forceinline__ unsigned long long select_key(const unsigned long long* keys, int n, int want, int* hist,
                                                          unsigned long long* sh_prefix, int* sh_need) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31;
   if (tid == 0) { *sh_prefix = 0ull; *sh_need = want; }
   __syncthreads();
   for (int shift = 56; shift >= 0; shift -= 8) {
@@ -145,9 +148,16 @@ __device__ __forceinline__ unsigned long long select_key(const unsigned long lon
     __syncthreads();
     const unsigned long long prefix = *sh_prefix;
     const unsigned long long mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
-    for (int i = tid; i < n; i += blockDim.x) {
-      const unsigned long long k = keys[i];
-      if (k != 0ull && (k & mask) == prefix) atomicAdd(&hist[(int)((k >> shift) & 255ull)], 1);
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+      const int i = i0 + tid;
+      const unsigned long long k = i < n ? keys[i] : 0ull;
+      const bool in = k != 0ull && (k & mask) == prefix;
+      const unsigned act = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int bin = (int)((k >> shift) & 255ull);
+        const unsigned same = __match_any_sync(act, bin);
+        if (lane == __ffs(same) - 1) atomicAdd(&hist[bin], __popc(same));
+      }
     }
     __syncthreads();
     if (tid < 32) {                                       // warp 0: bins 255 down to 0, eight per lane
@@ -163,28 +173,48 @@ __device__ __forceinline__ unsigned long long select_key(const unsigned long lon
       }
       int above = incl - sum;                             // keys in higher bins than this lane's
       int found = -1, found_need = 0;
+      bool whole = false;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if (found < 0 && above + mine[j] >= need && above < need) { found = 255 - (tid * 8 + j); found_need = need - above; }
+        if (found < 0 && above + mine[j] >= need && above < need) {
+          found = 255 - (tid * 8 + j);
+          found_need = need - above;
+          whole = found_need == mine[j];
+        }
         above += mine[j];
       }
       const unsigned who = __ballot_sync(0xffffffffu, found >= 0);
       if (who == 0u) { if (tid == 0) *sh_need = -1; }     // fewer keys than wanted
-      else if (tid == __ffs(who) - 1) { *sh_prefix = prefix | ((unsigned long long)found << shift); *sh_need = found_need; }
+      else if (tid == __ffs(who) - 1) {
+        *sh_prefix = prefix | ((unsigned long long)found << shift);
+        *sh_need = whole ? 0 : found_need;                // 0: every key of that bin is wanted, the walk is over
+      }
     }
     __syncthreads();
     if (*sh_need < 0) return 0ull;
+    if (*sh_need == 0) break;
   }
   return *sh_prefix;
 }
 
 // ---- kernel 1: one slice of one row -----------------------------------------------------------------------------------
 // out_keys [rows, n_slices, 64] (zero = absent), out_stats [rows, n_slices, 2] = (maximum, sum of exp(v - maximum)) of the
-// slice BEFORE the penalty.  states may be null (no penalty); slot_rows etc. as in kf_sample.
+// slice BEFORE the penalty (only when `need_stats`).  states may be null (no penalty); slot_rows etc. as in kf_sample.
+// A row whose request takes the best token (temperature <= 0) needs one key per slice, unless `rank_all` (the caller
+// wants the ranked candidates themselves).
+__device__ __forceinline__ const int* row_state(int row, const int* logit_rows, const int* row_req, const int* req_slot,
+                                                const int* states) {
+  if (states == nullptr) return nullptr;
+  const int lr = logit_rows ? logit_rows[row] : row;
+  const int rq = row_req ? row_req[lr] : 0;
+  if (rq < 0) return nullptr;
+  return states + (size_t)(req_slot ? req_slot[rq] : rq) * ST_WORDS;
+}
+
 __global__ void __launch_bounds__(SL_THREADS)
 sample_slices_kernel(const float* __restrict__ logits, int V, int n_slices, const int* __restrict__ logit_rows,
                      const int* __restrict__ row_req, const int* __restrict__ req_slot, const int* __restrict__ states,
-                     unsigned long long* __restrict__ out_keys, float* __restrict__ out_stats) {
+                     unsigned long long* __restrict__ out_keys, float* __restrict__ out_stats, int need_stats, int rank_all) {
   kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ unsigned long long keys[SLICE];
@@ -196,54 +226,90 @@ sample_slices_kernel(const float* __restrict__ logits, int V, int n_slices, cons
   const int c0 = slice * SLICE, n = min(SLICE, V - c0);
   const float* src = logits + (size_t)row * V + c0;
   float* vals = reinterpret_cast<float*>(keys);           // the values sit in the lower half until the keys are made
+  const int* st = row_state(row, logit_rows, row_req, req_slot, states);
+  const bool best_only = !rank_all && st != nullptr && st_f(st, ST_TEMP) <= 0.f;
   float mx = -INFINITY;
-  for (int i = tid; i < n; i += SL_THREADS) { const float v = src[i]; vals[i] = v; mx = fmaxf(mx, v); }
-  mx = kf_warp_max(mx);
-  if ((tid & 31) == 0) red[tid >> 5] = mx;
-  __syncthreads();
-  if (tid < 32) {
-    float t = tid < SL_THREADS / 32 ? red[tid] : -INFINITY;
-    t = kf_warp_max(t);
-    if (tid == 0) red[32] = t;
+  {
+    float r[SLICE / SL_THREADS];                          // every load of the thread in flight at once
+#pragma unroll
+    for (int j = 0; j < SLICE / SL_THREADS; ++j) { const int i = tid + j * SL_THREADS; r[j] = i < n ? src[i] : -INFINITY; }
+#pragma unroll
+    for (int j = 0; j < SLICE / SL_THREADS; ++j) {
+      const int i = tid + j * SL_THREADS;
+      if (i < n) { vals[i] = r[j]; mx = fmaxf(mx, r[j]); }
+    }
+  }
+  if (need_stats) {
+    mx = kf_warp_max(mx);
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    if (tid < 32) {
+      float t = tid < SL_THREADS / 32 ? red[tid] : -INFINITY;
+      t = kf_warp_max(t);
+      if (tid == 0) red[32] = t;
+    }
+    __syncthreads();
+    mx = red[32];
+    float sum = 0.f;
+    for (int i = tid; i < n; i += SL_THREADS) sum += expf(vals[i] - mx);
+    sum = kf_block_sum(sum, red);
+    if (tid == 0) {
+      out_stats[((size_t)row * n_slices + slice) * 2] = mx;
+      out_stats[((size_t)row * n_slices + slice) * 2 + 1] = sum;
+    }
   }
   __syncthreads();
-  mx = red[32];
-  float sum = 0.f;
-  for (int i = tid; i < n; i += SL_THREADS) sum += expf(vals[i] - mx);
-  sum = kf_block_sum(sum, red);
-  if (tid == 0) {
-    out_stats[((size_t)row * n_slices + slice) * 2] = mx;
-    out_stats[((size_t)row * n_slices + slice) * 2 + 1] = sum;
-  }
   // the repeat penalty on this slice's columns (one thread: at most 256 tokens, applied as often as they occur)
-  if (states != nullptr && tid == 0) {
-    const int lr = logit_rows ? logit_rows[row] : row;
-    const int rq = row_req ? row_req[lr] : 0;
-    if (rq >= 0) {
-      const int* st = states + (size_t)(req_slot ? req_slot[rq] : rq) * ST_WORDS;
-      const float pen = st_f(st, ST_PENALTY);
-      if (pen != 1.f) {
-        const int count = st[ST_COUNT], window = min(min(st[ST_WINDOW], RING), count);
-        for (int j = count - window; j < count; ++j) {
-          const int t = st[ST_RING + (j & (RING - 1))] - c0;
-          if (t >= 0 && t < n) vals[t] = kf_penalized(vals[t], pen);
-        }
+  if (st != nullptr && tid == 0) {
+    const float pen = st_f(st, ST_PENALTY);
+    if (pen != 1.f) {
+      const int count = st[ST_COUNT], window = min(min(st[ST_WINDOW], RING), count);
+      for (int j = count - window; j < count; ++j) {
+        const int t = st[ST_RING + (j & (RING - 1))] - c0;
+        if (t >= 0 && t < n) vals[t] = kf_penalized(vals[t], pen);
       }
     }
   }
   __syncthreads();
-  // values -> keys, from the top down so that a key never overwrites a value not yet read
-  for (int base = ((SLICE - 1) / SL_THREADS) * SL_THREADS; base >= 0; base -= SL_THREADS) {
-    const int i = base + tid;
-    const float v = i < n ? vals[i] : 0.f;
+  unsigned long long* dst = out_keys + ((size_t)row * n_slices + slice) * CAND;
+  if (best_only) {                                        // the slice's best key and 63 absent ones
+    unsigned long long best = 0ull;
+    for (int i = tid; i < n; i += SL_THREADS) {
+      const unsigned long long k = kf_key(vals[i], (unsigned)(c0 + i));
+      best = k > best ? k : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    __syncthreads();                                      // everyone has read its values: the keys' array is free
+    if ((tid & 31) == 0) keys[SLICE - 1 - (tid >> 5)] = best;
     __syncthreads();
-    if (i < SLICE) keys[i] = i < n ? kf_key(v, (unsigned)(c0 + i)) : 0ull;
+    if (tid == 0) {
+      for (int w = 1; w < SL_THREADS / 32; ++w) { const unsigned long long other = keys[SLICE - 1 - w]; best = other > best ? other : best; }
+      dst[0] = best;
+    } else if (tid < CAND) {
+      dst[tid] = 0ull;
+    }
+    return;
+  }
+  // values -> keys: the keys overwrite the values, so every thread first takes its values into registers
+  {
+    float mine[SLICE / SL_THREADS];
+#pragma unroll
+    for (int j = 0; j < SLICE / SL_THREADS; ++j) { const int i = tid + j * SL_THREADS; mine[j] = i < n ? vals[i] : 0.f; }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < SLICE / SL_THREADS; ++j) {
+      const int i = tid + j * SL_THREADS;
+      keys[i] = i < n ? kf_key(mine[j], (unsigned)(c0 + i)) : 0ull;
+    }
     __syncthreads();
   }
   const unsigned long long kth = select_key(keys, SLICE, CAND, hist, &sh_prefix, &sh_need);
   if (tid == 0) sh_count = 0;
   __syncthreads();
-  unsigned long long* dst = out_keys + ((size_t)row * n_slices + slice) * CAND;
   for (int i = tid; i < SLICE; i += SL_THREADS) {
     const unsigned long long k = keys[i];
     if (k != 0ull && k >= kth) {                          // kth = 0: fewer than 64 columns, all of them
@@ -271,7 +337,7 @@ __device__ __forceinline__ void record_token(int* st, int token) {
 
 // ---- kernel 2: one row: merge, rank, draw -----------------------------------------------------------------------------
 // Dynamic shared memory: n_slices * 64 keys.  flags[row] = 1 when the row must be finished by the third kernel.
-__global__ void __launch_bounds__(SL_THREADS)
+__global__ void __launch_bounds__(MG_THREADS)
 sample_merge_kernel(const unsigned long long* __restrict__ slice_keys, const float* __restrict__ slice_stats, int n_slices,
                     int V, const int* __restrict__ logit_rows, const int* __restrict__ row_req,
                     const int* __restrict__ req_slot, int* __restrict__ states, int draw, int* __restrict__ out_ids,
@@ -287,14 +353,39 @@ sample_merge_kernel(const unsigned long long* __restrict__ slice_keys, const flo
   __shared__ int sh_need, sh_count;
   const int row = blockIdx.x, tid = threadIdx.x;
   const int n = n_slices * CAND;
-  for (int i = tid; i < n; i += SL_THREADS) all_keys[i] = slice_keys[(size_t)row * n + i];
+  if (draw && cand_ids == nullptr && cand_lse == nullptr) {
+    // a row that takes the best token: the first kernel left one key per slice
+    int* st0 = const_cast<int*>(row_state(row, logit_rows, row_req, req_slot, states));
+    if (st0 != nullptr && st_f(st0, ST_TEMP) <= 0.f) {
+      if (tid >= 32) return;
+      unsigned long long best = 0ull;
+      for (int sl = tid; sl < n_slices; sl += 32) {
+        const unsigned long long k = slice_keys[((size_t)row * n_slices + sl) * CAND];
+        best = k > best ? k : best;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+      }
+      if (tid == 0) {
+        if (flags) flags[row] = 0;
+        const int token = kf_key_id(best);
+        out_ids[row] = token;
+        record_token(st0, token);
+      }
+      return;
+    }
+  }
+#pragma unroll 4
+  for (int i = tid; i < n; i += MG_THREADS) all_keys[i] = slice_keys[(size_t)row * n + i];
   if (tid < CAND) { top[tid] = 0ull; ranked[tid] = 0ull; }
   __syncthreads();
   const int k = min(CAND, V);
   const unsigned long long kth = select_key(all_keys, n, k, hist, &sh_prefix, &sh_need);
   if (tid == 0) sh_count = 0;
   __syncthreads();
-  for (int i = tid; i < n; i += SL_THREADS) {
+  for (int i = tid; i < n; i += MG_THREADS) {
     const unsigned long long key = all_keys[i];
     if (key != 0ull && key >= kth) {
       const int at = atomicAdd(&sh_count, 1);
@@ -325,7 +416,17 @@ sample_merge_kernel(const unsigned long long* __restrict__ slice_keys, const flo
     sum = kf_warp_sum(sum);
     if (tid == 0) cand_lse[row] = m + logf(sum);
   }
-  if (!draw || tid != 0) return;
+  if (!draw) return;
+  __shared__ float w[CAND];                                // weights of the ranked candidates, one thread each
+  {
+    const int* st1 = row_state(row, logit_rows, row_req, req_slot, states);
+    if (st1 != nullptr && tid < CAND) {
+      const float t1 = st_f(st1, ST_TEMP);
+      w[tid] = (t1 > 0.f && ranked[tid] != 0ull) ? expf((kf_key_value(ranked[tid]) - kf_key_value(ranked[0])) / t1) : 0.f;
+    }
+  }
+  __syncthreads();
+  if (tid != 0) return;
   if (flags) flags[row] = 0;
   const int lr = logit_rows ? logit_rows[row] : row;
   const int rq = row_req ? row_req[lr] : 0;
@@ -338,11 +439,9 @@ sample_merge_kernel(const unsigned long long* __restrict__ slice_keys, const flo
     token = kf_key_id(ranked[0]);
   } else if (top_k >= 1 && (top_k <= CAND || V <= CAND)) {
     const int n1 = min(min(top_k, k), V);
-    const float vmax = kf_key_value(ranked[0]);
     const float min_p = st_f(st, ST_MIN_P), top_p = st_f(st, ST_TOP_P);
     double mass1 = 0.0;
-    float w[CAND];
-    for (int i = 0; i < n1; ++i) { w[i] = expf((kf_key_value(ranked[i]) - vmax) / temp); mass1 += (double)w[i]; }
+    for (int i = 0; i < n1; ++i) mass1 += (double)w[i];
     int keep = n1;
     if (min_p > 0.f) {
       keep = 0;
@@ -563,9 +662,10 @@ KF_API int kf_sample(const float* logits, int rows, int V, unsigned long long* s
     configured = true;
   }
   kf_launch(sample_slices_kernel, dim3(n_slices, rows), dim3(SL_THREADS), 0, stream, logits, V, n_slices, logit_rows, row_req,
-            req_slot, (const int*)states, slice_keys, slice_stats);
+            req_slot, (const int*)states, slice_keys, slice_stats, cand_lse != nullptr ? 1 : 0,
+            (cand_ids != nullptr || cand_lse != nullptr) ? 1 : 0);
   KF_CHECK_LAUNCH();
-  kf_launch(sample_merge_kernel, dim3(rows), dim3(SL_THREADS), merge_smem, stream, (const unsigned long long*)slice_keys,
+  kf_launch(sample_merge_kernel, dim3(rows), dim3(MG_THREADS), merge_smem, stream, (const unsigned long long*)slice_keys,
             (const float*)slice_stats, n_slices, V, logit_rows, row_req, req_slot, states, states ? 1 : 0, out_ids, cand_ids,
             cand_vals, cand_lse, k_out, flags);
   KF_CHECK_LAUNCH();
