@@ -3,15 +3,20 @@
 //
 // A block is (tile of up to 128 consecutive rows of one request, query head).  Keys are walked in tiles of 64, which
 // is one cache page (or a 64-aligned part of one), so a tile is a handful of TMA boxes [64 keys x 64 elements].
-//   warp 8   : one lane issues the TMA loads: the Q tile once, then K and V tiles into a two-stage ring
-//   warp 9   : allocates tensor memory; one lane issues the MMAs:  S_i = Q K_i^T (M 128, N 64, K = head size) into
-//              one of two S buffers, and O += P_i V_i (M 128, N = head size, K 64) with V as an MN-major operand
-//   warps 0-7: two threads per query row (= tensor-memory lane), warps 0-3 the first 32 keys of a tile and warps 4-7
-//              the other 32: read their half of the row of S, scale, cap, mask, agree on the row's maximum through
-//              shared memory, exponentiate, keep the running maximum and their half of the sum, round P to bfloat16
-//              into swizzled shared memory for the second MMA, and at the end read their half of O's columns, divide
-//              by the sum and store.  Two warps per scheduler hide each other's tensor-memory and barrier latencies;
-//              the exponentials (three per score with the cap) are what bounds the tile.
+//   warp 8   : one lane issues the TMA loads of the Q tile (once) and of the K tiles into a two-stage ring
+//   warp 11  : one lane issues the TMA loads of the V tiles into a ring of their own
+//   warp 10  : one lane issues S_i = Q K_i^T (M 128, N 64, K = head size) into S buffer i % 2 as soon as the keys are
+//              there and the softmax group has taken S_(i-2) out of that buffer: long before P_(i-2) is complete, so
+//              the group finds its next scores waiting
+//   warp 9   : allocates tensor memory; one lane issues O += P_i V_i (M 128, N = head size, K 64) with V as an
+//              MN-major operand, as soon as P_i and the values are there
+//   warps 0-7: two groups of four warps, one thread per query row (= tensor-memory lane) in each.  Group g takes the
+//              key tiles i with i % 2 == g (which land in S buffer g): read the row of S, scale, cap, mask, take the
+//              maximum, exponentiate, add to the group's sum, round P to bfloat16 into swizzled shared memory for the
+//              second MMA.  The groups are out of step by half a tile, so while one waits (for S, for tensor memory,
+//              for P V) the other has arithmetic to issue.  The row's running maximum, to which O is scaled, is one
+//              word in shared memory that the groups hand to each other tile by tile.  At the end each thread reads
+//              half of O's columns of its row, divides by the sum and stores.
 // The running maximum used for the exponentials is only raised when a tile's maximum exceeds it by more than 8
 // (a factor 256, harmless in bfloat16/32-bit accumulators); only then is O in tensor memory rescaled.  All of S, the
 // softmax and the sums are 32-bit.  Every wait is bounded; on a timeout an error code is recorded and the block
@@ -28,7 +33,7 @@ namespace {
 
 constexpr int BMQ = 128;           // query rows per block
 constexpr int BKV = 64;            // keys per tile
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;
 constexpr int SOFTMAX_THREADS = 256;
 constexpr long WAIT_LIMIT = 20L * 1000 * 1000;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -99,6 +104,12 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// max(a, b, c) in one instruction (three-input maximum of sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
 __device__ __forceinline__ float rcp_fast(float x) {
@@ -219,11 +230,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint64_t* k_free = bars + 5;                            // [2] commit after Q K^T of the tile in that stage
   uint64_t* v_free = bars + 7;                            // [2] commit after P V of the tile in that stage
   uint64_t* s_full = bars + 9;                            // [2] commit after Q K^T
-  uint64_t* p_full = bars + 11;                           // all softmax threads
-  uint64_t* pv_done = bars + 12;                          // commit after P V
-  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  uint64_t* p_full = bars + 11;                           // the softmax group of the tile
+  uint64_t* pv_done = bars + 12;                          // [2] commit after P V of tile i on barrier i % 2: a group waits
+                                                          // for every other tile, and a parity tells only one phase back
+  uint64_t* m_done = bars + 14;                           // [2] group g has published the row maxima after its tile
+  uint64_t* s_free = bars + 16;                           // [2] group g has taken its scores out of S buffer g
+  uint32_t* tmem_slot = (uint32_t*)(bars + 18);
   volatile int* s_abort = (volatile int*)(tmem_slot + 1);
-  float* s_max = (float*)(tmem_slot + 2);                 // [2 tile parities][2 halves][128 rows]; later [2][128] sums
+  float* s_max = (float*)(tmem_slot + 2);                 // [128 rows] the running maximum O is scaled to; then [2][128] sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Blocks are numbered (tile, run, head) with the head fastest and the last tile first: tiles late in a request have
@@ -241,8 +255,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_free[s], 1); mbar_init(&v_free[s], 1);
       mbar_init(&s_full[s], 1);
     }
-    mbar_init(p_full, SOFTMAX_THREADS);
-    mbar_init(pv_done, 1);
+    mbar_init(p_full, SOFTMAX_THREADS / 2);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
+    mbar_init(&m_done[0], SOFTMAX_THREADS / 2);
+    mbar_init(&m_done[1], SOFTMAX_THREADS / 2);
+    mbar_init(&s_free[0], SOFTMAX_THREADS / 2);
+    mbar_init(&s_free[1], SOFTMAX_THREADS / 2);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -255,8 +274,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   kf_pdl_trigger();
-  kf_pdl_wait();
 
+  // the step's integers were written before the step's first kernel: read before the grid dependency is waited for
   const int req = row_req[row0];
   const int pos0 = positions[row0];
   int kt_first;
@@ -266,9 +285,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int per_part = (n_tiles_all + my_parts - 1) / my_parts;
   const int kt_begin = kt_first + part * per_part * BKV;
   const int n_tiles = idle ? 0 : max(0, min(per_part, n_tiles_all - part * per_part));
+  kf_pdl_wait();                                          // Q, and the keys and values of this step's rows, come from the kernel before
 
   if (warp == 8) {
-    // ---- TMA producer --------------------------------------------------------------------------------------
+    // ---- TMA producer of Q and the keys ----------------------------------------------------------------------
     if (lane == 0 && n_tiles > 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
@@ -282,24 +302,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         int page = tab[kt / page_size];
         if (page < 0) page = 0;                            // a page already given back: every key of it is masked
         const int krow = ((page * 2 + 0) * nkv + kvh) * page_size + (kt % page_size);
-        const int vrow = krow + nkv * page_size;
         if (i >= 2 && !mbar_wait(&k_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
         mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
         for (int j = 0; j < NSUB; ++j) tma_load_2d(sK + s * KV_BYTES + j * (BKV * 128), &tm_kv, &k_full[s], j * 64, krow);
+      }
+    }
+  } else if (warp == 11) {
+    // ---- TMA producer of the values: a thread of its own, so that the next keys never wait for a value stage -----------
+    if (lane == 0 && n_tiles > 0) {
+      const int* tab = table + (size_t)req * table_stride;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i & 1;
+        const int kt = kt_begin + i * BKV;
+        int page = tab[kt / page_size];
+        if (page < 0) page = 0;
+        const int vrow = ((page * 2 + 1) * nkv + kvh) * page_size + (kt % page_size);
         if (i >= 2 && !mbar_wait(&v_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
         mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
         for (int j = 0; j < NSUB; ++j) tma_load_2d(sV + s * KV_BYTES + j * (BKV * 128), &tm_kv, &v_full[s], j * 64, vrow);
       }
     }
-  } else if (warp == 9) {
-    // ---- MMA issuer ----------------------------------------------------------------------------------------
+  } else if (warp == 10) {
+    // ---- issuer of S = Q K^T -------------------------------------------------------------------------------
     if (lane == 0 && n_tiles > 0) {
-      const uint32_t id_s = idesc(BKV, 0), id_o = idesc(D, 1);
-      bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
-      auto issue_s = [&](int i) {                          // S_i = Q K_i^T into S buffer i & 1
+      const uint32_t id_s = idesc(BKV, 0);
+      bool ok = mbar_wait(q_full, 0);
+      for (int i = 0; i < n_tiles && ok; ++i) {
         const int s = i & 1;
+        ok = mbar_wait(&k_full[s], (i >> 1) & 1) && (i < 2 || mbar_wait(&s_free[s], ((i >> 1) - 1) & 1));
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int j = 0; j < NSUB; ++j) {
@@ -310,15 +343,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         umma_commit(&s_full[s]);
         umma_commit(&k_free[s]);
-      };
-      if (ok) issue_s(0);
+      }
+      if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 2); *s_abort = 1; }
+    }
+  } else if (warp == 9) {
+    // ---- issuer of O += P V -----------------------------------------------------------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t id_o = idesc(D, 1);
+      bool ok = true;
       for (int i = 0; i < n_tiles && ok; ++i) {
         const int s = i & 1;
-        if (i + 1 < n_tiles) {
-          ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
-          if (ok) issue_s(i + 1);
-        }
-        ok = ok && mbar_wait(&v_full[s], (i >> 1) & 1) && mbar_wait(p_full, i & 1);
+        ok = mbar_wait(&v_full[s], (i >> 1) & 1) && mbar_wait(p_full, i & 1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -328,13 +363,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           umma(tmem_base + O_COL, da, db, id_o, (i | k) ? 1u : 0u);
         }
         umma_commit(&v_free[s]);
-        umma_commit(pv_done);
+        umma_commit(&pv_done[i & 1]);
       }
       if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 2); *s_abort = 1; }
     }
   } else {
-    // ---- softmax and epilogue: two threads per query row, each with half of a tile's keys and half of O's columns ----------
-    const int half = warp >> 2, wq = warp & 3;             // warps 0-3: keys 0..31 of a tile; warps 4-7: keys 32..63
+    // ---- softmax and epilogue: group `grp` takes every other key tile; one thread per query row -----------------------
+    const int grp = warp >> 2, wq = warp & 3;
+    const int half = grp;                                  // in the epilogue: which half of O's columns this thread stores
     const int r = wq * 32 + lane;                          // row of the tile = tensor-memory lane
     const int prow = pos0 + r;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
@@ -343,105 +379,124 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const float c3 = softcap * LOG2E;
     const float ct = softcap > 0.f ? scale / softcap : 0.f;
     const float c4 = c3 * ct;
-    constexpr int HC = D / 2;                              // O columns of this thread
-    float m_used = -INFINITY, l_sum = 0.f;                 // the maximum is the row's; the sum is this half's
+    constexpr int HC = D / 2;                              // O columns of this thread in the epilogue
+    float m_mine = -INFINITY, l_sum = 0.f;                 // this group's sum of exponentials, scaled to 2^-m_mine
     bool ok = true;
-    // Every softmax thread runs every turn of this loop and meets the others at its barrier, also after a wait has run
-    // out (the waits are then skipped and the numbers are garbage that nobody stores): nobody is left at a barrier.
-    for (int i = 0; i < n_tiles; ++i) {
-      const int sb = i & 1;
-      ok = ok && mbar_wait(&s_full[sb], (i >> 1) & 1);
+    // A thread runs every turn of its loop and arrives at every barrier of it, also after a wait has run out (the waits
+    // are then skipped and the numbers are garbage that nobody stores): nobody is left waiting for it.
+    for (int i = grp; i < n_tiles; i += 2) {
+      ok = ok && mbar_wait(&s_full[grp], (i >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kt = kt_begin + i * BKV + half * 32;       // first key of this thread's half
-      float sv[32];
-      tmem_ld32(lane_addr + sb * S_COLS + half * 32, sv);
+      const int kt = kt_begin + i * BKV;                   // first key of the tile
+      float sv[64];
+      tmem_ld64(lane_addr + grp * S_COLS, sv);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&s_free[grp]);                           // the buffer may take the scores of tile i + 2
       // Scores in base-2 units: s2 = log2(e) * cap * tanh(scale * s / cap) = c3 - 2 c3 / (exp2(s * c1) + 1), or
-      // s * c0 without a cap.  A half tile that every row of this warp sees whole skips the mask.
-      const bool whole = (kt + 31 <= pos0 + wq * 32) && (window <= 0 || pos0 + wq * 32 + 31 - kt < window);
-      float m_tile = -INFINITY;
+      // s * c0 without a cap.  A tile that every row of this warp sees whole skips the mask.
+      const bool whole = (kt + BKV - 1 <= pos0 + wq * 32) && (window <= 0 || pos0 + wq * 32 + 31 - kt < window);
       if (softcap > 0.f) {
-        // A cap is chosen beyond what scores usually reach: while every score of this warp's half tile is within it
+        // A cap is chosen beyond what scores usually reach: while every score of this warp's tile is within it
         // (|scale * s / cap| <= 1), tanh is a polynomial on the packed 32-bit pipe; otherwise it goes through exp2 and
         // 1 / x on the special-function unit, which bounds the tile with three of its operations per score.
-        float amax = 0.f;
+        float am[4] = {0.f, 0.f, 0.f, 0.f};               // four chains: a single one is 64 dependent operations
 #pragma unroll
-        for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fabsf(sv[c]));
+        for (int c = 0; c < BKV; c += 8) {
+          am[0] = max3(am[0], fabsf(sv[c]), fabsf(sv[c + 1])); am[1] = max3(am[1], fabsf(sv[c + 2]), fabsf(sv[c + 3]));
+          am[2] = max3(am[2], fabsf(sv[c + 4]), fabsf(sv[c + 5])); am[3] = max3(am[3], fabsf(sv[c + 6]), fabsf(sv[c + 7]));
+        }
+        const float amax = fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3]));
         if (__all_sync(0xffffffffu, amax * ct <= 1.f)) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
+          for (int c = 0; c < BKV; c += 2) {
             const float2 y = capped2(make_float2(sv[c], sv[c + 1]), ct, c4);
             sv[c] = y.x, sv[c + 1] = y.y;
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
+          for (int c = 0; c < BKV; ++c) sv[c] = fmaf(-2.f * c3, rcp_fast(ex2_fast(sv[c] * c1) + 1.f), c3);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] *= c0;
+        for (int c = 0; c < BKV; ++c) sv[c] *= c0;
       }
       if (!whole) {
+        // key kt + c is seen by this row iff first <= c <= last: one bit per key, tested with constant masks
+        const int last = prow - kt;                                        // >= 64: all of the tile
+        const int first = window > 0 ? last - window + 1 : 0;              // <= 0: from the tile's first key
+        unsigned long long seen = last < 0 ? 0ull : (last >= 63 ? ~0ull : ((2ull << last) - 1ull));
+        if (first > 0) seen &= first >= 64 ? 0ull : ~((1ull << first) - 1ull);
+        const uint32_t seen_lo = (uint32_t)seen, seen_hi = (uint32_t)(seen >> 32);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const int j = kt + c;
-          const bool seen = j <= prow && (window <= 0 || prow - j < window);
-          sv[c] = seen ? sv[c] : -INFINITY;
+          sv[c] = (seen_lo & (1u << c)) ? sv[c] : -INFINITY;
+          sv[32 + c] = (seen_hi & (1u << c)) ? sv[32 + c] : -INFINITY;
         }
       }
+      float mt[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, sv[c]);
-      // the row's maximum over both halves (slots alternate with the tile's parity, so one barrier per tile is enough)
-      s_max[(sb * 2 + half) * BMQ + r] = m_tile;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      m_tile = fmaxf(m_tile, s_max[(sb * 2 + (half ^ 1)) * BMQ + r]);
+      for (int c = 0; c < BKV; c += 8) {
+        mt[0] = max3(mt[0], sv[c], sv[c + 1]); mt[1] = max3(mt[1], sv[c + 2], sv[c + 3]);
+        mt[2] = max3(mt[2], sv[c + 4], sv[c + 5]); mt[3] = max3(mt[3], sv[c + 6], sv[c + 7]);
+      }
+      const float m_tile = fmaxf(fmaxf(mt[0], mt[1]), fmaxf(mt[2], mt[3]));
+      // the maximum O is scaled to after tile i - 1, from the other group; this tile's goes back the same way
+      if (i > 0) ok = ok && mbar_wait(&m_done[grp ^ 1], ((i - 1) >> 1) & 1);
+      const float m_used = i > 0 ? s_max[r] : -INFINITY;
       const bool raise = m_tile > m_used + RESCALE_STEP;   // also true for the first finite maximum
       const float m_new = raise ? m_tile : m_used;
-      const float corr = raise ? ex2_fast(m_used - m_new) : 1.f;   // exp2(-inf) = 0 when nothing was accumulated yet
+      s_max[r] = m_new;
+      mbar_arrive(&m_done[grp]);
+      const float corr = raise ? ex2_fast(m_used - m_new) : 1.f;   // for O; exp2(-inf) = 0 when nothing was accumulated yet
       const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen nothing yet: exp2(-inf - 0) = 0
-      float l_add = 0.f;
-      uint32_t pk[16];
+      const float l_corr = (m_mine == m_new) ? 1.f : ex2_fast(m_mine - m_new);   // this group's sum follows the maximum
+      float2 la[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // four chains of packed sums; the order is fixed
+      const float2 neg_m = make_float2(-m_sub, -m_sub);
+      uint32_t pk[BKV / 2];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float p0 = ex2_fast(sv[c] - m_sub);
-        const float p1 = ex2_fast(sv[c + 1] - m_sub);
-        l_add += p0 + p1;
-        const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+      for (int c = 0; c < BKV; c += 2) {
+        const float2 x = __fadd2_rn(make_float2(sv[c], sv[c + 1]), neg_m);
+        const float2 pp = make_float2(ex2_fast(x.x), ex2_fast(x.y));
+        la[(c >> 1) & 3] = __fadd2_rn(la[(c >> 1) & 3], pp);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(pp.x, pp.y);
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
       }
-      l_sum = l_sum * corr + l_add;
-      m_used = m_new;
+      l_sum = l_sum * l_corr + (((la[0].x + la[0].y) + (la[1].x + la[1].y)) + ((la[2].x + la[2].y) + (la[3].x + la[3].y)));
+      m_mine = m_new;
       if (i > 0) {                                          // P V of the previous tile must be done: O is at rest, P is free
-        ok = ok && mbar_wait(pv_done, (i - 1) & 1);
+        ok = ok && mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, raise)) {              // rescale this thread's half of O (all lanes of the warp take part)
+        if (__any_sync(0xffffffffu, raise)) {              // rescale this row of O (all lanes of the warp take part)
 #pragma unroll 1
-          for (int c = 0; c < HC; c += 16) {
+          for (int c = 0; c < D; c += 16) {
             float o[16];
-            tmem_ld16(lane_addr + O_COL + half * HC + c, o);
+            tmem_ld16(lane_addr + O_COL + c, o);
 #pragma unroll
             for (int e = 0; e < 16; ++e) o[e] *= corr;
-            tmem_st16(lane_addr + O_COL + half * HC + c, o);
+            tmem_st16(lane_addr + O_COL + c, o);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // this half of the P row -> shared memory, K-major with the 128-byte swizzle (chunk index XOR row % 8)
+      // the P row -> shared memory, K-major with the 128-byte swizzle (chunk index XOR row % 8)
       uint8_t* prow_ptr = sP + r * 128;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int ch = half * 4 + q;
+      for (int q = 0; q < 8; ++q) {
         const uint4 v = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-        *reinterpret_cast<uint4*>(prow_ptr + ((ch ^ (r & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(prow_ptr + ((q ^ (r & 7)) << 4)) = v;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(p_full);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
+    if (ok && n_tiles > 0) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
     if (!ok) { atomicExch(error_flag, ERR_ATTN_WAIT + 3); *s_abort = 1; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // the row's sum is the two halves' sums (both were scaled by the same maxima); every softmax thread reaches this
-    asm volatile("bar.sync 2, 256;" ::: "memory");          // the maxima in s_max have been read by everyone
+    // the row's sum is the two groups' sums, both brought to the last maximum; every softmax thread reaches this
+    asm volatile("bar.sync 2, 256;" ::: "memory");          // every tile's maximum has been published
+    const float m_used = n_tiles > 0 ? s_max[r] : -INFINITY;
+    l_sum = (m_mine == m_used) ? l_sum : l_sum * ex2_fast(m_mine - m_used);
+    asm volatile("bar.sync 2, 256;" ::: "memory");          // ... and read by both threads of the row
     s_max[half * BMQ + r] = l_sum;
     asm volatile("bar.sync 2, 256;" ::: "memory");
     l_sum = s_max[r] + s_max[BMQ + r];
