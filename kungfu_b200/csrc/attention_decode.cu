@@ -64,9 +64,10 @@ constexpr int MERGE_MAX_HEADS = 16;
 constexpr int MERGE_MAX_SPLITS = 64;
 
 // The block that arrived last merges the splits of its heads.  Loads from L2 are the whole cost here, so they are
-// made independent of one another: first every (head, split) pair's maximum is fetched by a thread of its own, a
-// warp per head turns them into weights exp(m_s - m) / l in shared memory, and then every thread sums four
-// elements over the splits with eight 16-byte loads in flight.  Splits are summed in index order.
+// made independent of one another.  Up to eight splits: a thread asks for the maxima, the sums and its four elements of
+// every split at once (one round trip) and weighs them itself.  More: first every (head, split) pair's maximum is
+// fetched by a thread of its own, a warp per head turns them into weights exp(m_s - m) / l in shared memory, and then
+// every thread sums four elements over the splits with eight 16-byte loads in flight.  Splits are summed in index order.
 template <int D, bool BASE2>
 __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, size_t first_record, int n_heads,
                                              int n_splits, __nv_bfloat16* __restrict__ o_first) {
@@ -74,6 +75,40 @@ __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, 
   __shared__ float s_w[MERGE_MAX_HEADS][MERGE_MAX_SPLITS];
   const float* rec0 = partial + first_record * PS;              // record (h, s) at rec0 + (h * n_splits + s) * PS
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
+  if (n_splits <= 8) {
+    for (int e = tid; e < n_heads * (D / 4); e += blockDim.x) {
+      const int h = e / (D / 4), i4 = e - h * (D / 4);
+      const float* src = rec0 + (size_t)h * n_splits * PS;
+      float ms[8], ls[8];
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = u < n_splits;
+        const float* rec = src + (size_t)(in ? u : 0) * PS;
+        ms[u] = in ? __ldcg(rec + D) : -INFINITY;
+        ls[u] = in ? __ldcg(rec + D + 1) : 0.f;
+        v[u] = in ? __ldcg(reinterpret_cast<const float4*>(rec + i4 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) m = fmaxf(m, ms[u]);
+      float l = 0.f;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float c = (ms[u] == -INFINITY) ? 0.f : (BASE2 ? exp2f(ms[u] - m) : expf(ms[u] - m));
+        l += ls[u] * c;
+        a.x += v[u].x * c; a.y += v[u].y * c; a.z += v[u].z * c; a.w += v[u].w * c;
+      }
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv), hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o_first + (size_t)h * D + i4 * 4) = packed;
+    }
+    return;
+  }
   for (int idx = tid; idx < n_heads * n_splits; idx += blockDim.x) {
     const int h = idx / n_splits, sp = idx - h * n_splits;
     s_w[h][sp] = __ldcg(rec0 + (size_t)idx * PS + D);
