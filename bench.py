@@ -300,11 +300,12 @@ def measure_mixed(torch, args, cfg, runner) -> dict:
     from kungfu_b200.engine.scheduler import Request
     from kungfu_b200.sampling import STATE_WORDS, Sampling, pack_state
     B, ctx_len, vocab = args.batch, args.context, cfg.vocab_size
-    portion = 512
     out = {}
     states = torch.zeros((runner.cache.max_requests, STATE_WORDS), dtype=torch.int32, device=runner.device)
     states[:] = torch.from_numpy(pack_state(Sampling(temperature=0.0), 1)).to(runner.device)
-    for name, n_dec in (("decode8_portion512", B), ("portion512", 0)):
+    # the scheduler's budget counts decode rows, so with a budget of 512 a mixed step has 512 rows in all (the second case:
+    # two whole 256-token tiles); the first case is 520 rows, a third tile for eight of them
+    for name, n_dec, portion in ((f"decode{B}_portion512", B, 512), (f"decode{B}_portion{512 - B}", B, 512 - B), ("portion512", 0, 512)):
         rids = [f"m{k}" for k in range(n_dec)]
         for r in rids:
             fill_cache(runner, r, ctx_len - 16)

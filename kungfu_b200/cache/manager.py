@@ -75,6 +75,7 @@ def host_library():
         lib.kf_sched_create.restype = vp
         lib.kf_sched_create.argtypes = [vp, ci, ci]
         lib.kf_sched_destroy.argtypes = [vp]
+        lib.kf_sched_pad_decode_rows.argtypes = [vp, ci]
         lib.kf_sched_add.argtypes = [vp, i64, ci, ci, ci]
         lib.kf_sched_adopt.argtypes = [vp, i64, ci, ci, ci, ci]
         lib.kf_sched_forget.argtypes = [vp, i64]

@@ -437,6 +437,9 @@ struct SPortion {
 struct Sched {
   Cache* cache = nullptr;
   int max_batch_tokens = 0, max_requests = 0;
+  // 1: a step's decode rows count towards the budget as the next power of two (the step function pads them to that
+  // when it replays steps from captured graphs), so that decode rows and prompt rows together stay within the budget
+  int pad_decode_rows = 0;
   std::deque<int64_t> waiting;
   std::vector<int64_t> running;                      // in order of admission
   std::unordered_map<int64_t, SReq> reqs;
@@ -575,6 +578,11 @@ struct Sched {
         }
         i = (size_t)(std::find(running.begin(), running.end(), key) - running.begin());
       }
+      if (pad_decode_rows && !plan.empty()) {
+        int padded = 1;
+        while (padded < (int)plan.size()) padded *= 2;
+        budget = std::min(budget, max_batch_tokens - padded);
+      }
       // 2. prompt portions of running requests
       for (const int64_t key : running) {
         if (budget <= 0) break;
@@ -637,6 +645,7 @@ KF_HOST_API void* kf_sched_create(void* cache, int max_batch_tokens, int max_req
   return s;
 }
 KF_HOST_API void kf_sched_destroy(void* h) { delete (Sched*)h; }
+KF_HOST_API void kf_sched_pad_decode_rows(void* h, int on) { ((Sched*)h)->pad_decode_rows = on ? 1 : 0; }
 
 KF_HOST_API int kf_sched_add(void* h, int64_t key, int prompt_len, int out_len, int max_tokens) {
   Sched* s = (Sched*)h;

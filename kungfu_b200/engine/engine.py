@@ -80,7 +80,8 @@ class Engine:
                          weight_bytes=model.weight_bytes(), cache_bytes_per_token=self.runner.cache.bytes_per_token(),
                          pool_pages=",".join(str(g.pages) for g in plan.groups), ctx=n_ctx,
                          load_s=f"{time.time() - t0:.2f}")
-        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=batch, max_requests=parallel)
+        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=batch, max_requests=parallel,
+                                   pad_decode_rows=bool(getattr(self.runner, "cuda_graphs", False)))
         self._next_id = 0
         self.requests: dict[Hashable, Request] = {}
         self._t_start: dict = {}

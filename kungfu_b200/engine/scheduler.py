@@ -89,7 +89,7 @@ class Scheduler:
 
     _FINISH = {1: "eos", 2: "length", 3: "context"}
 
-    def __init__(self, cache, *, max_batch_tokens: int = 512, max_requests: int | None = None):
+    def __init__(self, cache, *, max_batch_tokens: int = 512, max_requests: int | None = None, pad_decode_rows: bool = False):
         self.cache = cache
         self.max_batch_tokens = int(max_batch_tokens)
         self.max_requests = int(max_requests if max_requests is not None else cache.max_requests)
@@ -98,6 +98,10 @@ class Scheduler:
         self.finished: list[Request] = []
         self._lib = cache._lib
         self._h = ctypes.c_void_p(self._lib.kf_sched_create(cache._h, self.max_batch_tokens, self.max_requests))
+        # decode rows count as their next power of two: what a step function that replays captured graphs pads them to, so
+        # that a step's rows (decode + prompt) stay within the budget and its products within the budget's tiles
+        self.pad_decode_rows = bool(pad_decode_rows)
+        self._lib.kf_sched_pad_decode_rows(self._h, int(self.pad_decode_rows))
         self._by_key: dict[int, Request] = {}
         self._key_of: dict[int, int] = {}         # id(request object) -> key
         cap = 4 * (self.max_requests + 8)

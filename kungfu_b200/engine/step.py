@@ -389,8 +389,10 @@ class Runner:
             d = 1
             while d < nd:
                 d *= 2
+        # decode and prompt rows TOGETHER are rounded up to the unit (a scheduler that pads its decode rows the same way hands
+        # out budget - d prompt rows, and the step's products then see exactly the budget's rows)
         unit = 64 if rows <= 512 else 128 if rows <= 1024 else 256
-        key = ("mixed", d, -(-rows // unit) * unit, 1 if len(rest) == 1 else 2 if len(rest) == 2 else 4)
+        key = ("mixed", d, -(-(d + rows) // unit) * unit - d, 1 if len(rest) == 1 else 2 if len(rest) == 2 else 4)
         held = {k[1] for k in self._graphs if isinstance(k, tuple) and isinstance(k[1], tuple)}
         return key if (key in held or len(held) < self.MAX_MIXED_GRAPHS) else None
 

@@ -171,6 +171,26 @@ def test_budget_cuts_prompts_and_decodes_first():
     assert c.free_pages() == [64, 64] and [r.finish_reason for r in s.finished] == ["length", "length"]
 
 
+@pytest.mark.parametrize("n_short,padded", [(1, 1), (3, 4), (4, 4), (5, 8)])
+def test_padded_decode_rows_count_as_their_power_of_two(n_short, padded):
+    """A step function that replays captured graphs pads a step's decode rows to a power of two; a scheduler told so
+    (`pad_decode_rows`) leaves that many rows out of the prompts' budget, so that decode and prompt rows together are the
+    budget: three decoding requests cost four rows, five cost eight."""
+    for pad in (False, True):
+        c = make_cache(n_pages=256, page=4, window=8, max_requests=8, max_context=400)
+        s = Scheduler(c, max_batch_tokens=32, max_requests=8, pad_decode_rows=pad)
+        for k in range(n_short):
+            s.add(Request(f"s{k}", [1, 2, 3], greedy(), max_tokens=50))
+        run_plan(s, s.schedule())                       # the short prompts; from now on they decode
+        s.add(Request("long", list(range(200)), greedy(), max_tokens=2))
+        for _ in range(3):
+            plan = s.schedule()
+            got = [(p.request.id, p.n) for p in plan]
+            assert got[:n_short] == [(f"s{k}", 1) for k in range(n_short)]
+            assert got[n_short:] == [("long", 32 - (padded if pad else n_short))], (pad, got)
+            run_plan(s, plan)
+
+
 def test_admission_waits_for_slots_and_pages():
     c = make_cache(n_pages=6, page=4, window=None, max_requests=2, max_context=64, state=False)
     s = Scheduler(c, max_batch_tokens=64, max_requests=2)
