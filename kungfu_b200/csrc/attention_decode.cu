@@ -66,8 +66,8 @@ constexpr int MERGE_MAX_SPLITS = 64;
 // The block that arrived last merges the splits of its heads.  Loads from L2 are the whole cost here, so they are
 // made independent of one another.  Up to eight splits: a thread asks for the maxima, the sums and its four elements of
 // every split at once (one round trip) and weighs them itself.  More: first every (head, split) pair's maximum is
-// fetched by a thread of its own, a warp per head turns them into weights exp(m_s - m) / l in shared memory, and then
-// every thread sums four elements over the splits with eight 16-byte loads in flight.  Splits are summed in index order.
+// and sum are fetched by a thread of its own, a warp per head turns them into weights exp(m_s - m) / l in shared memory,
+// and then every thread sums four elements over the splits with sixteen 16-byte loads in flight.  Splits are summed in index order.
 template <int D, bool BASE2>
 __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, size_t first_record, int n_heads,
                                              int n_splits, __nv_bfloat16* __restrict__ o_first) {
@@ -109,9 +109,11 @@ __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, 
     }
     return;
   }
+  __shared__ float s_l[MERGE_MAX_HEADS][MERGE_MAX_SPLITS];
   for (int idx = tid; idx < n_heads * n_splits; idx += blockDim.x) {
     const int h = idx / n_splits, sp = idx - h * n_splits;
     s_w[h][sp] = __ldcg(rec0 + (size_t)idx * PS + D);
+    s_l[h][sp] = __ldcg(rec0 + (size_t)idx * PS + D + 1);
   }
   __syncthreads();
   for (int h = warp; h < n_heads; h += n_warps) {
@@ -122,7 +124,7 @@ __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, 
     for (int sp = lane; sp < n_splits; sp += 32) {
       const float ms = s_w[h][sp];
       const float c = (ms == -INFINITY) ? 0.f : (BASE2 ? exp2f(ms - m) : expf(ms - m));
-      l += __ldcg(rec0 + ((size_t)h * n_splits + sp) * PS + D + 1) * c;
+      l += s_l[h][sp] * c;
       s_w[h][sp] = c;
     }
     // the sum over splits in a fixed order: lanes hold interleaved splits, the butterfly adds them the same way each time
@@ -136,21 +138,16 @@ __device__ __forceinline__ void merge_splits(const float* __restrict__ partial, 
     const int h = e / (D / 4), i4 = e - h * (D / 4);
     const float* src = rec0 + (size_t)h * n_splits * PS + i4 * 4;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    int sp = 0;
-    for (; sp + 8 <= n_splits; sp += 8) {
-      float4 v[8];
+    for (int sp = 0; sp < n_splits; sp += 16) {              // sixteen 16-byte loads in flight
+      float4 v[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * PS));
+      for (int u = 0; u < 16; ++u)
+        v[u] = sp + u < n_splits ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * PS)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float c = s_w[h][sp + u];
+      for (int u = 0; u < 16; ++u) {
+        const float c = sp + u < n_splits ? s_w[h][sp + u] : 0.f;
         a.x += v[u].x * c; a.y += v[u].y * c; a.z += v[u].z * c; a.w += v[u].w * c;
       }
-    }
-    for (; sp < n_splits; ++sp) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * PS));
-      const float c = s_w[h][sp];
-      a.x += v.x * c; a.y += v.y * c; a.z += v.z * c; a.w += v.w * c;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
     uint2 packed;
