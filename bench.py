@@ -3,7 +3,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--size 2b|9b|27b] [--layers L] [--batch B] [--context C] [--only-headline]
-    python bench.py --micro attention|gemm|products|reference   (kernels alone, JSON lines; for the summaries in profiles/)
+    python bench.py --micro attention|prompt-attention|gemm|products|reference
+                    (kernels alone, JSON lines; for the summaries in profiles/)
 
 A "step" is one decode step: every live request gets one token.  Default: the layer sizes of Gemma 2 2B, random
 bfloat16 weights, 8 requests at a context of 8192 tokens.  `value` is decoded tokens per second timed with CUDA events
@@ -514,6 +515,60 @@ def micro_attention() -> int:
     return 0
 
 
+def micro_prompt_attention() -> int:
+    """Prompt attention alone (8 heads / 4 kv heads of 256, softcap 50, page 64): whole prompts of 512 to 4,096 rows and a
+    512-row portion at context 8,192, each replayed from a CUDA graph of three launches over distinct pages; one JSON line
+    each with microseconds per launch and TFLOP/s."""
+    import math
+    import torch
+    from kungfu_b200 import api, ops
+
+    class View:
+        def __init__(self, pages, page_size):
+            self.pages, self.page_size, self.group, self.writes = pages, page_size, 0, False
+
+    class Ctx:
+        pass
+
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(0)
+    nh, nkv, d, page, copies = 8, 4, 256, 64, 3
+    scale = 1.0 / math.sqrt(d)
+    for T, past in ((512, 0), (1024, 0), (2048, 0), (4096, 0), (512, 7680)):
+        total = T + past
+        per_req = total // page
+        pages = torch.empty(copies * per_req, 2, nkv, page, d, device=device, dtype=torch.bfloat16).normal_(0.0, 0.5, generator=gen)
+        ctxs = []
+        for k in range(copies):
+            c = Ctx()
+            c.positions = torch.arange(past, total, dtype=torch.int32, device=device)
+            c.row_req = torch.zeros(T, dtype=torch.int32, device=device)
+            c.block_tables = [(torch.arange(per_req, dtype=torch.int32, device=device) + k * per_req).view(1, per_req).contiguous()]
+            c.n_rows = c.n_pre_rows = T
+            c.n_dec_rows = 0
+            c.dec_rows = None
+            c.pre_rows = torch.arange(T, dtype=torch.int32, device=device)
+            c.n_tiles, c.n_wide = T // 64, T // 128
+            c.tile_row0 = torch.arange(0, T, 64, dtype=torch.int32, device=device)
+            c.tile_nrows = torch.full((T // 64,), 64, dtype=torch.int32, device=device)
+            c.wide_row0 = torch.arange(0, T, 128, dtype=torch.int32, device=device)
+            c.wide_nrows = torch.full((T // 128,), 128, dtype=torch.int32, device=device)
+            c.max_kv_len = total
+            ctxs.append(c)
+        q = torch.randn(T, nh * d, device=device, generator=gen).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        view = View(pages, page)
+        us = _graph_us(torch, lambda: [ops.paged_attention(q, out, c, view, nh, nkv, d, scale, 50.0, None) for c in ctxs], copies)
+        flops = 4.0 * nh * d * (T * (T + 1) / 2 + T * past)
+        print(json.dumps({"micro": "prompt attention", "rows": T, "keys_before": past, "us_per_launch": round(us, 1),
+                          "tflops": round(flops / us / 1e6, 1)}), flush=True)
+        del pages
+    ops.raise_on_device_error()
+    return 0
+
+
 def micro_gemm() -> int:
     """One square bfloat16 product (8192 cubed) on the tensor-core kernel, timed with CUDA events; one JSON line."""
     import torch
@@ -751,10 +806,12 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
-    ap.add_argument("--micro", choices=["attention", "gemm", "products", "reference"], help="time kernels alone instead of the model step")
+    ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "reference"],
+                    help="time kernels alone instead of the model step")
     args = ap.parse_args()
     if args.micro:
-        return {"attention": micro_attention, "gemm": micro_gemm, "products": micro_products, "reference": micro_reference}[args.micro]()
+        return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
+                "products": micro_products, "reference": micro_reference}[args.micro]()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built "

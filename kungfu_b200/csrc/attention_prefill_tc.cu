@@ -675,8 +675,9 @@ KF_API void kf_set_attention_prefill_plan(int parts, int run_tiles) { g_forced_p
 #endif
 
 // Into how many runs the keys of a tile are cut, and how long a run may be (0: every tile gets `parts` runs).
-// Few blocks (tiles x heads fill less than half of the GPU): every tile is cut so that the blocks fill it; at most 8
-// runs, and never so many that a run of the longest tile has fewer than two 64-key tiles.
+// Few blocks (tiles x heads fill less than half of the GPU): every tile may be cut so that the blocks fill it; at most 8
+// runs, never so many that a run of the longest tile has fewer than two 64-key tiles, and only if the shorter loop
+// saves more than the partial rows and their merge cost.
 // About one block per SM and long tiles (a whole prompt of 2,048 tokens x 8 heads: the launch lasts as long as the tile
 // with the most keys, twice the average): cutting only the tiles longer than 1/2 or 5/8 of the longest in two
 // (kf_set_attention_prefill_plan(2, 16 or 20)) measured within +-0.5 % of uncut over the 26-layer step, three or four
@@ -691,7 +692,16 @@ KF_API int kf_attention_prefill_tc_plan(int n_tiles, int nh, int max_keys, int* 
   if (parts > 8) parts = 8;
   const int key_tiles = (max_keys + BKV - 1) / BKV;
   if (parts > key_tiles / 2) parts = key_tiles / 2;
-  return parts < 1 ? 1 : parts;
+  if (parts < 1) parts = 1;
+  // A key tile takes a block about 0.93 us; partial rows, their merge kernel and its launch about 11 us together.  Of the
+  // run counts that fill the GPU the one with the shortest estimate wins, so short prompts stay whole.
+  int best = 1;
+  float best_us = 0.93f * (float)key_tiles;
+  for (int p = 2; p <= parts; ++p) {
+    const float us = 0.93f * (float)((key_tiles + p - 1) / p) + 11.f;
+    if (us < best_us) { best_us = us; best = p; }
+  }
+  return best;
 }
 
 // q, out: [T, nh*d] bfloat16; pages: [n_pages, 2, nkv, page_size, d] bfloat16.  tile_row0/tile_nrows: tiles of up to 128

@@ -299,6 +299,25 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
+def test_prompt_attention_planner_cuts_only_what_repays(ops):
+    """The planner's choice of runs per tile: whole prompts stay whole (a second wave of blocks, or partial rows and their
+    merge, cost more than a short loop saves), a short portion at a long context is cut so that its blocks fill the GPU."""
+    import ctypes
+    lib = ops.library()
+
+    def plan(n_tiles, nh, max_keys):
+        run_tiles = ctypes.c_int(-1)
+        return lib.kf_attention_prefill_tc_plan(n_tiles, nh, max_keys, ctypes.byref(run_tiles)), run_tiles.value
+
+    assert plan(16, 8, 2048) == (1, 0)          # 128 blocks: one wave
+    assert plan(4, 8, 512) == (1, 0)            # 32 blocks of at most 8 key tiles: nothing to gain
+    assert plan(8, 8, 1024) == (1, 0)
+    parts, run_tiles = plan(4, 8, 8192)         # 512 rows at context 8192: 128 key tiles per block
+    assert parts == 4 and run_tiles == 0
+    assert plan(1, 8, 32768)[0] == 8            # one tile at a very long context: the most runs there are
+    assert plan(1, 8, 100) == (1, 0)
+
+
 @pytest.mark.parametrize("nh,nkv,d,window", [(8, 4, 256, None), (4, 1, 128, 300), (6, 2, 64, None)])
 @pytest.mark.parametrize("lens", [[700], [2048], [130, 513, 64]])
 def test_prompt_attention_with_keys_cut_into_runs(ops, nh, nkv, d, window, lens):
@@ -316,14 +335,14 @@ def test_prompt_attention_with_keys_cut_into_runs(ops, nh, nkv, d, window, lens)
                torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), [], list(range(len(rows))))
     outs = []
     for split in (True, False):
-        ops.split_prompt_keys = split
+        ops.prefill_plan_override = (3, 0) if split else (1, 0)     # three runs per tile, whatever the planner would choose
         try:
             out = torch.full((len(rows), nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
             before = ops.launch_count()
             ops.paged_attention(q.view(len(rows), nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, 50.0, window)
             outs.append((out, ops.launch_count() - before))
         finally:
-            ops.split_prompt_keys = True
+            ops.prefill_plan_override = None
     ops.raise_on_device_error()
     assert outs[0][1] == 2 and outs[1][1] == 1, "cut into runs: the attention kernel and the merge"
     ref = torch.stack([_attn_ref(q[i], ks[r], vs[r], p, nh, nkv, scale, 50.0, window) for i, (r, p) in enumerate(rows)])
