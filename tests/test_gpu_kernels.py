@@ -299,6 +299,45 @@ def test_decode_attention(ops, nh, nkv, d, P, window, cap, mixed, tensor_cores):
     assert rel_err(out.view(len(rows), nh, d), ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("nh,nkv,d", [(2, 1, 256), (4, 2, 128), (2, 2, 64)])
+@pytest.mark.parametrize("shape", ["rising", "falling", "sawtooth"])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prompt_attention_when_the_running_maximum_moves(ops, nh, nkv, d, shape, window):
+    """The tcgen05 prompt kernel keeps one running maximum per row that its two softmax groups hand to each other tile by
+    tile, rescales O only when the maximum grows by more than 2^8, and carries each group's sum along.  Scores that rise
+    by about 12 nats per 64-key tile raise the maximum (and rescale O) at every tile of both groups; falling scores never
+    raise it after the first tile, so late tiles add weights near 2^-400 (flushed to zero) to a sum made early; a sawtooth
+    mixes both.  No cap (a cap would flatten the differences), with and without a window, against float64."""
+    P, n = 64, 1100
+    g = torch.Generator().manual_seed(77)
+    pages, table, ks, vs = _paged_setup(torch.bfloat16, nh, nkv, d, P, [n], seed=78)
+    j = torch.arange(n, dtype=torch.float32)
+    ramp = {"rising": j * 0.19, "falling": (n - j) * 0.19, "sawtooth": (j % 150) * 0.9}[shape]
+    # the first coordinate of every key carries the ramp; queries have 1 there, so the score is ramp + small noise
+    k = (torch.randn(n, nkv, d, generator=g) * 0.05)
+    k[:, :, 0] = (ramp / (1.0 / math.sqrt(d))).unsqueeze(1)
+    k = k.to(torch.bfloat16)
+    ks[0] = k
+    for i in range(-(-n // P)):
+        m = min(P, n - i * P)
+        pages[table[0, i], 0, :, :m] = k[i * P:i * P + m].transpose(0, 1)
+    rows = [(0, p) for p in range(n)]
+    q = torch.randn(n, nh, d, generator=g) * 0.05
+    q[:, :, 0] = 1.0
+    q = q.to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ctx = _Ctx(torch.arange(n, dtype=torch.int32, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV), table.to(DEV), [],
+               list(range(n)))
+    out = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.view(n, nh * d).to(DEV), out, ctx, _View(pages.to(DEV), P), nh, nkv, d, scale, 0.0, window)
+    ops.raise_on_device_error()
+    pick = sorted(set(range(0, n, 11)) | set(range(n - 70, n)) | set(range(0, 70)))
+    ref = torch.stack([_attn_ref(q[i], ks[0], vs[0], i, nh, nkv, scale, 0.0, window) for i in pick])
+    got = out.view(n, nh, d)[pick]
+    assert not torch.isnan(got.float()).any()
+    assert rel_err(got, ref) < 1e-2
+
+
 def test_prompt_attention_planner_cuts_only_what_repays(ops):
     """The planner's choice of runs per tile: whole prompts stay whole (a second wave of blocks, or partial rows and their
     merge, cost more than a short loop saves), a short portion at a long context is cut so that its blocks fill the GPU."""
