@@ -581,7 +581,8 @@ struct Sched {
       if (pad_decode_rows && !plan.empty()) {
         int padded = 1;
         while (padded < (int)plan.size()) padded *= 2;
-        budget = std::min(budget, max_batch_tokens - padded);
+        // (only while the padded rows leave at least half of the budget: prompts must not starve behind many decoders)
+        if (2 * padded <= max_batch_tokens) budget = std::min(budget, max_batch_tokens - padded);
       }
       // 2. prompt portions of running requests
       for (const int64_t key : running) {

@@ -191,6 +191,20 @@ def test_padded_decode_rows_count_as_their_power_of_two(n_short, padded):
             run_plan(s, plan)
 
 
+def test_padding_never_starves_prompts():
+    """Five decoding requests under a budget of 8 would be padded to 8 rows and leave nothing: padding then stands back."""
+    c = make_cache(n_pages=256, page=4, window=8, max_requests=8, max_context=400)
+    s = Scheduler(c, max_batch_tokens=8, max_requests=8, pad_decode_rows=True)
+    for k in range(5):
+        s.add(Request(f"s{k}", [1, 2], greedy(), max_tokens=50))
+    run_plan(s, s.schedule())
+    run_plan(s, s.schedule())
+    run_plan(s, s.schedule())                           # all five decode by now
+    s.add(Request("long", list(range(100)), greedy(), max_tokens=2))
+    plan = s.schedule()
+    assert [(p.request.id, p.n) for p in plan][-1] == ("long", 3)
+
+
 def test_admission_waits_for_slots_and_pages():
     c = make_cache(n_pages=6, page=4, window=None, max_requests=2, max_context=64, state=False)
     s = Scheduler(c, max_batch_tokens=64, max_requests=2)
