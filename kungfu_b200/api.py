@@ -7,7 +7,6 @@ file, finds the architecture by the name the file gives and builds the model
 from __future__ import annotations
 
 import os
-from typing import Sequence
 
 import torch
 

@@ -53,7 +53,6 @@ def _engine(args, parallel: int = 1):
 def cmd_inspect(args) -> int:
     from . import registry
     from .api import load_config
-    from .parts.base import PagedKV
     from .weights.safetensors_io import open_model_tensors
     from .config.base import ConfigError
     from .registry import UnknownArchitecture

@@ -16,7 +16,7 @@ import torch
 from .. import events as _events
 from .. import ops
 from ..sampling.sampler import STATE_WORDS, Sampling, pack_state
-from .scheduler import Portion, Request, Scheduler
+from .scheduler import Request, Scheduler
 from .step import Runner, StepEntry
 
 
