@@ -129,6 +129,7 @@ constexpr int ST_WORDS = 272, ST_RNG = 0, ST_TEMP = 2, ST_TOP_P = 3, ST_MIN_P = 
 constexpr int CAND = 64;               // candidates kept per slice and per row (reference: TOP = 64, session.rs:80)
 constexpr int SLICE = 4096;            // columns per block of the first kernel
 constexpr int SL_THREADS = 256;
+constexpr int SL_CAND_MAX = 1024;      // keys of a slice that can still be among its 64 largest, after the bound (a list in shared memory)
 constexpr int MG_THREADS = 1024;        // the second kernel: one block per row, its loads from L2 are the cost
 
 __device__ __forceinline__ float st_f(const int* st, int w) { return __int_as_float(st[w]); }
@@ -307,14 +308,42 @@ sample_slices_kernel(const float* __restrict__ logits, int V, int n_slices, cons
     }
     __syncthreads();
   }
-  const unsigned long long kth = select_key(keys, SLICE, CAND, hist, &sh_prefix, &sh_need);
+  // The slice's 64 largest keys.  A walk over all 4,096 keys is most of this kernel's time, so first a bound: every thread
+  // takes the largest of its sixteen keys; the 64th largest of those 256 is reached by at least 64 keys of the slice, so
+  // only keys that reach it can be among the 64 largest.  Usually that leaves a hundred or two, and the exact walk runs
+  // over them; if it leaves more than the list holds (keys in falling order thread by thread), over everything.
+  __shared__ unsigned long long cand[SL_CAND_MAX];
+  unsigned long long mine[SLICE / SL_THREADS], lmax = 0ull;
+#pragma unroll
+  for (int j = 0; j < SLICE / SL_THREADS; ++j) { mine[j] = keys[tid + j * SL_THREADS]; lmax = mine[j] > lmax ? mine[j] : lmax; }
+  cand[tid] = lmax;                                       // SL_CAND_MAX >= SL_THREADS
   if (tid == 0) sh_count = 0;
   __syncthreads();
-  for (int i = tid; i < SLICE; i += SL_THREADS) {
-    const unsigned long long k = keys[i];
+  const unsigned long long bound = select_key(cand, SL_THREADS, CAND, hist, &sh_prefix, &sh_need);   // 0: fewer than 64 non-empty threads
+  __syncthreads();
+  int n_mine = 0;
+#pragma unroll
+  for (int j = 0; j < SLICE / SL_THREADS; ++j) n_mine += (mine[j] != 0ull && mine[j] >= bound) ? 1 : 0;
+  int at = n_mine ? atomicAdd(&sh_count, n_mine) : 0;
+  __syncthreads();
+  const int n_cand = sh_count;
+  const bool listed = n_cand <= SL_CAND_MAX;
+  if (listed) {
+#pragma unroll
+    for (int j = 0; j < SLICE / SL_THREADS; ++j)
+      if (mine[j] != 0ull && mine[j] >= bound) cand[at++] = mine[j];
+  }
+  __syncthreads();
+  const unsigned long long* pool = listed ? cand : keys;
+  const int n_pool = listed ? n_cand : SLICE;
+  const unsigned long long kth = select_key(pool, n_pool, CAND, hist, &sh_prefix, &sh_need);
+  if (tid == 0) sh_count = 0;
+  __syncthreads();
+  for (int i = tid; i < n_pool; i += SL_THREADS) {
+    const unsigned long long k = pool[i];
     if (k != 0ull && k >= kth) {                          // kth = 0: fewer than 64 columns, all of them
-      const int at = atomicAdd(&sh_count, 1);
-      if (at < CAND) dst[at] = k;
+      const int where = atomicAdd(&sh_count, 1);
+      if (where < CAND) dst[where] = k;
     }
   }
   __syncthreads();
