@@ -227,6 +227,35 @@ def test_mixed_steps_replayed_from_graphs_give_the_plain_tokens(tmp_path):
             assert float(row.max() - row[tok]) <= 2 * 2e-2 * float(logits.abs().max())
 
 
+def test_many_requests_of_random_lengths_under_a_tight_cache(tmp_path):
+    """Two dozen requests of random prompt lengths through one engine with six state slots, a budget of 96 rows and a
+    cache of forty pages of 16 tokens: admission in waves, prompts fed in portions beside decoding
+    requests (steps replayed from graphs, decode rows padded in the budget), pages given back and used again, requests
+    preempted and recomputed.  Greedy ids in 32-bit equal the plain implementation's for every request, with and
+    without graphs, and nothing is left behind."""
+    import random
+    from kungfu_b200 import Engine, ops
+    from kungfu_b200.sampling import Sampling
+    cfg = helpers.TINY_E
+    folder = helpers.write_model(str(tmp_path / "m"), cfg, seed=23, dtype=torch.bfloat16)
+    tensors = helpers.read_tensors(folder)
+    rnd = random.Random(5)
+    lengths = [rnd.choice([1, 2, 3, 7, 30, 63, 64, 65, 100, 129, 200, 260]) for _ in range(24)]
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 300 + i) for i, n in enumerate(lengths)]
+    want = [pg.greedy(cfg, tensors, p, 20) for p in prompts]
+    for graphs in (True, False):
+        e = Engine(folder, dtype="float32", device=DEV, ctx=512, batch=96, parallel=6, page_size=16, cuda_graphs=graphs,
+                   max_tokens_in_cache=640)
+        got = e.generate(prompts, Sampling(temperature=0.0), max_tokens=20, ignore_eos=True)
+        ops.raise_on_device_error()
+        assert got == want, [i for i, (a, b) in enumerate(zip(got, want)) if a != b]
+        assert e.runner.cache.n_live == 0 and e.idle
+        assert e.runner.cache.free_pages() == [g.pool.n_pages for g in e.runner.cache.groups]
+        handed = e.runner.cache.pages_handed_out()
+        assert all(h > g.pool.n_pages for h, g in zip(handed, e.runner.cache.groups)), "pages were used again"
+        assert e.scheduler.n_preemptions > 0
+
+
 def test_preemption_and_recompute_on_the_device(tmp_path):
     """Pages run out while three requests decode: the scheduler preempts the one admitted last, which is recomputed later
     from its prompt and the tokens it had produced.  The engine must read the tokens of the step in flight before it
