@@ -501,6 +501,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // gated product cannot overlap the next tile (its two accumulators fill tensor memory), and the last epilogue of every
 // launch is exposed too.
 constexpr int PAIR_THREADS = 576;
+constexpr int PAIR_SPLIT_STAGES = 6;                            // the split variant parks 128 KB of partial sums in its ring
 
 template <int EPI>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
@@ -660,6 +661,208 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
 }
 
+// ---- CTA pairs with K cut inside a cluster, for a few hundred tokens ----------------------------------------------------
+// With 256 x 256 tiles a portion of 256 to 1,024 tokens has fewer tiles than a quarter of the SMs.  Here a cluster of
+// 2 x `splits` CTAs owns one tile: pair z (cluster ranks 2z, 2z + 1) multiplies the z-th part of K exactly as the pair
+// kernel above does, every CTA parks its 128 features x 256 tokens of 32-bit partial sums in its own shared memory (the
+// stage ring is free by then), and after a cluster barrier the CTA of pair z and half h sums, in split order, the tokens
+// [z, z + 1) * 256 / splits of half h out of its peers' shared memory (16-byte loads) and stores them.  One tile per
+// cluster; plain 32-bit or bfloat16 store.
+__device__ __forceinline__ void umma_commit_pair_at(uint64_t* bar, uint32_t leader) {   // both CTAs of the pair led by `leader`
+  const uint16_t mask = (uint16_t)(3u << leader);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_split_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                          void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int stages, int splits,
+                          int* __restrict__ error_flag) {
+  constexpr int PN = 256;
+  constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (PN / 2) * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;
+  constexpr int TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  volatile int* s_abort = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const uint32_t half = rank & 1u, leader = rank & ~1u;
+  const int z = (int)(rank >> 1);
+  const int tile = blockIdx.x / (2 * splits);
+  const int n_ft = (N + 2 * BM - 1) / (2 * BM);
+  const int f0 = (tile % n_ft) * 2 * BM + (int)half * BM, t0 = (tile / n_ft) * PN;
+  const int nkb_total = (K + BK - 1) / BK;
+  const int kb_per = (nkb_total + splits - 1) / splits;
+  const int kb0 = z * kb_per;
+  const int nkb = min(nkb_total, kb0 + kb_per) - kb0;              // >= 1 by the host's choice of splits
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                             // the peers' barriers exist before anyone signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  kf_pdl_trigger();
+
+  if (warp == 0) {
+    // ---- TMA producer (every CTA): own weight rows, own half of the token tile; bytes are counted in the pair's leader ---
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
+      const uint32_t full0 = map_to_rank(smem_u32(&full[0]), leader);
+      const int tx0 = t0 + (int)half * (PN / 2);
+      // the weights do not depend on the kernel before: the first stages' weight tiles are asked for at once
+      const int pre = nkb < stages ? nkb : stages;
+      for (int i = 0; i < pre; ++i) {
+        if (half == 0) mbar_expect_tx(&full[i], 2 * STAGE_BYTES);
+        tma_load_2d_pair(smem + (size_t)i * STAGE_BYTES, &tm_w, full0 + 8u * (uint32_t)i, (kb0 + i) * BK, f0);
+      }
+      kf_pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_pair(smem + (size_t)i * STAGE_BYTES + A_BYTES, &tm_x, full0 + 8u * (uint32_t)i, (kb0 + i) * BK, tx0);
+      int s = 0;
+      uint32_t ph = 0;                                             // parity of `empty` when a stage has been used once
+      for (int i = pre; i < nkb; ++i) {
+        if (!mbar_wait(&empty[s], ph)) {
+          atomicExch(error_flag, ERR_WAIT_EMPTY);
+          *s_abort = 1;
+          break;
+        }
+        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+        if (half == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+        const uint32_t bar = full0 + 8u * (uint32_t)s;
+        const int k = (kb0 + i) * BK;
+        tma_load_2d_pair(st, &tm_w, bar, k, f0);
+        tma_load_2d_pair(st + A_BYTES, &tm_x, bar, k, tx0);
+        if (++s == stages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (the pair's leader only) --------------------------------------------------------------------------
+    if (lane == 0 && half == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      const uint64_t da0 = umma_desc(smem), db0 = umma_desc(smem + A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+        const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));
+        const uint64_t da = da0 + so, db = db0 + so;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_pair(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        umma_commit_pair_at(&empty[s], leader);
+        if (++s == stages) { s = 0; ph ^= 1; }
+      }
+      umma_commit_pair_at(acc_full, leader);
+      if (!ok) { atomicExch(error_flag, ERR_WAIT_FULL); *s_abort = 1; }
+    }
+  } else {
+    // ---- epilogue, first half: every CTA parks its own 128 lanes x 256 tokens in shared memory as [token][feature] -------
+    const int quarter = warp & 3;
+    const int col_q = (warp - 2) >> 2;                             // which quarter of the tile's tokens this warp drains
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float* red = reinterpret_cast<float*>(smem);
+    const int fl = quarter * 32 + lane;
+    if (!mbar_wait(acc_full, 0) || *s_abort) {
+      if (lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = col_q * (PN / 4); c0 < (col_q + 1) * (PN / 4); c0 += 32) {
+        float v[32];
+        tmem_ld32(lane_addr + c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) red[(size_t)(c0 + j) * BM + fl] = v[j];
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                             // every partial tile of the cluster is parked
+  if (warp >= 2) {
+    // ---- epilogue, second half: sum this CTA's share of the tokens over the splits, in split order, and store ----------
+    kf_pdl_wait();                                                 // before any global write
+    const int te = threadIdx.x - 64;                               // 0..511
+    const int fq = (te & 31) * 4, trow = te >> 5;                  // four features of one token per thread, 16 tokens a pass
+    const int slice = PN / splits;
+    const int f = f0 + fq;
+    const uint32_t red_addr = smem_u32(smem) + (uint32_t)fq * 4u;
+    uint32_t src[4];
+#pragma unroll
+    for (int zz = 0; zz < 4; ++zz) src[zz] = map_to_rank(red_addr, (uint32_t)((zz < splits ? zz : 0) * 2) + half);
+    const bool vec = (f + 3 < N) && (ld_out % 4 == 0);
+    for (int tl0 = z * slice + trow; tl0 < (z + 1) * slice; tl0 += 64) {
+      float4 p[4][4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int tl = tl0 + b * 16;
+#pragma unroll
+        for (int zz = 0; zz < 4; ++zz) {
+          p[b][zz] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (zz < splits && tl < (z + 1) * slice && t0 + tl < T) p[b][zz] = ld_cluster_f4(src[zz] + (uint32_t)tl * (BM * 4u));
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int tl = tl0 + b * 16, t = t0 + tl;
+        if (tl >= (z + 1) * slice || t >= T) continue;
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int zz = 0; zz < 4; ++zz) { r[0] += p[b][zz].x; r[1] += p[b][zz].y; r[2] += p[b][zz].z; r[3] += p[b][zz].w; }
+        if (EPI == EPI_F32) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) r[j] = kf_softcap(r[j], softcap);
+          float* o = (float*)out + (size_t)t * ld_out + f;
+          if (vec) *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+          else
+            for (int j = 0; j < 4; ++j) if (f + j < N) o[j] = r[j];
+        } else {
+          __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)t * ld_out + f;
+          if (vec) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+            uint2 w;
+            w.x = *reinterpret_cast<uint32_t*>(&lo);
+            w.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(o) = w;
+          } else {
+            for (int j = 0; j < 4; ++j) if (f + j < N) o[j] = __float2bfloat16_rn(r[j]);
+          }
+        }
+      }
+    }
+  }
+  cluster_sync_all();                                             // nobody leaves while a peer reads its shared memory
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -717,6 +920,10 @@ int g_stage_cap_kb = 108;
 // Choice of token tile and split-K for a launch.
 int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix the plan of products over more than 64 rows
 
+int g_pair = 1;             // many tokens: CTA pairs
+int g_pair_split = 1;       // a few hundred tokens: CTA pairs with K cut inside the cluster
+int pair_split_capacity(int splits);
+
 int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
   const int n_sm = kf_sm_count();
   int bn = 16;
@@ -729,6 +936,20 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
     return KF_OK;
   }
   int splits = 1;
+  if (!gated && T >= 224 && g_pair) {
+    // A few hundred tokens: with 256 x 256 tiles there are fewer tiles than CTA pairs.  While all clusters of a launch run
+    // at once, K is cut four or two ways inside a cluster of pairs (`gemm_tc_pair_split_kernel`); with more tiles than
+    // that, whole tiles on pairs.  Measured at the 2304-, 3584- and 4608-wide layers, 256 to 768 rows, against 64-token
+    // tiles on the weight-streaming kernel: 9216 -> 2304 at 256 rows 33 -> 23 us, 14336 -> 3584 at 512 rows 77 -> 47 us,
+    // 3584 -> 8192 at 512 rows 50 -> 28 us (whole tiles), nothing more than a tenth slower.
+    const int tt = kf_ceil_div(T, 256);
+    const int tiles = kf_ceil_div(N_features, 2 * BM) * tt;
+    const bool filled = (long)T * 5 >= (long)tt * 256 * 3;         // the token tiles are at least 0.6 full
+    const int cap4 = g_pair_split ? pair_split_capacity(4) : 0, cap2 = g_pair_split ? pair_split_capacity(2) : 0;
+    if (filled && tiles <= cap4 && nkb >= 32) { *bn_out = 256; *splits_out = 4; return KF_OK; }
+    if (filled && tiles <= cap2 && nkb >= 16) { *bn_out = 256; *splits_out = 2; return KF_OK; }
+    if (tiles > n_sm / 4 - 4) { *bn_out = 256; *splits_out = 1; return KF_OK; }
+  }
   if (T > 64 && gated) {
     // Prompt portions through the gated epilogue never split K (their partial tiles would have to go through global
     // memory); up to 256 rows a 128-token tile gives twice the tiles (measured at 256 rows, 9216 x 2304: 29 us against
@@ -742,7 +963,7 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
     while (splits < 8 && tiles * splits * 2 <= 2 * n_sm && nkb / (splits * 2) >= 8) splits *= 2;
   } else {
     const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
-    if (tiles <= n_sm / 2) {                                 // fewer tiles than half the SMs: cut K so that every SM streams
+    if (tiles <= n_sm / 2 && !(bn == 256 && g_pair)) {       // fewer tiles than half the SMs: cut K so that every SM streams
       splits = (int)(n_sm / tiles);                     // weights, in ONE wave (one CTA per SM fits)
       if (splits > 8) splits = 8;                      // a portable thread-block cluster holds 8 CTAs
       if (splits > nkb) splits = nkb;
@@ -845,7 +1066,6 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* out, i
   return KF_OK;
 }
 
-int g_pair = 1;
 
 template <int EPI>
 int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
@@ -893,6 +1113,74 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, 
 }
 
 template <int EPI>
+void pair_split_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int n_tiles, int splits, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = BM * BK * 2 + 128 * BK * 2;
+  cfg->gridDim = dim3(2 * splits * n_tiles);
+  cfg->blockDim = dim3(PAIR_THREADS);
+  cfg->dynamicSmemBytes = (size_t)PAIR_SPLIT_STAGES * STAGE_BYTES + 1024 + 512;
+  cfg->stream = stream;
+  int na = 0;
+  if (kf_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2 * splits;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  cfg->attrs = attr;
+  cfg->numAttrs = na;
+}
+
+template <int EPI>
+bool pair_split_configure() {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_split_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return false;
+    }
+    configured = true;
+  }
+  return true;
+}
+
+// How many clusters of 2 x splits CTAs of the split pair kernel the GPU holds at once (0 if it cannot be asked).
+int pair_split_capacity(int splits) {
+  static int cap[5] = {-1, -1, -1, -1, -1};
+  if (splits < 2 || splits > 4) return 0;
+  if (cap[splits] < 0) {
+    cap[splits] = 0;
+    if (pair_split_configure<EPI_F32>()) {
+      cudaLaunchConfig_t cfg = {};
+      cudaLaunchAttribute attr[2];
+      pair_split_config<EPI_F32>(&cfg, attr, 1, splits, nullptr);
+      cfg.attrs = &attr[cfg.numAttrs - 1];                         // the query takes the cluster shape alone
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_split_kernel<EPI_F32>, &cfg) == cudaSuccess) cap[splits] = n;
+      else cudaGetLastError();
+    }
+  }
+  return cap[splits];
+}
+
+template <int EPI>
+int launch_pair_split(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
+                      int splits, int* error_flag, cudaStream_t stream) {
+  if (!pair_split_configure<EPI>()) return KF_ERR_SETUP;
+  const int n_tiles = kf_ceil_div(N, 2 * BM) * kf_ceil_div(T, 256);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[2];
+  pair_split_config<EPI>(&cfg, attr, n_tiles, splits, stream);
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_split_kernel<EPI>, tw, tx, out, T, N, K, ld_out, softcap, PAIR_SPLIT_STAGES, splits, error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+template <int EPI>
 int launch_bn(int bn, const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
               int act, int up_offset, int splits, float* partial, int* counters, int* error_flag, cudaStream_t s) {
   switch (bn) {
@@ -913,6 +1201,8 @@ KF_API void kf_set_gemm_cluster_reduce(int on) { g_cluster_reduce = on ? 1 : 0; 
 KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
+KF_API void kf_set_gemm_pair_split(int on) { g_pair_split = on ? 1 : 0; }
+KF_API int kf_gemm_pair_split_capacity(int splits) { return pair_split_capacity(splits); }
 KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 #endif
@@ -954,6 +1244,18 @@ KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T
   CUtensorMap tw, tx;
   if (!tensor_map(w, w_rows, K, BM, &tw) || !tensor_map(x, T, K, bn, &tx)) return KF_ERR_SETUP;
   const int up_offset = mode == EPI_GATED ? N : 0;
+  if (g_pair && g_pair_split && bn == 256 && (splits == 2 || splits == 4) && mode != EPI_GATED && ((uintptr_t)out & 15) == 0 &&
+      (K + BK - 1) / BK >= splits) {
+    // a few hundred tokens: one tile per cluster of 2 x splits CTAs, K cut between the pairs
+    CUtensorMap txp;
+    if (!tensor_map(x, T, K, 128, &txp)) return KF_ERR_SETUP;
+    const int nkb = (K + BK - 1) / BK, kb_per = (nkb + splits - 1) / splits;
+    const int sp = (nkb + kb_per - 1) / kb_per;                    // no empty split
+    if (sp == splits) {
+      if (mode == EPI_F32) return launch_pair_split<EPI_F32>(tw, txp, out, T, N, K, N, softcap, splits, error_flag, stream);
+      return launch_pair_split<EPI_BF16>(tw, txp, out, T, N, K, N, softcap, splits, error_flag, stream);
+    }
+  }
   if (g_pair && splits == 1 && bn == 256) {
     // many tokens: CTA pairs; every CTA loads boxes of 128 rows (its weight rows, its half of the token tile)
     CUtensorMap txp;

@@ -95,7 +95,35 @@ def test_linear(ops, T, N, K, xd, wd):
 
 
 TC_SHAPES = [(1, 256, 64), (8, 2304, 2048), (5, 130, 200), (16, 128, 96), (17, 1000, 120), (40, 4096, 2304), (64, 777, 320),
-             (100, 300, 72), (256, 512, 512), (300, 2304, 9216), (700, 136, 64), (2048, 256, 128)]
+             (100, 300, 72), (256, 512, 512), (300, 2304, 9216), (700, 136, 64), (2048, 256, 128),
+             # a few hundred rows: K cut four and two ways inside a cluster of CTA pairs (ragged N, K and T), whole tiles on pairs
+             (256, 2304, 2048), (512, 4096, 2304), (250, 1002, 1032), (700, 130, 2056), (400, 8192, 512)]
+
+
+def test_linear_plans_for_a_few_hundred_rows(ops):
+    """What the planner picks between 224 and about a thousand rows: (token tile, K splits) = (256, 4) while the tiles of
+    256 x 256 fit the clusters of eight that run at once, (256, 2) while they fit the clusters of four, whole tiles on
+    CTA pairs beyond that; short K, nearly empty token tiles and gated products keep their earlier plans."""
+    import ctypes
+    lib = ops.library()
+
+    def plan(T, N, K, gated=0):
+        bn, sp = ctypes.c_int(0), ctypes.c_int(0)
+        lib.kf_linear_tc_plan(T, N, K, gated, ctypes.byref(bn), ctypes.byref(sp))
+        return bn.value, sp.value
+
+    assert plan(256, 2304, 9216) == (256, 4)            # 9 tiles
+    assert plan(512, 2304, 9216) == (256, 2)            # 18 tiles
+    assert plan(512, 4096, 2304) == (256, 2)            # 32 tiles
+    assert plan(512, 8192, 3584) == (256, 1)            # 64 tiles: whole tiles
+    assert plan(768, 2304, 2048) == (256, 2)            # 27 tiles
+    assert plan(1024, 2304, 2048) == (256, 1)           # 36 tiles
+    assert plan(250, 1002, 1032) == (256, 2)            # K too short to cut in four
+    assert plan(300, 2304, 9216)[0] == 64               # the second token tile would be a sixth full
+    assert plan(200, 2304, 9216)[0] == 64
+    assert plan(256, 2304, 512)[0] == 64                # K too short to cut
+    assert plan(512, 9216, 2304, 1) == (256, 1)         # gated: as before
+    assert plan(8, 2304, 9216) == (16, 8)               # decode: as before
 
 
 @pytest.mark.parametrize("T,N,K", TC_SHAPES)
