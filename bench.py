@@ -593,18 +593,21 @@ def micro_gemm() -> int:
     return 0
 
 
-def micro_products() -> int:
-    """The four products of a Gemma 2 2B layer over 8 to 2,048 rows, each replayed from a CUDA graph of six launches over
-    distinct weights; one JSON line per (rows, product) with microseconds per launch."""
+def micro_products(size: str = "2b") -> int:
+    """The four products of a Gemma 2 layer (`--size`) over 8 to 2,048 rows, each replayed from a CUDA graph of six
+    launches over distinct weights; one JSON line per (rows, product) with microseconds per launch."""
     import torch
     from kungfu_b200 import api, ops
     device = api.require_cuda("cuda:0")
     ops.library()
-    H, Q, inner, n_w = 2304, 2048, 9216, 6
+    sz = SIZES[size]
+    H, inner, n_w = sz["hidden_size"], sz["intermediate_size"], 6
+    Q = sz["num_attention_heads"] * sz["head_dim"]
+    qkv = Q + 2 * sz["num_key_value_heads"] * sz["head_dim"]
     gen = torch.Generator(device=device)
     gen.manual_seed(0)
-    shapes = {"q,k,v": (4096, H, False), "o": (H, Q, False), "gate+up": (inner, H, True), "down": (H, inner, False)}
-    for rows in (8, 64, 128, 256, 512, 1024, 2048):
+    shapes = {"q,k,v": (qkv, H, False), "o": (H, Q, False), "gate+up": (inner, H, True), "down": (H, inner, False)}
+    for rows in (8, 64, 128, 256, 384, 512, 768, 1024, 2048):
         for name, (n_out, k, gated) in shapes.items():
             ws = [(torch.randn(2 * n_out if gated else n_out, k, device=device, generator=gen) * 0.02).to(torch.bfloat16)
                   for _ in range(n_w)]
@@ -636,7 +639,7 @@ def micro_products() -> int:
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) / 10 / n_w * 1e3
             flops = 2.0 * rows * n_out * k * (2 if gated else 1)
-            print(json.dumps({"micro": "product", "rows": rows, "product": name, "us": round(us, 1),
+            print(json.dumps({"micro": "product", "size": size, "rows": rows, "product": name, "us": round(us, 1),
                               "tflops": round(flops / us / 1e6, 1)}))
             del ws
     ops.raise_on_device_error()
@@ -811,7 +814,7 @@ def main() -> int:
     args = ap.parse_args()
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
-                "products": micro_products, "reference": micro_reference}[args.micro]()
+                "products": lambda: micro_products(args.size), "reference": micro_reference}[args.micro]()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built "
