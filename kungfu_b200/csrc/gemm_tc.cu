@@ -923,6 +923,7 @@ int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix th
 int g_pair = 1;             // many tokens: CTA pairs
 int g_pair_split = 1;       // a few hundred tokens: CTA pairs with K cut inside the cluster
 int pair_split_capacity(int splits);
+int stream_cluster_capacity(int splits);
 
 int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* splits_out) {
   const int n_sm = kf_sm_count();
@@ -936,7 +937,7 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
     return KF_OK;
   }
   int splits = 1;
-  if (!gated && T >= 224 && g_pair) {
+  if (!gated && T > 128 && g_pair) {
     // A few hundred tokens: with 256 x 256 tiles there are fewer tiles than CTA pairs.  While all clusters of a launch run
     // at once, K is cut four or two ways inside a cluster of pairs (`gemm_tc_pair_split_kernel`); with more tiles than
     // that, whole tiles on pairs.  Measured at the 2304-, 3584- and 4608-wide layers, 256 to 768 rows, against 64-token
@@ -944,11 +945,13 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
     // 3584 -> 8192 at 512 rows 50 -> 28 us (whole tiles), nothing more than a tenth slower.
     const int tt = kf_ceil_div(T, 256);
     const int tiles = kf_ceil_div(N_features, 2 * BM) * tt;
-    const bool filled = (long)T * 5 >= (long)tt * 256 * 3;         // the token tiles are at least 0.6 full
+    const bool filled = tt == 1 || (long)T * 5 >= (long)tt * 256 * 3;   // several token tiles: at least 0.6 full
     const int cap4 = g_pair_split ? pair_split_capacity(4) : 0, cap2 = g_pair_split ? pair_split_capacity(2) : 0;
-    if (filled && tiles <= cap4 && nkb >= 32) { *bn_out = 256; *splits_out = 4; return KF_OK; }
-    if (filled && tiles <= cap2 && nkb >= 16) { *bn_out = 256; *splits_out = 2; return KF_OK; }
-    if (tiles > n_sm / 4 - 4) { *bn_out = 256; *splits_out = 1; return KF_OK; }
+    const int cut = (filled && tiles <= cap4 && nkb >= 32) ? 4 : (filled && tiles <= cap2 && nkb >= 16) ? 2 : 0;
+    // Up to 192 rows the 64-token tiles are three and read the weights three times from L2: the clusters win where they
+    // cover most of the GPU (14336 -> 3584 at 160 rows: 43 -> 30 us), and lose where they are few (9216 -> 2304: 19 -> 21 us).
+    if (cut && (T > 192 || tiles * 2 * cut * 10 >= n_sm * 7)) { *bn_out = 256; *splits_out = cut; return KF_OK; }
+    if (T >= 224 && tiles > n_sm / 4 - 4) { *bn_out = 256; *splits_out = 1; return KF_OK; }
   }
   if (T > 64 && gated) {
     // Prompt portions through the gated epilogue never split K (their partial tiles would have to go through global
@@ -958,9 +961,13 @@ int plan_linear(int T, int N_features, int K, int gated, int* bn_out, int* split
   } else if (T > 64 && (T <= 512 || (T <= 1024 && K <= 4096 && (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, 64) <= 2 * n_sm))) {
     // Short portions: 64-token tiles on the weight-streaming kernel, two CTAs per SM, K cut so that about two CTAs per SM
     // run (measured at 2304-wide layers, 128 to 512 rows: 1.3x to 2x faster than one 256-token tile split four ways).
+    // A cluster needs all its CTAs at once, so fewer CTAs fit than two per SM (clusters of eight: 32 x 8, not 296): K is
+    // cut only as far as every cluster of the launch still runs at once (9216 -> 2304 at 128 rows, 36 tiles: in four 17.9 us,
+    // in eight 22.7 us; 4096 -> 4608 at 128 rows, 72 tiles: in two 18.2 us, in four 22.7 us).
     bn = 64;
     const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
-    while (splits < 8 && tiles * splits * 2 <= 2 * n_sm && nkb / (splits * 2) >= 8) splits *= 2;
+    while (splits < 8 && tiles * splits * 2 <= 2 * n_sm && nkb / (splits * 2) >= 8 && tiles <= stream_cluster_capacity(splits * 2))
+      splits *= 2;
   } else {
     const long tiles = (long)kf_ceil_div(N_features, BM) * kf_ceil_div(T, bn);
     if (tiles <= n_sm / 2 && !(bn == 256 && g_pair)) {       // fewer tiles than half the SMs: cut K so that every SM streams
@@ -1034,6 +1041,40 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
                      cluster ? 1 : 0, partial, counters, error_flag);
   KF_CHECK_LAUNCH();
   return KF_OK;
+}
+
+// How many clusters of `splits` CTAs of the weight-streaming kernel with 64-token tiles the GPU holds at once.
+int stream_cluster_capacity(int splits) {
+  static int cap[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (splits < 2 || splits > 8) return 1 << 30;
+  if (cap[splits] < 0) {
+    cap[splits] = 1 << 30;                                         // if it cannot be asked: no limit, as before
+    constexpr int STAGE_BYTES = Tile<64>::A_BYTES + Tile<64>::B_BYTES;
+    int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    if (g_stage_cap_kb > 0 && stages > g_stage_cap_kb * 1024 / STAGE_BYTES) stages = g_stage_cap_kb * 1024 / STAGE_BYTES;
+    if (cudaFuncSetAttribute(gemm_tc_kernel<64, EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 1, splits);
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = (size_t)stages * STAGE_BYTES + 1024 + 512;
+      cudaLaunchAttribute cl;
+      cl.id = cudaLaunchAttributeClusterDimension;
+      cl.val.clusterDim.x = 1;
+      cl.val.clusterDim.y = 1;
+      cl.val.clusterDim.z = splits;
+      cfg.attrs = &cl;
+      cfg.numAttrs = 1;
+      // The cluster query answers as if one CTA ran per SM (74 / 33 / 15 clusters of 2 / 4 / 8 here); two of these CTAs share
+      // an SM's shared memory, and twice its answer is where the measured launches begin to take a second round.
+      int n = 0;
+      const int per_sm = (int)((228u * 1024u) / (cfg.dynamicSmemBytes + 1024u));
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<64, EPI_F32>, &cfg) == cudaSuccess && n > 0) cap[splits] = n * (per_sm > 1 ? per_sm : 1);
+      else cudaGetLastError();
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return cap[splits];
 }
 
 int g_persistent = 1;
@@ -1203,6 +1244,7 @@ KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair_split(int on) { g_pair_split = on ? 1 : 0; }
 KF_API int kf_gemm_pair_split_capacity(int splits) { return pair_split_capacity(splits); }
+KF_API int kf_gemm_stream_cluster_capacity(int splits) { return stream_cluster_capacity(splits); }
 KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
 KF_API void kf_set_gemm_gated_wide(int on) { g_gated_wide = on ? 1 : 0; }
 #endif

@@ -101,7 +101,8 @@ TC_SHAPES = [(1, 256, 64), (8, 2304, 2048), (5, 130, 200), (16, 128, 96), (17, 1
 
 
 def test_linear_plans_for_a_few_hundred_rows(ops):
-    """What the planner picks between 224 and about a thousand rows: (token tile, K splits) = (256, 4) while the tiles of
+    """What the planner picks between 65 and about a thousand rows: up to 192 rows 64-token tiles with K cut as far as all
+    clusters still run at once; beyond (and below where the clusters cover most of the GPU) (token tile, K splits) = (256, 4) while the tiles of
     256 x 256 fit the clusters of eight that run at once, (256, 2) while they fit the clusters of four, whole tiles on
     CTA pairs beyond that; short K, nearly empty token tiles and gated products keep their earlier plans."""
     import ctypes
@@ -120,7 +121,12 @@ def test_linear_plans_for_a_few_hundred_rows(ops):
     assert plan(1024, 2304, 2048) == (256, 1)           # 36 tiles
     assert plan(250, 1002, 1032) == (256, 2)            # K too short to cut in four
     assert plan(300, 2304, 9216)[0] == 64               # the second token tile would be a sixth full
-    assert plan(200, 2304, 9216)[0] == 64
+    assert plan(200, 2304, 9216) == (256, 4)
+    assert plan(160, 2304, 9216) == (64, 4)             # three 64-token tiles; nine clusters of eight would leave half the GPU idle
+    assert plan(160, 3584, 14336) == (256, 4)           # fourteen clusters of eight
+    assert plan(128, 2304, 9216) == (64, 4)             # 36 tiles: clusters of eight would need a second round
+    assert plan(128, 4608, 4096) == (64, 2)             # 72 tiles: so would clusters of four
+    assert plan(128, 4096, 2304) == (64, 4)             # 64 tiles
     assert plan(256, 2304, 512)[0] == 64                # K too short to cut
     assert plan(512, 9216, 2304, 1) == (256, 1)         # gated: as before
     assert plan(8, 2304, 9216) == (16, 8)               # decode: as before
