@@ -503,15 +503,30 @@ __device__ __forceinline__ void cluster_sync_all() {
 constexpr int PAIR_THREADS = 576;
 constexpr int PAIR_SPLIT_STAGES = 6;                            // the split variant parks 128 KB of partial sums in its ring
 
+// What the q,k,v product needs to rotate and file its own result (EPI_ROPE, head size 256): a CTA owns one head, its two
+// accumulators are the head's features i and i + 128 (weight rows h * 256 + i and h * 256 + 128 + i), so one thread holds
+// both elements of a rotation pair.  q heads go to q_out rotated, k heads rotated and v heads as they are into the request's
+// page at the token's position; rows of no request (padding) give zero q and write no keys.
+struct RopeArgs {
+  const float* cos_t;                                             // [T, 128] by token row
+  const float* sin_t;
+  const int* positions;
+  const int* row_req;
+  const int* block_table;
+  int table_stride, page_size, nh, nkv, write_kv;
+  __nv_bfloat16* pages;                                           // [page][k, v][nkv][page_size][256]
+  __nv_bfloat16* q_out;                                           // [T, nh * 256]
+};
+
 template <int EPI>
-__global__ void __launch_bounds__(PAIR_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                    void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
-                    int stages, int* __restrict__ error_flag) {
+__device__ __forceinline__ void
+gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __restrict__ out, int T, int N, int K, int ld_out,
+                  float softcap, int act, int up_offset, int stages, int* __restrict__ error_flag, const RopeArgs& ra) {
   constexpr bool GATED = EPI == EPI_GATED;
-  constexpr int NACC = GATED ? 2 : 1;
+  constexpr bool ROPE = EPI == EPI_ROPE;
+  constexpr int NACC = (GATED || ROPE) ? 2 : 1;
   constexpr int PN = 256;                                         // tokens of the pair's tile = MMA N
-  constexpr int NBUF = GATED ? 1 : 2;                             // accumulator sets in tensor memory
+  constexpr int NBUF = NACC == 2 ? 1 : 2;                         // accumulator sets in tensor memory
   constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (PN / 2) * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES * NACC + BH_BYTES;
   constexpr int TMEM_COLS = 512;
@@ -530,9 +545,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int n_feat = GATED ? up_offset : N;
-  const int n_ft = (n_feat + 2 * BM - 1) / (2 * BM), n_tt = (T + PN - 1) / PN;
+  // ROPE: a CTA's "feature tile" is one head (its 128 rotation pairs), a pair's tile two heads
+  const int n_ft = ROPE ? (ra.nh + 2 * ra.nkv + 1) / 2 : (n_feat + 2 * BM - 1) / (2 * BM), n_tt = (T + PN - 1) / PN;
   const int n_tiles = n_ft * n_tt;
   const int nkb = (K + BK - 1) / BK;
+  const int second = ROPE ? BM : up_offset;                       // weight rows of the second accumulator, after the first's
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -562,7 +579,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       bool ok = true;
       const uint32_t full0 = map_to_rank(smem_u32(&full[0]), 0);   // the leader's full[0], as a cluster address
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        const int f0 = (tile % n_ft) * 2 * BM + (int)rank * BM;
+        const int f0 = ((tile % n_ft) * 2 + (int)rank) * (ROPE ? 2 * BM : BM);
         const int t0 = (tile / n_ft) * PN + (int)rank * (PN / 2);
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[s], ph)) {
@@ -576,7 +593,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint32_t bar = full0 + 8u * (uint32_t)s;
           const int k = kb * BK;
           tma_load_2d_pair(st, &tm_w, bar, k, f0);
-          if (GATED) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, up_offset + f0);
+          if (NACC == 2) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, second + f0);
           tma_load_2d_pair(st + A_BYTES * NACC, &tm_x, bar, k, t0);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -604,7 +621,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
             umma_pair(acc, da + 2 * k, db + 2 * k, idesc, accumulate);
-            if (GATED) umma_pair(acc + PN, du + 2 * k, db + 2 * k, idesc, accumulate);
+            if (NACC == 2) umma_pair(acc + PN, du + 2 * k, db + 2 * k, idesc, accumulate);
           }
           umma_commit_pair(&empty[s]);
           if (++s == stages) { s = 0; ph ^= 1; }
@@ -622,29 +639,103 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     int ti = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++ti) {
       const int buf = ti % NBUF;
-      const int f0 = (tile % n_ft) * 2 * BM + (int)rank * BM, t0 = (tile / n_ft) * PN;
+      const int f0 = ((tile % n_ft) * 2 + (int)rank) * (ROPE ? 2 * BM : BM), t0 = (tile / n_ft) * PN;
       const int f = f0 + quarter * 32 + lane;
+      // ROPE: where this warp's 64 rows go, two rows per lane, looked up while the accumulator is still being filled:
+      // for k and v heads the row's slot in the pages (in rows of 256), for q heads 0; -1 for rows of no request
+      const int head = (tile % n_ft) * 2 + (int)rank;
+      const bool is_q = ROPE && head < ra.nh, is_k = ROPE && !is_q && head < ra.nh + ra.nkv;
+      const bool is_v = ROPE && !is_q && !is_k && head < ra.nh + 2 * ra.nkv;
+      const bool rope_work = is_q || ((is_k || is_v) && ra.write_kv);
+      int meta_a = -1, meta_b = -1;
+      if (ROPE && rope_work) {
+        const int kvh = is_k ? head - ra.nh : head - ra.nh - ra.nkv;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int t = t0 + col_half * (PN / 4) + cc * 32 + lane;
+          int m = -1;
+          if (t < T) {
+            const int req = __ldg(ra.row_req + t);
+            if (req >= 0) {
+              m = 0;
+              if (!is_q) {
+                const int pos = __ldg(ra.positions + t);
+                const int page = __ldg(ra.block_table + (size_t)req * ra.table_stride + pos / ra.page_size);
+                m = ((page * 2 + (is_v ? 1 : 0)) * ra.nkv + kvh) * ra.page_size + pos % ra.page_size;
+              }
+            }
+          }
+          if (cc) meta_b = m; else meta_a = m;
+        }
+      }
       if (!mbar_wait(&acc_full[buf], (uint32_t)(ti / NBUF) & 1) || *s_abort) {
         if (lane == 0) atomicExch(error_flag, ERR_WAIT_ACC);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = lane_addr + buf * PN;
+      if constexpr (ROPE) {
+        // this CTA's head: a q head (rotated to q_out), a k head (rotated into the page), a v head (into the page) or none
+        const int i = quarter * 32 + lane;                                           // the rotation pair (i, i + 128)
+        if (rope_work) {
 #pragma unroll 1
-      for (int c0 = col_half * (PN / 4); c0 < (col_half + 1) * (PN / 4); c0 += 32) {   // 32 tokens per wait on tensor memory
-        float v[32], u[32];
-        if (GATED) tmem_ld32x2(acc + c0, acc + PN + c0, v, u);
-        else tmem_ld32(acc + c0, v);
+          for (int cc = 0; cc < 4; ++cc) {                                           // sixteen rows at a time
+            const int c0 = col_half * (PN / 4) + cc * 16;
+            // the rows' angles are all asked for before the accumulator is read and the first of them is used
+            float cs[16], sn[16];
+            if (!is_v) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = t0 + c0 + j;
-          if (t < T && f < n_feat) {
-            float r;
-            if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
-            else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
-            else r = v[j];
-            if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
-            else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
+              for (int j = 0; j < 16; ++j) {
+                const int tc = min(t0 + c0 + j, T - 1);
+                cs[j] = __ldg(ra.cos_t + (size_t)tc * BM + i);
+                sn[j] = __ldg(ra.sin_t + (size_t)tc * BM + i);
+              }
+            }
+            float v[16], u[16];
+            tmem_ld16(acc + c0, v);
+            tmem_ld16(acc + PN + c0, u);
+            const int meta = (cc & 2) ? meta_b : meta_a;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c0 + j;
+              const int m = __shfl_sync(0xffffffffu, meta, (cc & 1) * 16 + j);
+              if (t >= T) continue;
+              float a = v[j], b = u[j];
+              if (!is_v) {
+                const float x1 = a, x2 = b;
+                a = x1 * cs[j] - x2 * sn[j];
+                b = x2 * cs[j] + x1 * sn[j];
+              }
+              if (is_q) {
+                if (m < 0) a = b = 0.f;
+                __nv_bfloat16* q = ra.q_out + ((size_t)t * ra.nh + head) * (2 * BM) + i;
+                q[0] = __float2bfloat16_rn(a);
+                q[BM] = __float2bfloat16_rn(b);
+              } else if (m >= 0) {
+                __nv_bfloat16* kv = ra.pages + (size_t)m * (2 * BM) + i;
+                kv[0] = __float2bfloat16_rn(a);
+                kv[BM] = __float2bfloat16_rn(b);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = col_half * (PN / 4); c0 < (col_half + 1) * (PN / 4); c0 += 32) {   // 32 tokens per wait on tensor memory
+          float v[32], u[32];
+          if (GATED) tmem_ld32x2(acc + c0, acc + PN + c0, v, u);
+          else tmem_ld32(acc + c0, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < T && f < n_feat) {
+              float r;
+              if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
+              else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
+              else r = v[j];
+              if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
+              else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
+            }
           }
         }
       }
@@ -659,6 +750,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                    void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
+                    int stages, int* __restrict__ error_flag) {
+  gemm_tc_pair_body<EPI>(tm_w, tm_x, out, T, N, K, ld_out, softcap, act, up_offset, stages, error_flag, RopeArgs{});
+}
+
+// The q,k,v product of a prompt with head size 256 that rotates q and k and files k and v itself (no 32-bit q,k,v rows in
+// memory, no kernel after it): see RopeArgs.
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_rope_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, int T, int N, int K,
+                         int stages, int* __restrict__ error_flag, const __grid_constant__ RopeArgs ra) {
+  gemm_tc_pair_body<EPI_ROPE>(tm_w, tm_x, nullptr, T, N, K, 0, 0.f, 0, 0, stages, error_flag, ra);
 }
 
 // ---- CTA pairs with K cut inside a cluster, for a few hundred tokens ----------------------------------------------------
@@ -922,6 +1029,7 @@ int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix th
 
 int g_pair = 1;             // many tokens: CTA pairs
 int g_pair_split = 1;       // a few hundred tokens: CTA pairs with K cut inside the cluster
+int g_pair_rope = 1;        // prompts, head size 256: the q,k,v product rotates and files its own result
 int pair_split_capacity(int splits);
 int stream_cluster_capacity(int splits);
 
@@ -1067,7 +1175,14 @@ int stream_cluster_capacity(int splits) {
       // The cluster query answers as if one CTA ran per SM (74 / 33 / 15 clusters of 2 / 4 / 8 here); two of these CTAs share
       // an SM's shared memory, and twice its answer is where the measured launches begin to take a second round.
       int n = 0;
-      const int per_sm = (int)((228u * 1024u) / (cfg.dynamicSmemBytes + 1024u));
+      int dev = 0, sm_bytes = 0, block_reserved = 0;
+      int per_sm = 1;
+      if (cudaGetDevice(&dev) == cudaSuccess &&
+          cudaDeviceGetAttribute(&sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
+          cudaDeviceGetAttribute(&block_reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) == cudaSuccess)
+        per_sm = (int)((size_t)sm_bytes / (cfg.dynamicSmemBytes + (size_t)block_reserved));
+      else
+        cudaGetLastError();
       if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<64, EPI_F32>, &cfg) == cudaSuccess && n > 0) cap[splits] = n * (per_sm > 1 ? per_sm : 1);
       else cudaGetLastError();
     } else {
@@ -1149,6 +1264,47 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, 
   cfg.attrs = attr;
   cfg.numAttrs = na;
   cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, up_offset, stages, error_flag);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+int launch_pair_rope(const CUtensorMap& tw, const CUtensorMap& tx, int T, int N, int K, const RopeArgs& ra, int* error_flag,
+                     cudaStream_t stream) {
+  constexpr int STAGE_BYTES = BM * BK * 2 * 2 + 128 * BK * 2;
+  int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  if (stages > 8) stages = 8;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+      kf_record_cuda_error(cudaGetLastError());
+      return KF_ERR_SETUP;
+    }
+    configured = true;
+  }
+  const int n_tiles = kf_ceil_div(ra.nh + 2 * ra.nkv, 2) * kf_ceil_div(T, 256);
+  int pairs = kf_sm_count() / 2;
+  if (pairs > n_tiles) pairs = n_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(PAIR_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (kf_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_rope_kernel, tw, tx, T, N, K, stages, error_flag, ra);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -1243,6 +1399,7 @@ KF_API void kf_set_gemm_stage_cap_kb(int kb) { g_stage_cap_kb = kb; }
 KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair_split(int on) { g_pair_split = on ? 1 : 0; }
+KF_API void kf_set_gemm_pair_rope(int on) { g_pair_rope = on ? 1 : 0; }
 KF_API int kf_gemm_pair_split_capacity(int splits) { return pair_split_capacity(splits); }
 KF_API int kf_gemm_stream_cluster_capacity(int splits) { return stream_cluster_capacity(splits); }
 KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
@@ -1261,6 +1418,47 @@ KF_API int kf_test_gemm_give_up(unsigned long long limit_ns, int drop_from_stage
     return KF_ERR_SETUP;
   }
   return KF_OK;
+}
+
+// Whether the q,k,v product of this step can rotate and file its own result: head size 256 rotated in full, bfloat16
+// everywhere, and so many rows that the product runs as whole 256 x 256 tiles on CTA pairs, one tile of two heads each.
+KF_API int kf_linear_rope_append_supported(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, int head_dim, int rot) {
+  if (!g_pair || !g_pair_rope || head_dim != 2 * BM || rot != head_dim || T <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || encode_fn() == nullptr) return 0;
+  int bn = 0, splits = 0;
+  if (plan_linear(T, (n_heads + 2 * n_kv_heads) * head_dim, K, 0, &bn, &splits) != KF_OK) return 0;
+  // Two accumulators of 256 columns fill tensor memory, so this epilogue cannot run under the next tile's products as the
+  // plain one does: it pays while every pair has one tile (2,048 rows of 16 heads: 8.93 -> 8.68 ms for the 26-layer prompt),
+  // and costs where pairs have two (2,048 rows of 32 heads: 34.1 -> 34.6 ms for 42 layers).
+  const int n_tiles = kf_ceil_div(n_heads + 2 * n_kv_heads, 2) * kf_ceil_div(T, 256);
+  return bn == 256 && splits == 1 && n_tiles <= kf_sm_count() / 2;
+}
+
+// x[T, K] . w[(n_heads + 2 n_kv_heads) * 256, K]^T with q and k rotated (pairs i, i + 128; cos, sin [T, 128] by row), q
+// written to q_out[T, n_heads * 256] and k, v into the pages of the rows' requests (if write_kv); all bfloat16.
+KF_API int kf_linear_rope_append(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, const float* cos_t,
+                                 const float* sin_t, const int* positions, const int* row_req, const int* block_table,
+                                 int table_stride, int page_size, void* pages, void* q_out, int write_kv, int* error_flag,
+                                 cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  if (!kf_linear_rope_append_supported(x, w, T, K, n_heads, n_kv_heads, 2 * BM, 2 * BM) || !cos_t || !sin_t) return KF_ERR_SIZE;
+  const int N = (n_heads + 2 * n_kv_heads) * 2 * BM;
+  CUtensorMap tw, txp;
+  if (!tensor_map(w, N, K, BM, &tw) || !tensor_map(x, T, K, 128, &txp)) return KF_ERR_SETUP;
+  RopeArgs ra;
+  ra.cos_t = cos_t;
+  ra.sin_t = sin_t;
+  ra.positions = positions;
+  ra.row_req = row_req;
+  ra.block_table = block_table;
+  ra.table_stride = table_stride;
+  ra.page_size = page_size;
+  ra.nh = n_heads;
+  ra.nkv = n_kv_heads;
+  ra.write_kv = write_kv;
+  ra.pages = (__nv_bfloat16*)pages;
+  ra.q_out = (__nv_bfloat16*)q_out;
+  return launch_pair_rope(tw, txp, T, N, K, ra, error_flag, stream);
 }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.

@@ -12,7 +12,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int WAIT_LIMIT = 40 * 1000 * 1000;
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_GATED = 2 };
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_GATED = 2, EPI_ROPE = 3 };
 enum { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_ACC = 3 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -262,6 +262,8 @@ def add(a, x) -> None:
 _scratch: dict = {}          # device -> {"partial": tensor, "counters": tensor, "error": tensor, "retired": [tensors]}
 use_tensor_cores = True      # tests switch this off to reach the generic product with bfloat16 operands
 use_fast_attention = True    # likewise for the generic attention kernel
+fused_qkv_rope = True        # False: the q,k,v product of a prompt always leaves 32-bit rows for `rope_kv_append`
+fused_qkv_rope_launches = 0  # how often the product that rotates and files its own result has run (tests look at it)
 prefill_on_tcgen05 = True       # False: the mma.sync prompt kernel for every head and page size
 split_prompt_keys = True        # False: one block per (tile of rows, head) however few blocks that makes
 decode_on_tensor_cores = True   # False: the SIMT split-KV decode kernel (kept for groups of more than 16 heads)
@@ -311,6 +313,7 @@ def raise_on_device_error(device=None) -> None:
                           f"3 = accumulator never completed)")
 
 
+_rope_plans: dict = {}            # (rows, K, heads, kv heads, head size, rotated) -> whether the fused q,k,v product takes them
 _linear_plans: dict = {}          # (rows, features, K, mode) -> (token tile, K splits) as the library plans them
 
 
@@ -385,6 +388,33 @@ def rope_kv_append(qkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_
                                        _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
                                        _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out), int(cache.writes),
                                        T, _stream()), "rope_kv_append")
+
+
+@_dispatch("linear_rope_kv_append")
+def linear_rope_kv_append(x, wqkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_dim: int, ctx, cache, q_out) -> bool:
+    """q,k,v = x . wqkv^T, q and k rotated, q to q_out, k and v into the pages of `cache`: one launch whose product files
+    its own result (no 32-bit q,k,v rows in memory).  True if it ran; False if this step does not qualify (then the
+    caller runs `linear` and `rope_kv_append`): it takes bfloat16 operands, q and pages, head size 256 rotated in full,
+    and so many rows that the product runs as whole tiles on CTA pairs."""
+    T, K = x.shape
+    if not (use_tensor_cores and fused_qkv_rope and cos is not None and x.dtype == torch.bfloat16
+            and wqkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16 and cache.pages.dtype == torch.bfloat16):
+        return False
+    lib = library()
+    key = (T, K, n_heads, n_kv_heads, head_dim, rot)
+    ok = _rope_plans.get(key)
+    if ok is None:
+        ok = _rope_plans[key] = bool(lib.kf_linear_rope_append_supported(_p(x), _p(wqkv), T, K, n_heads, n_kv_heads, head_dim, rot))
+    if not ok or (x.data_ptr() | wqkv.data_ptr()) & 15:
+        return False
+    table = ctx.block_tables[cache.group]
+    sc = _dev_scratch(x.device)
+    global fused_qkv_rope_launches
+    fused_qkv_rope_launches += 1
+    _check(lib.kf_linear_rope_append(_p(x), _p(wqkv), T, K, n_heads, n_kv_heads, _p(cos), _p(sin), _p(ctx.positions),
+                                     _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, _p(cache.pages), _p(q_out),
+                                     int(cache.writes), _p(sc["error"]), _stream()), "linear_rope_kv_append")
+    return True
 
 
 @_dispatch("paged_attention")

@@ -39,8 +39,6 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         nh, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = ctx.buf("attn_qkv", (T, (nh + 2 * nkv) * d), torch.float32)
-        ops.linear(x, self.wqkv, qkv)
         if self.position is not None:
             cos, sin = self.position.rotation(ctx)
             rot = 2 * cos.shape[1]
@@ -50,10 +48,16 @@ class PagedAttention(Mixer):
         o = ctx.buf("attn_o", (T, nh * d), ctx.act_dtype)
         if ops.decode_attention_takes_qkv(ctx, cache, nh, nkv, d):
             # a decode step: the attention kernel rotates, appends and attends in one launch
+            qkv = ctx.buf("attn_qkv", (T, (nh + 2 * nkv) * d), torch.float32)
+            ops.linear(x, self.wqkv, qkv)
             ops.rope_append_attend(qkv, cos, sin, rot, o, ctx, cache, nh, nkv, d, self.scale, self.softcap, self.window)
         else:
             q = ctx.buf("attn_q", (T, nh * d), ctx.act_dtype)
-            ops.rope_kv_append(qkv, cos, sin, rot, nh, nkv, d, ctx, cache, q)
+            # a long prompt: the product rotates and files its own result where it can
+            if not ops.linear_rope_kv_append(x, self.wqkv, cos, sin, rot, nh, nkv, d, ctx, cache, q):
+                qkv = ctx.buf("attn_qkv", (T, (nh + 2 * nkv) * d), torch.float32)
+                ops.linear(x, self.wqkv, qkv)
+                ops.rope_kv_append(qkv, cos, sin, rot, nh, nkv, d, ctx, cache, q)
             ops.paged_attention(q, o, ctx, cache, nh, nkv, d, self.scale, self.softcap, self.window)
         y = ctx.buf("branch_out", (T, self.width), torch.float32)
         ops.linear(o, self.wo, y)

@@ -58,6 +58,9 @@ class CpuOps:
         cos.copy_(torch.cos(ang))
         sin.copy_(torch.sin(ang))
 
+    def linear_rope_kv_append(self, x, wqkv, cos, sin, rot, nh, nkv, d, ctx, cache, q_out):
+        return False                                   # no fused product here: the caller runs linear and rope_kv_append
+
     def rope_kv_append(self, qkv, cos, sin, rot, nh, nkv, d, ctx, cache, q_out):
         T = qkv.shape[0]
         q = qkv[:, :nh * d].view(T, nh, d).clone()

@@ -682,6 +682,76 @@ def test_rope_kv_append(ops, qd, kvd, nh, nkv, d, rot, P):
     assert bool((untouched == 7.0).all()), "a slot outside the step's positions was written"
 
 
+@pytest.mark.parametrize("nh,nkv,K,lens,writes", [(8, 4, 2304, [700, 330], True), (3, 1, 264, [1500, 1480, 20], True),
+                                                  (2, 2, 512, [3100], False), (16, 8, 520, [300, 257], True)])
+def test_qkv_product_that_rotates_and_files_its_result(ops, nh, nkv, K, lens, writes):
+    """The q,k,v product of a long prompt with head size 256 writes rotated q rows and the pages itself.  Against float64
+    from the same bfloat16 operands, and against the two-kernel path (32-bit rows, then rotation and append) to within one
+    bfloat16 rounding; requests at different positions on scattered pages, padding rows, an odd number of heads (the last CTA
+    pair has one head), a K that is no multiple of 64, a cache that is not written."""
+    d, P = 256, 64
+    g = torch.Generator().manual_seed(nh * 100 + K)
+    starts = [37, 0, 130][:len(lens)]
+    T_real = sum(lens)
+    T = T_real + 9                                                   # nine padding rows at the end
+    N = (nh + 2 * nkv) * d
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * (2.0 / K ** 0.5)).to(torch.bfloat16)
+    positions = torch.tensor([s0 + i for s0, n in zip(starts, lens) for i in range(n)] + [0] * 9, dtype=torch.int32)
+    row_req = torch.tensor([r for r, n in enumerate(lens) for _ in range(n)] + [-1] * 9, dtype=torch.int32)
+    need = [-(-(s0 + n) // P) for s0, n in zip(starts, lens)]
+    n_pages = sum(need) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((len(lens), max(need) + 1), -1, dtype=torch.int32)
+    for r, n in enumerate(need):
+        table[r, :n] = torch.tensor([perm.pop() for _ in range(n)])
+    inv = (10000.0 ** (-2.0 * torch.arange(d // 2, dtype=torch.float64) / d)).float()
+    ang = positions.float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
+    ctx = _Ctx(positions.to(DEV), row_req.to(DEV), table.to(DEV))
+    xd, wd = x.to(DEV), w.to(DEV)
+
+    def run(fused):
+        pages = torch.full((n_pages, 2, nkv, P, d), 7.0, dtype=torch.bfloat16, device=DEV)
+        view = _View(pages, P, writes)
+        q = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        if fused:
+            assert ops.linear_rope_kv_append(xd, wd, cos, sin, d, nh, nkv, d, ctx, view, q), "the fused product declined"
+        else:
+            qkv = torch.empty(T, N, device=DEV)
+            ops.linear(xd, wd, qkv)
+            ops.rope_kv_append(qkv, cos, sin, d, nh, nkv, d, ctx, view, q)
+        ops.raise_on_device_error()
+        return q.float().cpu(), pages.float().cpu()
+
+    q_f, pages_f = run(True)
+    q_u, pages_u = run(False)
+    qkv = x.double() @ w.double().T
+    c, s_ = cos.double().cpu()[:, None, :], sin.double().cpu()[:, None, :]
+
+    def rope(h):
+        a, b = h[..., :d // 2], h[..., d // 2:]
+        return torch.cat([a * c - b * s_, a * s_ + b * c], dim=-1)
+    q_ref = rope(qkv[:, :nh * d].view(T, nh, d))
+    q_ref[T_real:] = 0                                               # rows of no request give zero q
+    k_ref = rope(qkv[:, nh * d:(nh + nkv) * d].view(T, nkv, d))
+    v_ref = qkv[:, (nh + nkv) * d:].view(T, nkv, d)
+    scale = float(qkv.abs().max())
+    assert float((q_f.view(T, nh, d) - q_ref).abs().max()) < 6e-3 * scale
+    assert float((q_f - q_u).abs().max()) <= 2 ** -7 * scale, "more than a bfloat16 rounding from the two-kernel path"
+    assert float((pages_f - pages_u).abs().max()) <= 2 ** -7 * scale
+    touched = torch.zeros(n_pages, P, dtype=torch.bool)
+    if writes:
+        for t in range(T_real):
+            r, pos = int(row_req[t]), int(positions[t])
+            pg = int(table[r, pos // P])
+            touched[pg, pos % P] = True
+            assert float((pages_f[pg, 0, :, pos % P] - k_ref[t]).abs().max()) < 6e-3 * scale
+            assert float((pages_f[pg, 1, :, pos % P] - v_ref[t]).abs().max()) < 6e-3 * scale
+    untouched = pages_f[~touched[:, None, None, :].expand(n_pages, 2, nkv, P)]
+    assert bool((untouched == 7.0).all()), "a slot outside the step's positions was written"
+
+
 @pytest.mark.parametrize("V", [512, 1000, 256000])
 def test_argmax_and_topk(ops, V):
     g = torch.Generator().manual_seed(10)

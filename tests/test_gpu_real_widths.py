@@ -107,6 +107,30 @@ def test_real_widths_match_plain(cases, name, dtype, mode):
         assert all(n > g.pool.n_pages for n, g in zip(runner.cache.pages_handed_out(), runner.cache.groups))
 
 
+@pytest.mark.parametrize("name", ["2b-widths-2layers-v4096-w100", "9b-widths-2layers-v4096-w100"])
+def test_a_prompt_whose_qkv_product_rotates_and_files_its_result(cases, name):
+    """700 and 50 tokens of two requests in one step at head size 256: so many rows that the q,k,v product runs as whole
+    tiles on CTA pairs and writes rotated q rows and the pages itself (checked by its launch count); then eight tokens
+    one by one, which read those pages.  Every logit against the plain implementation."""
+    from kungfu_b200 import api, ops
+    cfg, typed, arch, tensors, _, _ = cases(name, "bfloat16")
+    toks = {"a": helpers.random_tokens(708, helpers.quiet_vocab(cfg), 31), "b": helpers.random_tokens(50, helpers.quiet_vocab(cfg), 32)}
+    ref = {r: plain_gemma2.forward(cfg, tensors, t, device=DEV).float() for r, t in toks.items()}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks["a"][:700], "want": list(range(700))},
+                                     {"id": "b", "tokens": toks["b"], "want": list(range(50))}], "end": ["b"]}]
+    for i in range(8):
+        steps.append({"step": 1 + i, "entries": [{"id": "a", "tokens": [toks["a"][700 + i]], "want": [0]}], "end": ["a"] if i == 7 else []})
+    model = _model(typed, arch, tensors, "bfloat16")
+    runner = api.make_runner(typed, model, dtype="bfloat16", device=DEV, page_size=64, max_tokens=1024, max_requests=2,
+                             max_context=1024, batch=768)
+    fused_before = ops.fused_qkv_rope_launches
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert ops.fused_qkv_rope_launches == fused_before + cfg["num_hidden_layers"]
+    assert len(got) == 758
+    _check(got, ref, TOL["bfloat16"])
+    ops.raise_on_device_error()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_real_window_with_a_prompt_that_crosses_it(dtype):
     """2B widths, window 4,096, 4,200 tokens: whole, and in portions of 512 with the last 8 tokens one by one; the
