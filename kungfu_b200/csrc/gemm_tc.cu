@@ -518,15 +518,14 @@ struct RopeArgs {
   __nv_bfloat16* q_out;                                           // [T, nh * 256]
 };
 
-template <int EPI>
+template <int EPI, int PN>                                        // PN: tokens of the pair's tile = MMA N (256, or 128 for EPI_ROPE)
 __device__ __forceinline__ void
 gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __restrict__ out, int T, int N, int K, int ld_out,
                   float softcap, int act, int up_offset, int stages, int* __restrict__ error_flag, const RopeArgs& ra) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr bool ROPE = EPI == EPI_ROPE;
   constexpr int NACC = (GATED || ROPE) ? 2 : 1;
-  constexpr int PN = 256;                                         // tokens of the pair's tile = MMA N
-  constexpr int NBUF = NACC == 2 ? 1 : 2;                         // accumulator sets in tensor memory
+  constexpr int NBUF = NACC * PN * 2 <= 512 ? 2 : 1;              // accumulator sets in tensor memory (512 columns)
   constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (PN / 2) * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES * NACC + BH_BYTES;
   constexpr int TMEM_COLS = 512;
@@ -612,7 +611,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
         const int buf = ti % NBUF;
         if (ti >= NBUF && !mbar_wait(&acc_empty[buf], (uint32_t)((ti / NBUF) - 1) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem_base + buf * PN;
+        const uint32_t acc = tmem_base + buf * NACC * PN;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&full[s], ph)) { ok = false; break; }
           const uint64_t so = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));
@@ -641,7 +640,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
       const int buf = ti % NBUF;
       const int f0 = ((tile % n_ft) * 2 + (int)rank) * (ROPE ? 2 * BM : BM), t0 = (tile / n_ft) * PN;
       const int f = f0 + quarter * 32 + lane;
-      // ROPE: where this warp's 64 rows go, two rows per lane, looked up while the accumulator is still being filled:
+      // ROPE: where this warp's PN / 4 rows go (one or two rows per lane), looked up while the accumulator is still being filled:
       // for k and v heads the row's slot in the pages (in rows of 256), for q heads 0; -1 for rows of no request
       const int head = (tile % n_ft) * 2 + (int)rank;
       const bool is_q = ROPE && head < ra.nh, is_k = ROPE && !is_q && head < ra.nh + ra.nkv;
@@ -651,7 +650,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
       if (ROPE && rope_work) {
         const int kvh = is_k ? head - ra.nh : head - ra.nh - ra.nkv;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < PN / 128; ++cc) {
           const int t = t0 + col_half * (PN / 4) + cc * 32 + lane;
           int m = -1;
           if (t < T) {
@@ -673,13 +672,13 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t acc = lane_addr + buf * PN;
+      const uint32_t acc = lane_addr + buf * NACC * PN;
       if constexpr (ROPE) {
         // this CTA's head: a q head (rotated to q_out), a k head (rotated into the page), a v head (into the page) or none
         const int i = quarter * 32 + lane;                                           // the rotation pair (i, i + 128)
         if (rope_work) {
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {                                           // sixteen rows at a time
+          for (int cc = 0; cc < PN / 64; ++cc) {                                     // sixteen rows at a time
             const int c0 = col_half * (PN / 4) + cc * 16;
             // the rows' angles are all asked for before the accumulator is read and the first of them is used
             float cs[16], sn[16];
@@ -757,15 +756,16 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int up_offset,
                     int stages, int* __restrict__ error_flag) {
-  gemm_tc_pair_body<EPI>(tm_w, tm_x, out, T, N, K, ld_out, softcap, act, up_offset, stages, error_flag, RopeArgs{});
+  gemm_tc_pair_body<EPI, 256>(tm_w, tm_x, out, T, N, K, ld_out, softcap, act, up_offset, stages, error_flag, RopeArgs{});
 }
 
 // The q,k,v product of a prompt with head size 256 that rotates q and k and files k and v itself (no 32-bit q,k,v rows in
 // memory, no kernel after it): see RopeArgs.
+template <int PN>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_rope_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, int T, int N, int K,
                          int stages, int* __restrict__ error_flag, const __grid_constant__ RopeArgs ra) {
-  gemm_tc_pair_body<EPI_ROPE>(tm_w, tm_x, nullptr, T, N, K, 0, 0.f, 0, 0, stages, error_flag, ra);
+  gemm_tc_pair_body<EPI_ROPE, PN>(tm_w, tm_x, nullptr, T, N, K, 0, 0.f, 0, 0, stages, error_flag, ra);
 }
 
 // ---- CTA pairs with K cut inside a cluster, for a few hundred tokens ----------------------------------------------------
@@ -1030,6 +1030,7 @@ int g_plan_bn = 0, g_plan_splits = 0;               // a tuning build can fix th
 int g_pair = 1;             // many tokens: CTA pairs
 int g_pair_split = 1;       // a few hundred tokens: CTA pairs with K cut inside the cluster
 int g_pair_rope = 1;        // prompts, head size 256: the q,k,v product rotates and files its own result
+int g_rope_pn = 0;          // tuning: token tile of that product (0: chosen by the tile count)
 int pair_split_capacity(int splits);
 int stream_cluster_capacity(int splits);
 
@@ -1268,21 +1269,22 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, 
   return KF_OK;
 }
 
+template <int PN>
 int launch_pair_rope(const CUtensorMap& tw, const CUtensorMap& tx, int T, int N, int K, const RopeArgs& ra, int* error_flag,
                      cudaStream_t stream) {
-  constexpr int STAGE_BYTES = BM * BK * 2 * 2 + 128 * BK * 2;
+  constexpr int STAGE_BYTES = BM * BK * 2 * 2 + (PN / 2) * BK * 2;
   int stages = (SMEM_LIMIT - 2048) / STAGE_BYTES;
   if (stages > 8) stages = 8;
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + 512;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_pair_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_rope_kernel<PN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
       kf_record_cuda_error(cudaGetLastError());
       return KF_ERR_SETUP;
     }
     configured = true;
   }
-  const int n_tiles = kf_ceil_div(ra.nh + 2 * ra.nkv, 2) * kf_ceil_div(T, 256);
+  const int n_tiles = kf_ceil_div(ra.nh + 2 * ra.nkv, 2) * kf_ceil_div(T, PN);
   int pairs = kf_sm_count() / 2;
   if (pairs > n_tiles) pairs = n_tiles;
   cudaLaunchConfig_t cfg = {};
@@ -1304,7 +1306,7 @@ int launch_pair_rope(const CUtensorMap& tw, const CUtensorMap& tx, int T, int N,
   ++na;
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaLaunchKernelEx(&cfg, gemm_tc_pair_rope_kernel, tw, tx, T, N, K, stages, error_flag, ra);
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_rope_kernel<PN>, tw, tx, T, N, K, stages, error_flag, ra);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -1400,6 +1402,7 @@ KF_API void kf_set_gemm_persistent(int on) { g_persistent = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair(int on) { g_pair = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair_split(int on) { g_pair_split = on ? 1 : 0; }
 KF_API void kf_set_gemm_pair_rope(int on) { g_pair_rope = on ? 1 : 0; }
+KF_API void kf_set_gemm_rope_pn(int pn) { g_rope_pn = pn; }
 KF_API int kf_gemm_pair_split_capacity(int splits) { return pair_split_capacity(splits); }
 KF_API int kf_gemm_stream_cluster_capacity(int splits) { return stream_cluster_capacity(splits); }
 KF_API void kf_set_gemm_plan(int bn, int splits) { g_plan_bn = bn; g_plan_splits = splits; }   // products over more than 64 rows
@@ -1421,17 +1424,13 @@ KF_API int kf_test_gemm_give_up(unsigned long long limit_ns, int drop_from_stage
 }
 
 // Whether the q,k,v product of this step can rotate and file its own result: head size 256 rotated in full, bfloat16
-// everywhere, and so many rows that the product runs as whole 256 x 256 tiles on CTA pairs, one tile of two heads each.
+// everywhere, and so many rows that the product runs as whole tiles on CTA pairs.
 KF_API int kf_linear_rope_append_supported(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, int head_dim, int rot) {
   if (!g_pair || !g_pair_rope || head_dim != 2 * BM || rot != head_dim || T <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || encode_fn() == nullptr) return 0;
   int bn = 0, splits = 0;
   if (plan_linear(T, (n_heads + 2 * n_kv_heads) * head_dim, K, 0, &bn, &splits) != KF_OK) return 0;
-  // Two accumulators of 256 columns fill tensor memory, so this epilogue cannot run under the next tile's products as the
-  // plain one does: it pays while every pair has one tile (2,048 rows of 16 heads: 8.93 -> 8.68 ms for the 26-layer prompt),
-  // and costs where pairs have two (2,048 rows of 32 heads: 34.1 -> 34.6 ms for 42 layers).
-  const int n_tiles = kf_ceil_div(n_heads + 2 * n_kv_heads, 2) * kf_ceil_div(T, 256);
-  return bn == 256 && splits == 1 && n_tiles <= kf_sm_count() / 2;
+  return bn == 256 && splits == 1;
 }
 
 // x[T, K] . w[(n_heads + 2 n_kv_heads) * 256, K]^T with q and k rotated (pairs i, i + 128; cos, sin [T, 128] by row), q
@@ -1443,8 +1442,15 @@ KF_API int kf_linear_rope_append(const void* x, const void* w, int T, int K, int
   if (T <= 0) return KF_OK;
   if (!kf_linear_rope_append_supported(x, w, T, K, n_heads, n_kv_heads, 2 * BM, 2 * BM) || !cos_t || !sin_t) return KF_ERR_SIZE;
   const int N = (n_heads + 2 * n_kv_heads) * 2 * BM;
+  // Token tile: with 256 tokens a pair's tile is two heads x 256 tokens, twice a plain tile, and its two accumulators fill
+  // tensor memory (no epilogue under the next tile's products); with 128 tokens two sets fit and tiles are as many as plain
+  // ones.  Measured beside the two-kernel path (us per launch, 16 heads of 256 over 2304 / 32 heads over 3584): 768 rows
+  // 25.2 -> 34.1 (256) / 23.7 (128) and 54.6 -> 47.0 / 58.3; 2,048 rows 43.6 -> 35.5 / 41.1 and 112.4 -> 94.5 / 111.2: the
+  // large tile wherever its tiles occupy most pairs.
+  const int tiles256 = kf_ceil_div(n_heads + 2 * n_kv_heads, 2) * kf_ceil_div(T, 256);
+  const int pn = g_rope_pn ? g_rope_pn : (tiles256 * 5 >= (kf_sm_count() / 2) * 3 ? 256 : 128);
   CUtensorMap tw, txp;
-  if (!tensor_map(w, N, K, BM, &tw) || !tensor_map(x, T, K, 128, &txp)) return KF_ERR_SETUP;
+  if (!tensor_map(w, N, K, BM, &tw) || !tensor_map(x, T, K, pn / 2, &txp)) return KF_ERR_SETUP;
   RopeArgs ra;
   ra.cos_t = cos_t;
   ra.sin_t = sin_t;
@@ -1458,7 +1464,8 @@ KF_API int kf_linear_rope_append(const void* x, const void* w, int T, int K, int
   ra.write_kv = write_kv;
   ra.pages = (__nv_bfloat16*)pages;
   ra.q_out = (__nv_bfloat16*)q_out;
-  return launch_pair_rope(tw, txp, T, N, K, ra, error_flag, stream);
+  return pn == 128 ? launch_pair_rope<128>(tw, txp, T, N, K, ra, error_flag, stream)
+                   : launch_pair_rope<256>(tw, txp, T, N, K, ra, error_flag, stream);
 }
 
 // Whether the tensor-core kernel takes this product: bfloat16 operands, rows a multiple of 16 bytes, aligned bases.
