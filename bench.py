@@ -646,6 +646,60 @@ def micro_products(size: str = "2b") -> int:
     return 0
 
 
+def micro_qkv_rope(size: str = "2b") -> int:
+    """The q,k,v product of a prompt with rotation and cache append: the product that files its own result
+    (`ops.linear_rope_kv_append`) beside the product that leaves 32-bit rows plus the kernel that rotates and files them;
+    four launches over distinct weights and pages replayed from a CUDA graph, one JSON line per row count."""
+    import torch
+    from kungfu_b200 import api, ops
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    sz = SIZES[size]
+    nh, nkv, d, K, P, n_w = sz["num_attention_heads"], sz["num_key_value_heads"], sz["head_dim"], sz["hidden_size"], 64, 4
+    N = (nh + 2 * nkv) * d
+
+    class View:
+        def __init__(self, pages):
+            self.pages, self.page_size, self.group, self.writes = pages, P, 0, True
+
+    class Ctx:
+        pass
+    for rows in (768, 1024, 2048, 4096):
+        ws = [(torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16) for _ in range(n_w)]
+        x = torch.randn(rows, K, device=device).to(torch.bfloat16)
+        n_pages = -(-rows // P)
+        ctx = Ctx()
+        ctx.positions = torch.arange(rows, dtype=torch.int32, device=device)
+        ctx.row_req = torch.zeros(rows, dtype=torch.int32, device=device)
+        ctx.block_tables = [torch.arange(n_pages, dtype=torch.int32, device=device)[None, :].contiguous()]
+        views = [View(torch.zeros(n_pages, 2, nkv, P, d, dtype=torch.bfloat16, device=device)) for _ in range(n_w)]
+        inv = (10000.0 ** (-2.0 * torch.arange(d // 2, dtype=torch.float64) / d)).float().to(device)
+        ang = ctx.positions.float()[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+        q = torch.empty(rows, nh * d, dtype=torch.bfloat16, device=device)
+        qkv = torch.empty(rows, N, device=device)
+        line = {"micro": "qkv-rope", "size": size, "rows": rows}
+
+        def two():
+            for w, v in zip(ws, views):
+                ops.linear(x, w, qkv)
+                ops.rope_kv_append(qkv, cos, sin, d, nh, nkv, d, ctx, v, q)
+
+        def fused():
+            for w, v in zip(ws, views):
+                if not ops.linear_rope_kv_append(x, w, cos, sin, d, nh, nkv, d, ctx, v, q):
+                    raise RuntimeError("declined")
+        line["two_kernels_us"] = round(_graph_us(torch, two, n_w), 1)
+        try:
+            line["fused_us"] = round(_graph_us(torch, fused, n_w), 1)
+        except RuntimeError:
+            line["fused_us"] = None                       # this shape keeps the two-kernel path (head size 128)
+        print(json.dumps(line))
+        del ws, views
+    ops.raise_on_device_error()
+    return 0
+
+
 def _graph_us(torch, run, n_launches: int, reps: int = 10) -> float:
     """Microseconds per launch of `run()` (which issues `n_launches` kernels) replayed from a CUDA graph."""
     run()
@@ -809,12 +863,13 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
-    ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "reference"],
+    ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
                     help="time kernels alone instead of the model step")
     args = ap.parse_args()
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
-                "products": lambda: micro_products(args.size), "reference": micro_reference}[args.micro]()
+                "products": lambda: micro_products(args.size), "qkv-rope": lambda: micro_qkv_rope(args.size),
+                "reference": micro_reference}[args.micro]()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built "
