@@ -503,19 +503,20 @@ __device__ __forceinline__ void cluster_sync_all() {
 constexpr int PAIR_THREADS = 576;
 constexpr int PAIR_SPLIT_STAGES = 6;                            // the split variant parks 128 KB of partial sums in its ring
 
-// What the q,k,v product needs to rotate and file its own result (EPI_ROPE, head size 256): a CTA owns one head, its two
-// accumulators are the head's features i and i + 128 (weight rows h * 256 + i and h * 256 + 128 + i), so one thread holds
-// both elements of a rotation pair.  q heads go to q_out rotated, k heads rotated and v heads as they are into the request's
+// What the q,k,v product needs to rotate and file its own result (EPI_ROPE): a CTA owns one head of 256 (or two of 128), its
+// two accumulators are the head's features i and i + half (weight rows h * d + i and h * d + half + i; with two heads the
+// second head's in lanes 64-127, fetched as boxes of 64 weight rows), so one thread holds both elements of a rotation pair.  q heads go to q_out rotated, k heads rotated and v heads as they are into the request's
 // page at the token's position; rows of no request (padding) give zero q and write no keys.
 struct RopeArgs {
-  const float* cos_t;                                             // [T, 128] by token row
+  const float* cos_t;                                             // [T, half] by token row
   const float* sin_t;
   const int* positions;
   const int* row_req;
   const int* block_table;
   int table_stride, page_size, nh, nkv, write_kv;
-  __nv_bfloat16* pages;                                           // [page][k, v][nkv][page_size][256]
-  __nv_bfloat16* q_out;                                           // [T, nh * 256]
+  int half;                                                       // head size / 2: 128 (a CTA holds one head) or 64 (two heads)
+  __nv_bfloat16* pages;                                           // [page][k, v][nkv][page_size][head size]
+  __nv_bfloat16* q_out;                                           // [T, nh * head size]
 };
 
 template <int EPI, int PN>                                        // PN: tokens of the pair's tile = MMA N (256, or 128 for EPI_ROPE)
@@ -545,7 +546,8 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int n_feat = GATED ? up_offset : N;
   // ROPE: a CTA's "feature tile" is one head (its 128 rotation pairs), a pair's tile two heads
-  const int n_ft = ROPE ? (ra.nh + 2 * ra.nkv + 1) / 2 : (n_feat + 2 * BM - 1) / (2 * BM), n_tt = (T + PN - 1) / PN;
+  const int hpc = ROPE ? BM / ra.half : 1;                        // heads per CTA
+  const int n_ft = ROPE ? (ra.nh + 2 * ra.nkv + 2 * hpc - 1) / (2 * hpc) : (n_feat + 2 * BM - 1) / (2 * BM), n_tt = (T + PN - 1) / PN;
   const int n_tiles = n_ft * n_tt;
   const int nkb = (K + BK - 1) / BK;
   const int second = ROPE ? BM : up_offset;                       // weight rows of the second accumulator, after the first's
@@ -591,8 +593,15 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           const uint32_t bar = full0 + 8u * (uint32_t)s;
           const int k = kb * BK;
-          tma_load_2d_pair(st, &tm_w, bar, k, f0);
-          if (NACC == 2) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, second + f0);
+          if (ROPE && hpc == 2) {                                                    // two heads of 128: four boxes of 64 weight rows
+            tma_load_2d_pair(st, &tm_w, bar, k, f0);
+            tma_load_2d_pair(st + A_BYTES / 2, &tm_w, bar, k, f0 + BM);
+            tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, f0 + BM / 2);
+            tma_load_2d_pair(st + A_BYTES + A_BYTES / 2, &tm_w, bar, k, f0 + BM + BM / 2);
+          } else {
+            tma_load_2d_pair(st, &tm_w, bar, k, f0);
+            if (NACC == 2) tma_load_2d_pair(st + A_BYTES, &tm_w, bar, k, second + f0);
+          }
           tma_load_2d_pair(st + A_BYTES * NACC, &tm_x, bar, k, t0);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -642,7 +651,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
       const int f = f0 + quarter * 32 + lane;
       // ROPE: where this warp's PN / 4 rows go (one or two rows per lane), looked up while the accumulator is still being filled:
       // for k and v heads the row's slot in the pages (in rows of 256), for q heads 0; -1 for rows of no request
-      const int head = (tile % n_ft) * 2 + (int)rank;
+      const int head = ((tile % n_ft) * 2 + (int)rank) * hpc + (hpc == 2 ? quarter >> 1 : 0);
       const bool is_q = ROPE && head < ra.nh, is_k = ROPE && !is_q && head < ra.nh + ra.nkv;
       const bool is_v = ROPE && !is_q && !is_k && head < ra.nh + 2 * ra.nkv;
       const bool rope_work = is_q || ((is_k || is_v) && ra.write_kv);
@@ -675,7 +684,8 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
       const uint32_t acc = lane_addr + buf * NACC * PN;
       if constexpr (ROPE) {
         // this CTA's head: a q head (rotated to q_out), a k head (rotated into the page), a v head (into the page) or none
-        const int i = quarter * 32 + lane;                                           // the rotation pair (i, i + 128)
+        const int i = (quarter * 32 + lane) & (ra.half - 1);                         // the rotation pair (i, i + half) of the head
+        const int hd = 2 * ra.half;
         if (rope_work) {
 #pragma unroll 1
           for (int cc = 0; cc < PN / 64; ++cc) {                                     // sixteen rows at a time
@@ -686,8 +696,8 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int tc = min(t0 + c0 + j, T - 1);
-                cs[j] = __ldg(ra.cos_t + (size_t)tc * BM + i);
-                sn[j] = __ldg(ra.sin_t + (size_t)tc * BM + i);
+                cs[j] = __ldg(ra.cos_t + (size_t)tc * ra.half + i);
+                sn[j] = __ldg(ra.sin_t + (size_t)tc * ra.half + i);
               }
             }
             float v[16], u[16];
@@ -707,13 +717,13 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
               }
               if (is_q) {
                 if (m < 0) a = b = 0.f;
-                __nv_bfloat16* q = ra.q_out + ((size_t)t * ra.nh + head) * (2 * BM) + i;
+                __nv_bfloat16* q = ra.q_out + ((size_t)t * ra.nh + head) * hd + i;
                 q[0] = __float2bfloat16_rn(a);
-                q[BM] = __float2bfloat16_rn(b);
+                q[ra.half] = __float2bfloat16_rn(b);
               } else if (m >= 0) {
-                __nv_bfloat16* kv = ra.pages + (size_t)m * (2 * BM) + i;
+                __nv_bfloat16* kv = ra.pages + (size_t)m * hd + i;
                 kv[0] = __float2bfloat16_rn(a);
-                kv[BM] = __float2bfloat16_rn(b);
+                kv[ra.half] = __float2bfloat16_rn(b);
               }
             }
           }
@@ -1284,7 +1294,7 @@ int launch_pair_rope(const CUtensorMap& tw, const CUtensorMap& tx, int T, int N,
     }
     configured = true;
   }
-  const int n_tiles = kf_ceil_div(ra.nh + 2 * ra.nkv, 2) * kf_ceil_div(T, PN);
+  const int n_tiles = kf_ceil_div(ra.nh + 2 * ra.nkv, 2 * (BM / ra.half)) * kf_ceil_div(T, PN);
   int pairs = kf_sm_count() / 2;
   if (pairs > n_tiles) pairs = n_tiles;
   cudaLaunchConfig_t cfg = {};
@@ -1423,35 +1433,37 @@ KF_API int kf_test_gemm_give_up(unsigned long long limit_ns, int drop_from_stage
   return KF_OK;
 }
 
-// Whether the q,k,v product of this step can rotate and file its own result: head size 256 rotated in full, bfloat16
+// Whether the q,k,v product of this step can rotate and file its own result: head size 256 or 128 rotated in full, bfloat16
 // everywhere, and so many rows that the product runs as whole tiles on CTA pairs.
 KF_API int kf_linear_rope_append_supported(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, int head_dim, int rot) {
-  if (!g_pair || !g_pair_rope || head_dim != 2 * BM || rot != head_dim || T <= 0) return 0;
+  if (!g_pair || !g_pair_rope || (head_dim != 2 * BM && head_dim != BM) || rot != head_dim || T <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || encode_fn() == nullptr) return 0;
   int bn = 0, splits = 0;
   if (plan_linear(T, (n_heads + 2 * n_kv_heads) * head_dim, K, 0, &bn, &splits) != KF_OK) return 0;
   return bn == 256 && splits == 1;
 }
 
-// x[T, K] . w[(n_heads + 2 n_kv_heads) * 256, K]^T with q and k rotated (pairs i, i + 128; cos, sin [T, 128] by row), q
-// written to q_out[T, n_heads * 256] and k, v into the pages of the rows' requests (if write_kv); all bfloat16.
-KF_API int kf_linear_rope_append(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, const float* cos_t,
+// x[T, K] . w[(n_heads + 2 n_kv_heads) * d, K]^T with q and k rotated (pairs i, i + d / 2; cos, sin [T, d / 2] by row), q
+// written to q_out[T, n_heads * d] and k, v into the pages of the rows' requests (if write_kv); all bfloat16, d 256 or 128.
+KF_API int kf_linear_rope_append(const void* x, const void* w, int T, int K, int n_heads, int n_kv_heads, int head_dim, const float* cos_t,
                                  const float* sin_t, const int* positions, const int* row_req, const int* block_table,
                                  int table_stride, int page_size, void* pages, void* q_out, int write_kv, int* error_flag,
                                  cudaStream_t stream) {
   if (T <= 0) return KF_OK;
-  if (!kf_linear_rope_append_supported(x, w, T, K, n_heads, n_kv_heads, 2 * BM, 2 * BM) || !cos_t || !sin_t) return KF_ERR_SIZE;
-  const int N = (n_heads + 2 * n_kv_heads) * 2 * BM;
+  if (!kf_linear_rope_append_supported(x, w, T, K, n_heads, n_kv_heads, head_dim, head_dim) || !cos_t || !sin_t) return KF_ERR_SIZE;
+  const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+  const int hpc = 2 * BM / head_dim;                              // heads per CTA: 1 or 2
   // Token tile: with 256 tokens a pair's tile is two heads x 256 tokens, twice a plain tile, and its two accumulators fill
   // tensor memory (no epilogue under the next tile's products); with 128 tokens two sets fit and tiles are as many as plain
   // ones.  Measured beside the two-kernel path (us per launch, 16 heads of 256 over 2304 / 32 heads over 3584): 768 rows
   // 25.2 -> 34.1 (256) / 23.7 (128) and 54.6 -> 47.0 / 58.3; 2,048 rows 43.6 -> 35.5 / 41.1 and 112.4 -> 94.5 / 111.2: the
   // large tile wherever its tiles occupy most pairs.
-  const int tiles256 = kf_ceil_div(n_heads + 2 * n_kv_heads, 2) * kf_ceil_div(T, 256);
+  const int tiles256 = kf_ceil_div(n_heads + 2 * n_kv_heads, 2 * hpc) * kf_ceil_div(T, 256);
   const int pn = g_rope_pn ? g_rope_pn : (tiles256 * 5 >= (kf_sm_count() / 2) * 3 ? 256 : 128);
   CUtensorMap tw, txp;
-  if (!tensor_map(w, N, K, BM, &tw) || !tensor_map(x, T, K, pn / 2, &txp)) return KF_ERR_SETUP;
+  if (!tensor_map(w, N, K, BM / hpc, &tw) || !tensor_map(x, T, K, pn / 2, &txp)) return KF_ERR_SETUP;
   RopeArgs ra;
+  ra.half = head_dim / 2;
   ra.cos_t = cos_t;
   ra.sin_t = sin_t;
   ra.positions = positions;

@@ -394,7 +394,7 @@ def rope_kv_append(qkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_
 def linear_rope_kv_append(x, wqkv, cos, sin, rot: int, n_heads: int, n_kv_heads: int, head_dim: int, ctx, cache, q_out) -> bool:
     """q,k,v = x . wqkv^T, q and k rotated, q to q_out, k and v into the pages of `cache`: one launch whose product files
     its own result (no 32-bit q,k,v rows in memory).  True if it ran; False if this step does not qualify (then the
-    caller runs `linear` and `rope_kv_append`): it takes bfloat16 operands, q and pages, head size 256 rotated in full,
+    caller runs `linear` and `rope_kv_append`): it takes bfloat16 operands, q and pages, head size 256 or 128 rotated in full,
     and so many rows that the product runs as whole tiles on CTA pairs."""
     T, K = x.shape
     if not (use_tensor_cores and fused_qkv_rope and cos is not None and x.dtype == torch.bfloat16
@@ -411,7 +411,7 @@ def linear_rope_kv_append(x, wqkv, cos, sin, rot: int, n_heads: int, n_kv_heads:
     sc = _dev_scratch(x.device)
     global fused_qkv_rope_launches
     fused_qkv_rope_launches += 1
-    _check(lib.kf_linear_rope_append(_p(x), _p(wqkv), T, K, n_heads, n_kv_heads, _p(cos), _p(sin), _p(ctx.positions),
+    _check(lib.kf_linear_rope_append(_p(x), _p(wqkv), T, K, n_heads, n_kv_heads, head_dim, _p(cos), _p(sin), _p(ctx.positions),
                                      _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, _p(cache.pages), _p(q_out),
                                      int(cache.writes), _p(sc["error"]), _stream()), "linear_rope_kv_append")
     return True

@@ -682,16 +682,18 @@ def test_rope_kv_append(ops, qd, kvd, nh, nkv, d, rot, P):
     assert bool((untouched == 7.0).all()), "a slot outside the step's positions was written"
 
 
-@pytest.mark.parametrize("nh,nkv,K,lens,writes", [(8, 4, 2304, [700, 330], True), (3, 1, 264, [1500, 1480, 20], True),
-                                                  (2, 2, 512, [3100], False), (16, 8, 520, [300, 257], True),
-                                                  (16, 8, 328, [1300, 1000], True)])
-def test_qkv_product_that_rotates_and_files_its_result(ops, nh, nkv, K, lens, writes):
-    """The q,k,v product of a long prompt with head size 256 writes rotated q rows and the pages itself.  Against float64
+@pytest.mark.parametrize("nh,nkv,d,K,lens,writes", [(8, 4, 256, 2304, [700, 330], True), (3, 1, 256, 264, [1500, 1480, 20], True),
+                                                    (2, 2, 256, 512, [3100], False), (16, 8, 256, 520, [300, 257], True),
+                                                    (16, 8, 256, 328, [1300, 1000], True), (32, 16, 128, 520, [600], True),
+                                                    (5, 1, 128, 264, [2000, 1000], True)])
+def test_qkv_product_that_rotates_and_files_its_result(ops, nh, nkv, d, K, lens, writes):
+    """The q,k,v product of a long prompt with head size 256 or 128 writes rotated q rows and the pages itself.  Against float64
     from the same bfloat16 operands, and against the two-kernel path (32-bit rows, then rotation and append) to within one
     bfloat16 rounding; requests at different positions on scattered pages, padding rows, an odd number of heads (the last CTA
     pair has one head), a K that is no multiple of 64, a cache that is not written; tiles of 128 tokens (the first three
-    cases: few tiles) and of 256 (the last two; the last with more tiles than CTA pairs)."""
-    d, P = 256, 64
+    cases: few tiles) and of 256 (the next two; the second with more tiles than CTA pairs); head size 128 puts two heads
+    into a CTA (the last two cases; seven heads leave the last CTA one)."""
+    P = 64
     g = torch.Generator().manual_seed(nh * 100 + K)
     starts = [37, 0, 130][:len(lens)]
     T_real = sum(lens)

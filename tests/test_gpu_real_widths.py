@@ -107,9 +107,9 @@ def test_real_widths_match_plain(cases, name, dtype, mode):
         assert all(n > g.pool.n_pages for n, g in zip(runner.cache.pages_handed_out(), runner.cache.groups))
 
 
-@pytest.mark.parametrize("name", ["2b-widths-2layers-v4096-w100", "9b-widths-2layers-v4096-w100"])
+@pytest.mark.parametrize("name", list(SIZES))
 def test_a_prompt_whose_qkv_product_rotates_and_files_its_result(cases, name):
-    """700 and 50 tokens of two requests in one step at head size 256: so many rows that the q,k,v product runs as whole
+    """700 and 50 tokens of two requests in one step at head sizes 256 and 128: so many rows that the q,k,v product runs as whole
     tiles on CTA pairs and writes rotated q rows and the pages itself (checked by its launch count); then eight tokens
     one by one, which read those pages.  Every logit against the plain implementation."""
     from kungfu_b200 import api, ops
