@@ -16,6 +16,9 @@
 // Ragged edges (N, T, K not multiples of the tile) are zero-filled by TMA and masked at the store.
 // Every wait on an mbarrier is bounded: after the limit the kernel records an error code and leaves through the
 // common exit that frees tensor memory.
+// Further down, for more rows: a persistent kernel with two accumulator sets (128-token tiles), CTA pairs
+// (cta_group::2) on 256 x 256 tiles, the same pairs with K cut inside a cluster of 4 or 8 CTAs for a few hundred rows,
+// and the pairs' q,k,v product that rotates q and k and files k and v in its epilogue; `plan_linear` says which runs.
 // The reference runs these products as 32-bit SIMT tiles (crates/kf-backend-cuda/src/kernels/quant.cuh:110-171).
 #include "common.cuh"
 #include "tc_common.cuh"
