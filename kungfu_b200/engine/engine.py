@@ -265,5 +265,21 @@ class Engine:
             ops.raise_on_device_error(self.runner.device)
         return [list(self.requests[i].output) for i in ids]
 
+    def warm_up(self) -> None:
+        """Run a few tokens of 1, 2, 4, ... up to `parallel` one-token requests, greedy and with a temperature, so that the
+        decode steps of every batch bucket are captured as CUDA graphs before the first real request (a layout's first step
+        is launched kernel by kernel and its second is captured; from the third on it is one replay).  Optional; call it
+        when the engine is idle."""
+        if not self.idle:
+            raise RuntimeError("warm_up() wants an idle engine")
+        limit = self.runner.cache.max_requests
+        n = 1
+        while True:
+            for s in (Sampling(temperature=0.0), Sampling(temperature=0.8)):
+                self.generate([[1 % self.runner.vocab]] * n, s, max_tokens=4, ignore_eos=True)
+            if n >= limit:
+                break
+            n = min(2 * n, limit)
+
     def finish_reason(self, request_id: Hashable) -> str | None:
         return self.requests[request_id].finish_reason

@@ -227,6 +227,24 @@ def test_mixed_steps_replayed_from_graphs_give_the_plain_tokens(tmp_path):
             assert float(row.max() - row[tok]) <= 2 * 2e-2 * float(logits.abs().max())
 
 
+def test_warm_up_captures_the_decode_graphs(tmp_path):
+    """After `Engine.warm_up()` the decode steps of every batch bucket replay from graphs; what a request generates
+    afterwards is what the plain implementation gives, and the warm-up leaves no request, page or state behind."""
+    from kungfu_b200 import Engine
+    from kungfu_b200.sampling import Sampling
+    cfg = helpers.TINY_A
+    folder = helpers.write_model(str(tmp_path / "m"), cfg, seed=6, dtype=torch.bfloat16)
+    tensors = helpers.read_tensors(folder)
+    e = Engine(folder, dtype="float32", device=DEV, ctx=64, batch=32, parallel=4, page_size=4)
+    e.warm_up()
+    assert e.idle and e.runner.cache.n_live == 0
+    assert e.runner.cache.free_pages() == [g.pool.n_pages for g in e.runner.cache.groups]
+    captured = {k[1] for k, st in e.runner._graphs.items() if isinstance(k, tuple) and k[0] == "sample" and st["graph"] is not None}
+    assert {1, 2, 4} <= captured
+    prompt = helpers.random_tokens(9, cfg["vocab_size"], 5)
+    assert e.generate([prompt], Sampling(temperature=0.0), max_tokens=6, ignore_eos=True) == [pg.greedy(cfg, tensors, prompt, 6)]
+
+
 def test_many_requests_of_random_lengths_under_a_tight_cache(tmp_path):
     """Two dozen requests of random prompt lengths through one engine with six state slots, a budget of 96 rows and a
     cache of forty pages of 16 tokens: admission in waves, prompts fed in portions beside decoding
